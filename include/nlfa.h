@@ -1,0 +1,130 @@
+/*
+ * nlfa -- causal / sliding-window flash attention for NVIDIA B200 (sm_100a).
+ *
+ * Plain C ABI.  The caller owns every buffer (inputs, outputs, the logsumexp
+ * tape and the backward's scratch); the library allocates no device memory and
+ * launches on the stream it is given, on the device that is current.
+ *
+ * This is the native boundary behind nanolab's `--flash_cuda` path.  It stands
+ * where the reference's pybind11 module `nanolab_flash_attn` stands
+ * (nanolab/csrc/flash_attn_cuda.cu:1815-1825: `fwd`, `bwd`, `mma_probe`).
+ *
+ * Layout contract (same as nanolab/csrc/flash_attn_cuda.cu:1628-1650, :1756-1762):
+ *   q, o, dout, dq : contiguous [B, T, H,   D]
+ *   k, v, dk, dv   : contiguous [B, T, Hkv, D],  Hkv > 0 and H % Hkv == 0
+ *   lse, delta     : contiguous [B, H, T] float32; lse is a natural-log logsumexp
+ *   all of q/k/v/o/dout/dq/dk/dv share one dtype; base pointers 16-byte aligned
+ *   D in {32, 64, 128}
+ *
+ * Mask: query i attends key j iff  j <= i  and, when window > 0,
+ *   (j > i - (window - sinks)  or  j < sinks)   with 0 <= sinks < window
+ * which is nanolab/mixers.py:125-132 (`sliding_window_mask`).  window == 0 is
+ * plain causal attention (the only mask the reference kernel has).
+ */
+#ifndef NLFA_H_
+#define NLFA_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of q/k/v/o and the gradients */
+#define NLFA_DTYPE_F32 0
+#define NLFA_DTYPE_F16 1
+#define NLFA_DTYPE_BF16 2
+
+/* kernel family; mirrors `use_mma` of nanolab/flash_cuda.py:233-279
+ * (None -> AUTO, False -> SIMT, True -> TENSOR) */
+#define NLFA_PATH_AUTO 0
+#define NLFA_PATH_SIMT 1   /* fp32 FMA kernels: every dtype, every head dim */
+#define NLFA_PATH_TENSOR 2 /* TMA + tcgen05 + TMEM kernels: f16/bf16, D in {64,128} */
+
+/* status codes: 0 is success, everything else is a refusal or a failure */
+#define NLFA_OK 0
+#define NLFA_ERR_NULL_POINTER 1
+#define NLFA_ERR_BAD_SHAPE 2
+#define NLFA_ERR_BAD_DTYPE 3
+#define NLFA_ERR_BAD_HEAD_DIM 4
+#define NLFA_ERR_BAD_WINDOW 5
+#define NLFA_ERR_MISALIGNED 6
+#define NLFA_ERR_UNSUPPORTED_PATH 7
+#define NLFA_ERR_NOT_SM100 8
+#define NLFA_ERR_CUDA 9
+#define NLFA_ERR_DEVICE_TIMEOUT 10
+#define NLFA_ERR_SCRATCH_TOO_SMALL 11
+#define NLFA_ERR_SELFTEST_MISMATCH 12
+
+/* Library version, bumped when the ABI changes. */
+int nlfa_version(void);
+
+/* Human-readable text for a status code; never NULL. */
+const char* nlfa_strerror(int status);
+
+/* 1 if the current device can run the tensor-core path (compute capability
+ * 10.x), else 0.  Replaces the capability half of the reference's load-time
+ * probe (nanolab/flash_cuda.py:59-88). */
+int nlfa_device_supported(void);
+
+/* The path AUTO resolves to for this dtype and head dim (NLFA_PATH_SIMT or
+ * NLFA_PATH_TENSOR), or a negative status code if the combination is refused.
+ * Plays the role of the reference's dtype x head_dim dispatch
+ * (nanolab/csrc/flash_attn_cuda.cu:1592-1626). */
+int nlfa_resolve_path(int dtype, int head_dim, int path);
+
+/* Forward: O = softmax(scale * Q K^T + mask) V and the per-row logsumexp.
+ * Replaces `flash_attn_fwd` (nanolab/csrc/flash_attn_cuda.cu:1655-1704) and the
+ * kernels it launches (:147-281, :583-797); unlike it, the caller allocates o
+ * and lse.  B, T or H of zero is a successful no-op (:1668). */
+int nlfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T,
+             int H, int Hkv, int D, float scale, int window, int sinks, int dtype, int path,
+             void* stream);
+
+/* Bytes of device scratch `nlfa_bwd` needs (the Delta tape, [B,H,T] float32).
+ * The reference allocates the same tensor itself (flash_attn_cuda.cu:1770-1773). */
+size_t nlfa_bwd_scratch_bytes(int B, int T, int H);
+
+/* Backward: Delta = rowsum(dO * O), then dQ, dK, dV with P recomputed from the
+ * taped lse.  Replaces `flash_attn_bwd` (nanolab/csrc/flash_attn_cuda.cu:1744-1813)
+ * and its launch sequence (:1518-1587): Delta kernel, dQ kernel, dK/dV kernel on
+ * one stream, no atomics, bit-reproducible.  `scratch` must hold
+ * nlfa_bwd_scratch_bytes(B, T, H) bytes. */
+int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+             const float* lse, void* dq, void* dk, void* dv, void* scratch, size_t scratch_bytes,
+             int B, int T, int H, int Hkv, int D, float scale, int window, int sinks, int dtype,
+             int path, void* stream);
+
+/* Bytes of device workspace `nlfa_selftest` needs. */
+size_t nlfa_selftest_workspace_bytes(void);
+
+/* Load-time hardware check.  Runs one 128-row tile through the exact operand
+ * paths the tensor-core kernels use (TMA 128B-swizzled tiles, K-major and
+ * MN-major shared-memory descriptors, an A operand read from TMEM, TMEM loads)
+ * and compares with a float reference computed on the host from the same
+ * rounded inputs.  max_abs_err[0] is the S = Q K^T tile, [1] the O = P V tile
+ * (both relative to the largest reference magnitude).  Returns
+ * NLFA_ERR_SELFTEST_MISMATCH when either exceeds 1e-2.  Replaces `mma_probe`
+ * (nanolab/csrc/flash_attn_cuda.cu:1710-1741) and its caller `_probe_mma`
+ * (nanolab/flash_cuda.py:59-88), whose job was the same for the mma.sync
+ * fragment layout.  Synchronises the stream. */
+int nlfa_selftest(int dtype, int head_dim, void* workspace, size_t workspace_bytes,
+                  float* max_abs_err, void* stream);
+
+/* Diagnostic form of the self-test: the caller supplies the 128 x D tiles q, k,
+ * v (device, 16-bit, row-major) and receives the raw products s_out [128,128]
+ * and o_out [128,D] (device, float32), where O = round16(S) V.  No counterpart
+ * in the reference. */
+int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,
+                        float* s_out, float* o_out, void* stream);
+
+/* Reads (and clears) the device status word that bounded waits inside the
+ * kernels write when they give up.  Synchronises the device.  Returns NLFA_OK
+ * or NLFA_ERR_DEVICE_TIMEOUT; *raw receives the raw word when raw != NULL. */
+int nlfa_device_status(unsigned* raw);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NLFA_H_ */

@@ -1,0 +1,310 @@
+// C-ABI entry points: argument validation, path selection, tensor-map encoding,
+// the device status word, and the host half of the self-test.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace nlfa {
+
+// Written by bounded waits inside the kernels when they give up.
+__device__ unsigned g_status_word;
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+unsigned* g_status_ptr[kMaxDevices];
+
+// Device address of the status word on the current device (looked up once per device).
+unsigned* status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (g_status_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_status_word) != cudaSuccess) return nullptr;
+    g_status_ptr[dev] = static_cast<unsigned*>(ptr);
+  }
+  return g_status_ptr[dev];
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_problem(const Problem& p) {
+  if (p.B < 0 || p.T < 0 || p.H < 0 || p.Hkv <= 0 || p.H % p.Hkv != 0) return NLFA_ERR_BAD_SHAPE;
+  if (p.dtype != NLFA_DTYPE_F32 && p.dtype != NLFA_DTYPE_F16 && p.dtype != NLFA_DTYPE_BF16)
+    return NLFA_ERR_BAD_DTYPE;
+  if (p.D != 32 && p.D != 64 && p.D != 128) return NLFA_ERR_BAD_HEAD_DIM;
+  if (p.window < 0 || p.sinks < 0) return NLFA_ERR_BAD_WINDOW;
+  if (p.window == 0 ? p.sinks != 0 : p.sinks >= p.window) return NLFA_ERR_BAD_WINDOW;
+  if (!(p.scale == p.scale)) return NLFA_ERR_BAD_SHAPE;
+  return NLFA_OK;
+}
+
+float bits_to_float(uint16_t bits, int dtype) {
+  if (dtype == NLFA_DTYPE_BF16) {
+    uint32_t w = static_cast<uint32_t>(bits) << 16;
+    float f;
+    std::memcpy(&f, &w, 4);
+    return f;
+  }
+  __half_raw r;
+  r.x = bits;
+  return __half2float(__half(r));
+}
+
+uint16_t float_to_bits(float x, int dtype) {
+  if (dtype == NLFA_DTYPE_BF16) {
+    __nv_bfloat16 b = __float2bfloat16_rn(x);
+    uint16_t u;
+    std::memcpy(&u, &b, 2);
+    return u;
+  }
+  __half hh = __float2half_rn(x);
+  uint16_t u;
+  std::memcpy(&u, &hh, 2);
+  return u;
+}
+
+}  // namespace
+
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, int heads, int D,
+                  int rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return NLFA_ERR_CUDA;
+  if (!aligned16(base)) return NLFA_ERR_MISALIGNED;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(heads),
+                              static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(D) * 2,
+                                 static_cast<cuuint64_t>(heads) * D * 2,
+                                 static_cast<cuuint64_t>(T) * heads * D * 2};
+  const cuuint32_t box[4] = {64u, 1u, static_cast<cuuint32_t>(rows), 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  const CUtensorMapDataType dt =
+      dtype == NLFA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? NLFA_OK : NLFA_ERR_CUDA;
+}
+
+}  // namespace nlfa
+
+using namespace nlfa;
+
+extern "C" {
+
+int nlfa_version(void) { return 1; }
+
+const char* nlfa_strerror(int status) {
+  switch (status < 0 ? -status : status) {
+    case NLFA_OK: return "ok";
+    case NLFA_ERR_NULL_POINTER: return "null pointer argument";
+    case NLFA_ERR_BAD_SHAPE: return "bad shape (need B,T,H >= 0, Hkv > 0, H % Hkv == 0, finite scale)";
+    case NLFA_ERR_BAD_DTYPE: return "unsupported dtype (float32, float16, bfloat16)";
+    case NLFA_ERR_BAD_HEAD_DIM: return "unsupported head dim (32, 64, 128)";
+    case NLFA_ERR_BAD_WINDOW: return "bad window/sinks (need window >= 0 and 0 <= sinks < window)";
+    case NLFA_ERR_MISALIGNED: return "base pointer is not 16-byte aligned";
+    case NLFA_ERR_UNSUPPORTED_PATH: return "tensor-core path needs float16/bfloat16 and head dim 64 or 128";
+    case NLFA_ERR_NOT_SM100: return "device is not compute capability 10.x";
+    case NLFA_ERR_CUDA: return "CUDA runtime or driver call failed";
+    case NLFA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
+    case NLFA_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small";
+    case NLFA_ERR_SELFTEST_MISMATCH: return "tensor-core self-test disagrees with the host reference";
+  }
+  return "unknown status";
+}
+
+int nlfa_device_supported(void) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return 0;
+  return major == 10 ? 1 : 0;
+}
+
+int nlfa_resolve_path(int dtype, int head_dim, int path) {
+  if (dtype != NLFA_DTYPE_F32 && dtype != NLFA_DTYPE_F16 && dtype != NLFA_DTYPE_BF16)
+    return -NLFA_ERR_BAD_DTYPE;
+  if (head_dim != 32 && head_dim != 64 && head_dim != 128) return -NLFA_ERR_BAD_HEAD_DIM;
+  const bool tensor_ok = dtype != NLFA_DTYPE_F32 && (head_dim == 64 || head_dim == 128);
+  if (path == NLFA_PATH_SIMT) return NLFA_PATH_SIMT;
+  if (path == NLFA_PATH_TENSOR) return tensor_ok ? NLFA_PATH_TENSOR : -NLFA_ERR_UNSUPPORTED_PATH;
+  if (path == NLFA_PATH_AUTO) return tensor_ok ? NLFA_PATH_TENSOR : NLFA_PATH_SIMT;
+  return -NLFA_ERR_UNSUPPORTED_PATH;
+}
+
+int nlfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T,
+             int H, int Hkv, int D, float scale, int window, int sinks, int dtype, int path,
+             void* stream) {
+  Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype};
+  int st = check_problem(p);
+  if (st != NLFA_OK) return st;
+  const int resolved = nlfa_resolve_path(dtype, D, path);
+  if (resolved < 0) return -resolved;
+  if (B == 0 || T == 0 || H == 0) return NLFA_OK;
+  if (!q || !k || !v || !o || !lse) return NLFA_ERR_NULL_POINTER;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return NLFA_ERR_MISALIGNED;
+  if (p.window > 0 && p.window - p.sinks >= p.T) {
+    p.window = 0;            // the window never cuts anything: plain causal
+    p.sinks = 0;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (resolved == NLFA_PATH_SIMT) return launch_fwd_simt(p, q, k, v, o, lse, s);
+  if (!nlfa_device_supported()) return NLFA_ERR_NOT_SM100;
+  unsigned* status = status_word();
+  if (!status) return NLFA_ERR_CUDA;
+  return launch_fwd_tc(p, q, k, v, o, lse, status, s);
+}
+
+size_t nlfa_bwd_scratch_bytes(int B, int T, int H) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  return static_cast<size_t>(B) * H * T * sizeof(float);
+}
+
+int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
+             const float* lse, void* dq, void* dk, void* dv, void* scratch, size_t scratch_bytes,
+             int B, int T, int H, int Hkv, int D, float scale, int window, int sinks, int dtype,
+             int path, void* stream) {
+  Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype};
+  int st = check_problem(p);
+  if (st != NLFA_OK) return st;
+  const int resolved = nlfa_resolve_path(dtype, D, path);
+  if (resolved < 0) return -resolved;
+  if (B == 0 || T == 0 || H == 0) return NLFA_OK;
+  if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv || !scratch)
+    return NLFA_ERR_NULL_POINTER;
+  if (!aligned16(dout) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) ||
+      !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+    return NLFA_ERR_MISALIGNED;
+  if (scratch_bytes < nlfa_bwd_scratch_bytes(B, T, H)) return NLFA_ERR_SCRATCH_TOO_SMALL;
+  if (p.window > 0 && p.window - p.sinks >= p.T) {
+    p.window = 0;
+    p.sinks = 0;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* delta = static_cast<float*>(scratch);
+  if (resolved == NLFA_PATH_SIMT)
+    return launch_bwd_simt(p, dout, q, k, v, o, lse, dq, dk, dv, delta, s);
+  if (!nlfa_device_supported()) return NLFA_ERR_NOT_SM100;
+  unsigned* status = status_word();
+  if (!status) return NLFA_ERR_CUDA;
+  return launch_bwd_tc(p, dout, q, k, v, o, lse, dq, dk, dv, delta, status, s);
+}
+
+int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,
+                        float* s_out, float* o_out, void* stream) {
+  if (!q || !k || !v || !s_out || !o_out) return NLFA_ERR_NULL_POINTER;
+  if (!nlfa_device_supported()) return NLFA_ERR_NOT_SM100;
+  unsigned* status = status_word();
+  if (!status) return NLFA_ERR_CUDA;
+  return launch_selftest_tiles(dtype, head_dim, q, k, v, s_out, o_out, status,
+                               static_cast<cudaStream_t>(stream));
+}
+
+size_t nlfa_selftest_workspace_bytes(void) {
+  // q, k, v tiles (16-bit, D <= 128) then S [128,128] and O [128,128] float32
+  return 3 * 128 * 128 * 2 + 2 * 128 * 128 * 4;
+}
+
+int nlfa_selftest(int dtype, int head_dim, void* workspace, size_t workspace_bytes,
+                  float* max_abs_err, void* stream) {
+  if (!workspace || !max_abs_err) return NLFA_ERR_NULL_POINTER;
+  if (workspace_bytes < nlfa_selftest_workspace_bytes()) return NLFA_ERR_SCRATCH_TOO_SMALL;
+  if (dtype != NLFA_DTYPE_F16 && dtype != NLFA_DTYPE_BF16) return NLFA_ERR_UNSUPPORTED_PATH;
+  if (head_dim != 64 && head_dim != 128) return NLFA_ERR_UNSUPPORTED_PATH;
+  const int D = head_dim;
+  const size_t n = static_cast<size_t>(128) * D;
+  std::vector<uint16_t> hq(n), hk(n), hv(n);
+  std::vector<float> fq(n), fk(n), fv(n);
+  uint32_t rng = 0x1234567u;
+  auto next = [&rng]() {                       // small LCG; values in [-1, 1)
+    rng = rng * 1664525u + 1013904223u;
+    return static_cast<float>(static_cast<int32_t>(rng >> 8) & 0xffff) / 32768.f - 1.f;
+  };
+  for (size_t i = 0; i < n; ++i) {
+    hq[i] = float_to_bits(next(), dtype); fq[i] = bits_to_float(hq[i], dtype);
+    hk[i] = float_to_bits(next(), dtype); fk[i] = bits_to_float(hk[i], dtype);
+    hv[i] = float_to_bits(next(), dtype); fv[i] = bits_to_float(hv[i], dtype);
+  }
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* dq = ws;
+  void* dk = ws + 128 * 128 * 2;
+  void* dv = ws + 2 * 128 * 128 * 2;
+  float* ds = reinterpret_cast<float*>(ws + 3 * 128 * 128 * 2);
+  float* dob = ds + 128 * 128;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(dq, hq.data(), n * 2, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+      cudaMemcpyAsync(dk, hk.data(), n * 2, cudaMemcpyHostToDevice, s) != cudaSuccess ||
+      cudaMemcpyAsync(dv, hv.data(), n * 2, cudaMemcpyHostToDevice, s) != cudaSuccess)
+    return NLFA_ERR_CUDA;
+  int st = nlfa_selftest_tiles(dtype, D, dq, dk, dv, ds, dob, stream);
+  if (st != NLFA_OK) return st;
+  std::vector<float> S(128 * 128), O(n);
+  if (cudaMemcpyAsync(S.data(), ds, S.size() * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaMemcpyAsync(O.data(), dob, n * 4, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess)
+    return NLFA_ERR_CUDA;
+  st = nlfa_device_status(nullptr);
+  if (st != NLFA_OK) return st;
+  double err_s = 0, mag_s = 1e-30, err_o = 0, mag_o = 1e-30;
+  std::vector<float> P(128 * 128);
+  for (int r = 0; r < 128; ++r)
+    for (int c = 0; c < 128; ++c) {
+      double acc = 0;
+      for (int d = 0; d < D; ++d) acc += static_cast<double>(fq[r * D + d]) * fk[c * D + d];
+      err_s = std::fmax(err_s, std::fabs(acc - S[r * 128 + c]));
+      mag_s = std::fmax(mag_s, std::fabs(acc));
+      P[r * 128 + c] = bits_to_float(float_to_bits(S[r * 128 + c], dtype), dtype);
+    }
+  for (int r = 0; r < 128; ++r)
+    for (int d = 0; d < D; ++d) {
+      double acc = 0;
+      for (int c = 0; c < 128; ++c) acc += static_cast<double>(P[r * 128 + c]) * fv[c * D + d];
+      err_o = std::fmax(err_o, std::fabs(acc - O[r * D + d]));
+      mag_o = std::fmax(mag_o, std::fabs(acc));
+    }
+  max_abs_err[0] = static_cast<float>(err_s / mag_s);
+  max_abs_err[1] = static_cast<float>(err_o / mag_o);
+  if (!(max_abs_err[0] < 1e-2f) || !(max_abs_err[1] < 1e-2f)) return NLFA_ERR_SELFTEST_MISMATCH;
+  return NLFA_OK;
+}
+
+int nlfa_device_status(unsigned* raw) {
+  unsigned* ptr = status_word();
+  if (!ptr) return NLFA_ERR_CUDA;
+  unsigned word = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return NLFA_ERR_CUDA;
+  if (cudaMemcpy(&word, ptr, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return NLFA_ERR_CUDA;
+  if (word != 0) {
+    const unsigned zero = 0;
+    cudaMemcpy(ptr, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+  }
+  if (raw) *raw = word;
+  return word == 0 ? NLFA_OK : NLFA_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,90 @@
+// Shared host/device definitions for the attention library.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/nlfa.h"
+
+namespace nlfa {
+
+constexpr int kTile = 128;          // query rows per tile and keys per block
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// One attention problem.  Layouts follow the reference kernel's contract
+// (nanolab/csrc/flash_attn_cuda.cu:1628-1650): q, o, dout, dq are contiguous
+// [B,T,H,D]; k, v, dk, dv are contiguous [B,T,Hkv,D]; lse and delta are fp32
+// [B,H,T]; lse is a natural-log logsumexp.
+struct Problem {
+  int B, T, H, Hkv, D;
+  int window, sinks;     // window == 0: plain causal
+  float scale;
+  int dtype;             // NLFA_DTYPE_*
+};
+
+// Which key blocks a 128-row query tile must visit.  Block j covers keys
+// [128 j, 128 j + 127].  The mask is the reference's sliding_window_mask
+// (nanolab/mixers.py:125-132): keep k <= q and (k > q - (window - sinks) or
+// k < sinks).
+struct TileRange {
+  int lo, hi;            // contiguous range of recent blocks, inclusive
+  int sink_blocks;       // blocks [0, sink_blocks) hold sink keys
+};
+
+__host__ __device__ inline TileRange tile_range(int tile, int window, int sinks) {
+  TileRange r;
+  r.hi = tile;
+  r.lo = 0;
+  r.sink_blocks = 0;
+  if (window > 0) {
+    const int span = window - sinks;
+    const int first_key = tile * kTile - span + 1;     // lowest recent key of the tile's first row
+    r.lo = first_key > 0 ? first_key / kTile : 0;
+    r.sink_blocks = (sinks + kTile - 1) / kTile;
+  }
+  return r;
+}
+
+// True when every (row, key) of query tile `tile` x key block `j` survives the
+// mask, so the element-wise predicate can be skipped.
+__host__ __device__ inline bool block_fully_visible(int tile, int j, int window, int sinks) {
+  if (j >= tile) return false;                                   // diagonal block
+  if (window > 0) {
+    const int span = window - sinks;
+    const int last_row = tile * kTile + kTile - 1;
+    if (j * kTile <= last_row - span) return false;              // lower window edge cuts in
+  }
+  return true;
+}
+
+__host__ __device__ inline bool key_visible(int q, int k, int window, int sinks) {
+  if (k > q) return false;
+  if (window == 0) return true;
+  return (k > q - (window - sinks)) || (k < sinks);
+}
+
+// Host-side launchers (one per translation unit); all return an NLFA_* status.
+int launch_fwd_simt(const Problem& p, const void* q, const void* k, const void* v, void* o,
+                    float* lse, cudaStream_t stream);
+int launch_bwd_simt(const Problem& p, const void* dout, const void* q, const void* k,
+                    const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
+                    float* delta, cudaStream_t stream);
+int launch_delta(const Problem& p, const void* dout, const void* o, float* delta,
+                 cudaStream_t stream);
+int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v, void* o,
+                  float* lse, unsigned* status, cudaStream_t stream);
+int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
+                  const void* o, const float* lse, void* dq, void* dk, void* dv, float* delta,
+                  unsigned* status, cudaStream_t stream);
+int launch_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,
+                          float* s_out, float* o_out, unsigned* status, cudaStream_t stream);
+
+// Encodes a 4-D tensor map over a contiguous [B,T,heads,D] 16-bit tensor with a
+// box of 64 elements x 1 head x `rows` rows x 1 batch and 128-byte swizzle.
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, int heads, int D,
+                  int rows);
+
+}  // namespace nlfa

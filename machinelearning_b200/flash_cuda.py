@@ -1,0 +1,373 @@
+"""B200 flash attention behind nanolab's ``flash_cuda`` module interface.
+
+Drop-in for ``nanolab/flash_cuda.py``: same public names, same call signatures,
+same exceptions.  What is different underneath:
+
+* the native side is a C-ABI shared library (``libnlfa.so``, ``include/nlfa.h``)
+  called through ctypes, not a pybind11 module built by ninja;
+* Python owns every buffer (outputs, the logsumexp tape, the backward's Delta
+  scratch) so torch's caching allocator and stream semantics apply;
+* ``use_mma`` still picks the kernel family (reference: ``flash_cuda.py:233-279``):
+  ``False`` is the fp32 SIMT kernels, ``True`` demands the tensor-core kernels
+  (TMA + tcgen05 + TMEM, sm_100a), ``None`` takes them whenever dtype and head dim
+  allow and the load-time self-test passed;
+* ``flash_attn`` also takes keyword-only ``window`` / ``sinks`` -- the mixer's
+  sliding-window mask (``nanolab/mixers.py:96-135``) runs inside the kernel with
+  masked key blocks skipped, instead of declining to SDPA (``mixers.py:357``).
+
+There is no CPU path here: when the library or a CUDA device is missing,
+``is_available()`` is False with a reason and ``flash_attn`` raises.
+
+    python -m machinelearning_b200.flash_cuda        # self-check, then timings
+"""
+from __future__ import annotations
+
+import logging
+import math
+import os
+
+import torch
+
+from . import _lib
+
+log = logging.getLogger("machinelearning_b200.flash_cuda")
+
+SUPPORTED_HEAD_DIMS = (32, 64, 128)
+SUPPORTED_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
+MMA_DTYPES = (torch.float16, torch.bfloat16)      # tcgen05 kind::f16 operands
+# Head dims with a tensor-core kernel, forward and backward alike.  The
+# reference stops its tensor-core backward at 64 (flash_cuda.py:48-51).
+MMA_HEAD_DIMS = (64, 128)
+MMA_BWD_HEAD_DIMS = (64, 128)
+
+_DTYPE_CODE = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16,
+               torch.bfloat16: _lib.DTYPE_BF16}
+
+_ext = None
+_load_error: str | None = None
+_load_attempted = False
+_mma_ok = False
+_mma_error: str | None = None
+
+
+def _probe_mma(lib) -> tuple[bool, str]:
+    """Run the tensor-core self-test on the device (reference: ``_probe_mma``,
+    ``flash_cuda.py:59-88``).  Fails closed: the tensor-core path stays off."""
+    try:
+        if not lib.nlfa_device_supported():
+            major, minor = torch.cuda.get_device_capability()
+            return False, f"tcgen05 needs sm_100, this device is sm_{major}{minor}"
+        import ctypes
+        ws = torch.empty(lib.nlfa_selftest_workspace_bytes(), dtype=torch.uint8, device="cuda")
+        errs = (ctypes.c_float * 2)()
+        stream = torch.cuda.current_stream().cuda_stream
+        for code, name in ((_lib.DTYPE_BF16, "bf16"), (_lib.DTYPE_F16, "f16")):
+            for d in MMA_HEAD_DIMS:
+                st = lib.nlfa_selftest(code, d, ws.data_ptr(), ws.numel(), errs, stream)
+                if st != _lib.OK:
+                    return False, (f"self-test failed for {name} D={d}: {_lib.strerror(st)} "
+                                   f"(S err {errs[0]:.3e}, O err {errs[1]:.3e})")
+        return True, ""
+    except Exception as e:                                    # noqa: BLE001
+        return False, f"{type(e).__name__}: {e}"
+
+
+def _load():
+    """Load the library once.  Never raises (reference: ``flash_cuda.py:91-135``);
+    callers gate on ``is_available()``."""
+    global _ext, _load_error, _load_attempted, _mma_ok, _mma_error
+    if _load_attempted:
+        return _ext
+    _load_attempted = True
+    if os.environ.get("NANOLAB_FLASH_CUDA", "1") == "0":
+        _load_error = "disabled by NANOLAB_FLASH_CUDA=0"
+        return None
+    if not torch.cuda.is_available():
+        _load_error = "no CUDA device"
+        return None
+    try:
+        _ext = _lib.load()
+    except Exception as e:                                    # noqa: BLE001
+        _ext = None
+        _load_error = f"{type(e).__name__}: {e}"
+        log.warning("libnlfa did not load (%s)", _load_error)
+        return None
+    _mma_ok, _mma_error = _probe_mma(_ext)
+    if not _mma_ok:
+        log.warning("tensor-core path off (%s); using the SIMT kernels", _mma_error)
+    return _ext
+
+
+def is_available() -> bool:
+    """True once the library is loaded on a machine with a CUDA device."""
+    return _load() is not None
+
+
+def unavailable_reason() -> str:
+    _load()
+    return "" if _ext is not None else (_load_error or "unknown")
+
+
+def mma_available() -> bool:
+    """True when the tensor-core kernels are usable: library loaded and the
+    on-device self-test passed."""
+    return _load() is not None and _mma_ok
+
+
+def mma_unavailable_reason() -> str:
+    if _load() is None:
+        return unavailable_reason()
+    return "" if _mma_ok else (_mma_error or "unknown")
+
+
+def effective_dtype(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.dtype | None:
+    """The dtype the kernel would run at (reference: ``flash_cuda.py:161-177``):
+    the autocast dtype under an enabled CUDA autocast, else the common dtype."""
+    if q.is_cuda and torch.is_autocast_enabled("cuda"):
+        return torch.get_autocast_dtype("cuda")
+    if q.dtype == k.dtype == v.dtype:
+        return q.dtype
+    return None
+
+
+def supports(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """Shape / dtype / device gate (reference: ``flash_cuda.py:180-202``).  Does
+    not load the library."""
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        return False
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        return False
+    if effective_dtype(q, k, v) not in SUPPORTED_DTYPES:
+        return False
+    if q.shape[-1] not in SUPPORTED_HEAD_DIMS:
+        return False
+    if k.shape[:2] != q.shape[:2] or v.shape[:2] != q.shape[:2]:
+        return False
+    if k.shape[2] != v.shape[2] or k.shape[3] != q.shape[3] or v.shape[3] != q.shape[3]:
+        return False
+    if k.shape[2] == 0 or q.shape[2] % k.shape[2] != 0:
+        return False
+    return True
+
+
+def check_window(window: int, sinks: int) -> None:
+    """Same refusals as ``sliding_window_mask`` (``nanolab/mixers.py:119-123``)."""
+    if window == 0:
+        if sinks:
+            raise ValueError("swa sinks set without a window")
+        return
+    if window < 1:
+        raise ValueError(f"swa window must be >=1, got {window}")
+    if not 0 <= sinks < window:
+        raise ValueError(f"swa sinks must satisfy 0 <= sinks < window, "
+                         f"got sinks={sinks} window={window}")
+
+
+def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0):
+    """(O, LSE) through the C ABI.  Contiguous same-dtype CUDA tensors only
+    (reference native entry: ``flash_attn_cuda.cu:1655-1704``)."""
+    lib = _load()
+    if lib is None:
+        raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
+    B, T, H, D = q.shape
+    Hkv = k.shape[2]
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
+    with torch.cuda.device(q.device):
+        st = lib.nlfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                          B, T, H, Hkv, D, float(scale), int(window), int(sinks),
+                          _DTYPE_CODE[q.dtype],
+                          _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
+                          torch.cuda.current_stream().cuda_stream)
+    _lib.check("nlfa_fwd", st)
+    return o, lse
+
+
+def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sinks: int = 0):
+    """(dQ, dK, dV) through the C ABI (reference: ``flash_attn_cuda.cu:1744-1813``)."""
+    lib = _load()
+    if lib is None:
+        raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
+    B, T, H, D = q.shape
+    Hkv = k.shape[2]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    nbytes = lib.nlfa_bwd_scratch_bytes(B, T, H)
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        st = lib.nlfa_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                          lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                          scratch.data_ptr(), scratch.numel(), B, T, H, Hkv, D, float(scale),
+                          int(window), int(sinks), _DTYPE_CODE[q.dtype],
+                          _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
+                          torch.cuda.current_stream().cuda_stream)
+    _lib.check("nlfa_bwd", st)
+    return dq, dk, dv
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    """Causal / windowed GQA attention on [B,T,H,D] with the taped LSE carried to
+    backward (reference: ``flash_cuda.py:205-230``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, use_mma, window, sinks):
+        o, lse = fwd(q, k, v, scale, use_mma, window, sinks)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale = float(scale)
+        ctx.use_mma = bool(use_mma)
+        ctx.window, ctx.sinks = int(window), int(sinks)
+        return o
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dout):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = bwd(dout.contiguous(), q, k, v, o, lse, ctx.scale, ctx.use_mma,
+                         ctx.window, ctx.sinks)
+        return dq, dk, dv, None, None, None, None
+
+
+def _tensor_path_fits(dtype, head_dim) -> bool:
+    return dtype in MMA_DTYPES and head_dim in MMA_HEAD_DIMS
+
+
+def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+               scale: float | None = None, use_mma: bool | None = None, *,
+               window: int = 0, sinks: int = 0) -> torch.Tensor:
+    """Causal GQA flash attention. q [B,T,H,D], k/v [B,T,Hkv,D] -> [B,T,H,D].
+
+    Same contract as the reference (``flash_cuda.py:233-279``): raises
+    ``ValueError`` for unsupported inputs instead of falling back; casts q/k/v to
+    the effective dtype and makes them contiguous as autograd ops.  ``window`` /
+    ``sinks`` select the sliding-window mask; ``window=0`` is plain causal.
+    """
+    if not supports(q, k, v):
+        raise ValueError(
+            "flash_cuda.flash_attn: unsupported inputs "
+            f"(q={tuple(q.shape)}/{q.dtype}, k={tuple(k.shape)}/{k.dtype}, "
+            f"v={tuple(v.shape)}/{v.dtype}); head_dim must be one of "
+            f"{SUPPORTED_HEAD_DIMS} and the effective dtype one of "
+            f"{SUPPORTED_DTYPES}")
+    check_window(window, sinks)
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    dtype = effective_dtype(q, k, v)
+    q = q.to(dtype).contiguous()
+    k = k.to(dtype).contiguous()
+    v = v.to(dtype).contiguous()
+
+    fits = _tensor_path_fits(dtype, q.shape[-1])
+    if use_mma is None:
+        use_mma = fits and mma_available()
+    elif use_mma:
+        if dtype not in MMA_DTYPES:
+            raise ValueError(
+                f"flash_cuda: use_mma=True but the effective dtype is {dtype}; "
+                f"the tensor-core kernels exist only for {MMA_DTYPES}")
+        if q.shape[-1] not in MMA_HEAD_DIMS:
+            raise ValueError(
+                f"flash_cuda: use_mma=True but head_dim is {q.shape[-1]}; "
+                f"the tensor-core kernels exist only for {MMA_HEAD_DIMS}")
+        if not mma_available():
+            raise RuntimeError(
+                f"flash_cuda: use_mma=True but the tensor-core path is "
+                f"unavailable ({mma_unavailable_reason()})")
+    return _FlashAttnFn.apply(q, k, v, scale, use_mma, window, sinks)
+
+
+def sdpa_reference(q, k, v, scale):
+    """What nanolab does without the kernel (reference: ``flash_cuda.py:282-294``):
+    widen KV heads, transpose, call torch SDPA.  A comparison arm for the
+    self-check below, on the same device as its inputs; not used by ``flash_attn``."""
+    import torch.nn.functional as F
+    group = q.shape[2] // k.shape[2]
+    qs = q.transpose(1, 2)
+    ks = k.repeat_interleave(group, dim=2).transpose(1, 2)
+    vs = v.repeat_interleave(group, dim=2).transpose(1, 2)
+    y = F.scaled_dot_product_attention(qs, ks, vs, is_causal=True, scale=scale)
+    return y.transpose(1, 2).contiguous()
+
+
+def _bench_once(fn, iters: int, warmup: int = 5) -> float:
+    """Median milliseconds per call, GPU-synchronised (reference: ``:297-312``)."""
+    import statistics
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+    return statistics.median(times)
+
+
+def main() -> int:
+    """Correctness against SDPA, then a speed comparison (reference: ``:315-379``)."""
+    import argparse
+
+    p = argparse.ArgumentParser(description=__doc__)
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--seq", type=int, default=1024)
+    p.add_argument("--heads", type=int, default=12)
+    p.add_argument("--kv_heads", type=int, default=4)
+    p.add_argument("--head_dim", type=int, default=64)
+    p.add_argument("--dtype", default="bf16", choices=("fp32", "fp16", "bf16"))
+    p.add_argument("--iters", type=int, default=20)
+    args = p.parse_args()
+
+    if not torch.cuda.is_available():
+        print("no CUDA device -- nothing to run")
+        return 1
+    if not is_available():
+        print(f"library unavailable: {unavailable_reason()}")
+        return 1
+
+    dtype = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[args.dtype]
+    B, T, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
+    torch.manual_seed(0)
+    q = torch.randn(B, T, H, D, device="cuda", dtype=dtype, requires_grad=True)
+    k = torch.randn(B, T, Hkv, D, device="cuda", dtype=dtype, requires_grad=True)
+    v = torch.randn(B, T, Hkv, D, device="cuda", dtype=dtype, requires_grad=True)
+    scale = 1.0 / math.sqrt(D)
+
+    print(f"shape B{B} T{T} H{H}/{Hkv} D{D} {args.dtype}")
+    if mma_available():
+        print("  tensor-core path: on (self-test passed)")
+    else:
+        print(f"  tensor-core path: OFF -- {mma_unavailable_reason()}")
+
+    mma_usable = mma_available() and _tensor_path_fits(dtype, D)
+    arms = [("SDPA", lambda: sdpa_reference(q, k, v, scale)),
+            ("simt", lambda: flash_attn(q, k, v, scale, use_mma=False))]
+    if mma_usable:
+        arms.append(("tc", lambda: flash_attn(q, k, v, scale, use_mma=True)))
+
+    y_ref = sdpa_reference(q, k, v, scale)
+    do = torch.randn_like(y_ref)
+    gr = torch.autograd.grad(y_ref, (q, k, v), do, retain_graph=False)
+    for name, fn in arms[1:]:
+        y = fn()
+        g = torch.autograd.grad(y, (q, k, v), do, retain_graph=False)
+        fe = (y.float() - y_ref.float()).abs().max().item()
+        be = max((a.float() - b.float()).abs().max().item() for a, b in zip(g, gr))
+        print(f"  {name:4s} vs SDPA:  max |dO| {fe:.3e}   max |dgrad| {be:.3e}")
+
+    def _fwd_bwd(fn):
+        torch.autograd.grad(fn(), (q, k, v), do, retain_graph=False)
+
+    print(f"  {'arm':4s} {'fwd ms':>10s} {'fwd+bwd ms':>12s} {'vs SDPA fwd':>13s}")
+    base = None
+    for name, fn in arms:
+        t_f = _bench_once(fn, args.iters)
+        t_fb = _bench_once(lambda fn=fn: _fwd_bwd(fn), args.iters)
+        base = base if base is not None else t_f
+        print(f"  {name:4s} {t_f:10.3f} {t_fb:12.3f} {base / t_f:12.2f}x")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
