@@ -1,0 +1,451 @@
+"""Attention forward+backward throughput on B200, one process per GPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one forward plus one backward of the causal bf16 attention path over
+one batch of synthetic input (B=32, H=12, T=1024, D=64, scale 1/8: the nanolab
+124M-model shape).  Each rank owns its own batch (weak scaling: the path shards
+by batch x head with no exchange step), so N ranks process N batches per step.
+
+Prints one JSON line:
+  value      whole-job TFLOP/s, algorithmic FLOPs (2 forward + 5 backward GEMMs
+             over the unmasked pairs), inputs resident in HBM, CUDA-event time,
+             slowest rank
+  e2e        the same metric through ``flash_cuda.flash_attn`` + autograd with
+             pinned host buffers: host->device copies of q, k, v, dO and
+             device->host copies of O, dQ, dK, dV inside the timed region
+  roofline   the dominant kernel timed alone against the measured dense bf16 peak
+  cpu_baseline  the reference's CPU attention (torch SDPA + autograd, restated in
+             oracle/sdpa_port.py) on this box's host cores, bounded sample
+
+``--impl reference`` times only that CPU path, on the same config and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (B, T, H, Hkv, D, window, sinks)
+    "c2": (32, 1024, 12, 12, 64, 0, 0),
+    "c3": (16, 4096, 16, 16, 64, 256, 0),
+    "c5": (1, 16384, 16, 16, 128, 0, 0),      # one batch element of B=8 per GPU
+}
+WORKLOAD_TEXT = {
+    "c2": "causal bf16 attention fwd+bwd, B=32 H=12 T=1024 D=64, scale 1/8 (per GPU)",
+    "c3": "sliding-window bf16 attention fwd+bwd, B=16 H=16 T=4096 D=64 window=256 (per GPU)",
+    "c5": "long-context causal bf16 attention fwd+bwd, B=1 of 8, H=16 T=16384 D=128 (per GPU)",
+}
+METRIC = "attention fwd+bwd TFLOP/s (bf16 causal)"
+FALLBACK_PEAK_TFLOPS = 1590.0
+
+
+def pairs(T, window, sinks):
+    if window == 0:
+        return T * (T + 1) // 2
+    span = window - sinks
+    total = 0
+    for q in range(T):
+        lo = max(0, q - span + 1)
+        total += (q - lo + 1) + min(sinks, lo)
+    return total
+
+
+def flops(B, T, H, D, window, sinks):
+    """(forward, backward) algorithmic FLOPs: 2 and 5 GEMMs over the unmasked pairs."""
+    n = pairs(T, window, sinks)
+    return 4.0 * D * n * B * H, 10.0 * D * n * B * H
+
+
+def measured_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            d = json.loads(path.read_text())
+            return float(d["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+        except Exception:                                         # noqa: BLE001
+            pass
+    return FALLBACK_PEAK_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, s[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(shape, seed, device, pin=False):
+    """q, k, v, dO ~ N(0,1) generated in fp32 from a seed, then cast to bf16."""
+    B, T, H, Hkv, D, _, _ = shape
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    out = []
+    for heads in (H, Hkv, Hkv, H):
+        t = torch.randn(B, T, heads, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        if pin:
+            out.append(t.pin_memory())          # stays on the host, page-locked
+        else:
+            out.append(t if device == "cpu" else t.to(device))
+    return out
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the reference's own attention path on host cores
+# ----------------------------------------------------------------------------
+
+def cpu_fwd_bwd_tflops(shape, sample_batch, reps, warmup=1):
+    from oracle import sdpa_port            # test infrastructure: only timed here, never shipped
+    B, T, H, Hkv, D, window, sinks = shape
+    sb = min(sample_batch, B)
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v, do = make_inputs((sb, T, H, Hkv, D, window, sinks), 1234, "cpu")
+    scale = 1.0 / math.sqrt(D)
+    times = []
+    for i in range(warmup + reps):
+        t0 = time.perf_counter()
+        sdpa_port.cpu_fwd_bwd(q, k, v, do, scale, window, sinks)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    ff, fb = flops(sb, T, H, D, window, sinks)
+    sec = statistics.median(times)
+    return (ff + fb) / sec / 1e12, sec, sb
+
+
+def run_reference_arm(args, shape, rank, world):
+    if rank != 0:
+        return
+    B, T, H, Hkv, D, window, sinks = shape
+    sample_b = max(1, B // 4)
+    times = []
+    tf = None
+    for i in range(args.warmup + args.steps):
+        tf_i, sec, sb = cpu_fwd_bwd_tflops(shape, sample_b, reps=1, warmup=0)
+        if i >= args.warmup:
+            times.append(sec)
+            tf = tf_i
+    sec = statistics.median(times)
+    ff, fb = flops(sb, T, H, D, window, sinks)
+    value = (ff + fb) / sec / 1e12
+    cores = torch.get_num_threads()
+    sample = (f"{sb} of {B} batch elements per step, torch CPU SDPA + autograd in bf16 "
+              f"(oracle/sdpa_port.py), {args.steps} timed steps, median")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3 * B / sb, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD_TEXT[args.workload], "cpu_sample": sample,
+                   "ms_per_step": "sample time scaled by B / sample size"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+
+class Step:
+    """Pre-allocated buffers and direct C-ABI calls for one forward+backward."""
+
+    def __init__(self, shape, q, k, v, do):
+        from machinelearning_b200 import _lib, flash_cuda
+        if not flash_cuda.is_available():
+            raise RuntimeError(f"libnlfa unavailable: {flash_cuda.unavailable_reason()}")
+        if not flash_cuda.mma_available():
+            raise RuntimeError(f"tensor-core path unavailable: {flash_cuda.mma_unavailable_reason()}")
+        self.L, self.lib = _lib, _lib.load()
+        self.B, self.T, self.H, self.Hkv, self.D, self.window, self.sinks = shape
+        self.scale = 1.0 / math.sqrt(self.D)
+        self.q, self.k, self.v, self.do = q, k, v, do
+        self.o = torch.empty_like(q)
+        self.lse = torch.empty(self.B, self.H, self.T, dtype=torch.float32, device=q.device)
+        self.dq, self.dk, self.dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        self.scratch = torch.empty(self.lib.nlfa_bwd_scratch_bytes(self.B, self.T, self.H),
+                                   dtype=torch.uint8, device=q.device)
+
+    def _dims(self):
+        return (self.B, self.T, self.H, self.Hkv, self.D, self.scale, self.window, self.sinks,
+                self.L.DTYPE_BF16, self.L.PATH_TENSOR)
+
+    def fwd(self):
+        st = self.lib.nlfa_fwd(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(),
+                               self.o.data_ptr(), self.lse.data_ptr(), *self._dims(),
+                               torch.cuda.current_stream().cuda_stream)
+        self.L.check("nlfa_fwd", st)
+
+    def bwd(self, passes=7):
+        st = self.lib.nlfa_bwd_passes(
+            self.do.data_ptr(), self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(),
+            self.o.data_ptr(), self.lse.data_ptr(), self.dq.data_ptr(), self.dk.data_ptr(),
+            self.dv.data_ptr(), self.scratch.data_ptr(), self.scratch.numel(), *self._dims(),
+            passes, torch.cuda.current_stream().cuda_stream)
+        self.L.check("nlfa_bwd_passes", st)
+
+    def step(self):
+        self.fwd()
+        self.bwd()
+
+    launches_per_step = 4          # forward, Delta, dK/dV, dQ
+
+
+def time_region(fn, iters):
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def kernel_times(step: Step, iters=10):
+    """Average device time of each kernel, timed alone with CUDA events on its stream."""
+    L = step.L
+    out = {}
+    for name, fn in (("fwd", step.fwd), ("delta", lambda: step.bwd(L.PASS_DELTA)),
+                     ("dkv", lambda: step.bwd(L.PASS_DKV)), ("dq", lambda: step.bwd(L.PASS_DQ))):
+        for _ in range(3):
+            fn()
+        out[name] = time_region(fn, iters)
+    return out
+
+
+def dram_traffic(kernel, workload):
+    path = ROOT / "profiles" / "dram_traffic.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()).get(f"{kernel}:{workload}")
+        except Exception:                                         # noqa: BLE001
+            return None
+    return None
+
+
+def run_gpu_arm(args, shape, rank, world, local_rank):
+    import torch.distributed as dist
+    from machinelearning_b200 import flash_cuda, sharding
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    B, T, H, Hkv, D, window, sinks = shape
+    q, k, v, do = make_inputs(shape, 1000 + rank, dev)
+    step = Step(shape, q, k, v, do)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernel-only throughput, inputs resident in HBM
+    for _ in range(max(args.warmup, 3)):
+        step.step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.__enter__()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step.step()
+    end.record()
+    barrier()
+    ms_local = start.elapsed_time(end) / args.steps
+    # keep the GPU busy a little longer so the clock sampler sees load even for short runs
+    if sampler:
+        t_end = time.time() + 1.0
+        while time.time() < t_end:
+            step.step()
+        torch.cuda.synchronize()
+        sampler.__exit__(None, None, None)
+    ms = sharding.max_over_ranks(ms_local, dev)
+    ff, fb = flops(B, T, H, D, window, sinks)
+    value = world * (ff + fb) / (ms * 1e-3) / 1e12
+
+    # ---- end to end through the public API, host buffers, copies inside the timed region
+    hq, hk, hv, hdo = make_inputs(shape, 1000 + rank, "cpu", pin=True)        # pinned host
+    host_out = [torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)]
+    scale = 1.0 / math.sqrt(D)
+
+    def e2e_step():
+        dq_, dk_, dv_, ddo = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
+        dq_.requires_grad_(), dk_.requires_grad_(), dv_.requires_grad_()
+        y = flash_cuda.flash_attn(dq_, dk_, dv_, scale, use_mma=True, window=window, sinks=sinks)
+        grads = torch.autograd.grad(y, (dq_, dk_, dv_), ddo)
+        for dst, src in zip(host_out, (y.detach(), *grads)):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_iters = max(3, min(args.steps, 10))
+    e2e_ms = sharding.max_over_ranks(time_region(e2e_step, e2e_iters), dev)
+    barrier()
+    e2e_value = world * (ff + fb) / (e2e_ms * 1e-3) / 1e12
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    # ---- verification glue (NCCL only here): every rank's output checksum must be finite
+    checksum = torch.stack([step.o.float().sum(), step.dq.float().sum(),
+                            step.dk.float().sum(), step.dv.float().sum()]).double()
+    if world > 1:
+        gathered = [torch.empty_like(checksum) for _ in range(world)]
+        dist.all_gather(gathered, checksum)
+        checksum = torch.stack(gathered)
+    finite = bool(torch.isfinite(checksum).all().item())
+
+    if rank != 0:
+        return
+    # ---- per-kernel times and the roofline of the dominant one (rank 0, kernels timed alone)
+    kt = kernel_times(step)
+    # FLOPs per launch.  Algorithmic: the backward's 5 GEMMs are S, dP, dV, dK (dK/dV kernel) and
+    # dQ (dQ kernel); the dQ kernel's own S and dP are recomputation and are not counted.
+    # Executed counts them (what the tensor pipe actually ran).
+    gemm = 2.0 * D * pairs(T, window, sinks) * B * H
+    kflops = {"fwd": 2 * gemm, "dkv": 4 * gemm, "dq": 1 * gemm}
+    kexec = {"fwd": 2 * gemm, "dkv": 4 * gemm, "dq": 3 * gemm}
+    dominant = max(("fwd", "dkv", "dq"), key=lambda n: kt[n])
+    peak, peak_src = measured_peak()
+    achieved = kflops[dominant] / (kt[dominant] * 1e-3) / 1e12
+    clocks = sampler.summary() if sampler else None
+
+    cpu_tf, cpu_sec, cpu_b = (None, None, None)
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_tf, cpu_sec, cpu_b = cpu_fwd_bwd_tflops(shape, max(1, B // 4), reps=3)
+        cpu = {"value": cpu_tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+               "kind": "port",
+               "sample": f"{cpu_b} of {B} batch elements, 1 warm-up + 3 timed fwd+bwd, median "
+                         f"{cpu_sec:.3f} s, torch CPU SDPA + autograd in bf16 (oracle/sdpa_port.py)"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD_TEXT[args.workload], "global_batch": B * world,
+                   "parallelism": f"batch-sharded x{world}, no collective in the path",
+                   "l2": "working set (q,k,v,o,dO,dq,dk,dv) larger than the 126 MB L2"
+                         if 8 * q.numel() * 2 > 126e6 else "working set smaller than L2",
+                   "flops_per_step_per_gpu": ff + fb},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": Step.launches_per_step * args.steps,
+        "kernel_ms": kt,
+        "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
+                     "flops_per_launch": kflops[dominant],
+                     "executed_tflops": kexec[dominant] / (kt[dominant] * 1e-3) / 1e12,
+                     "traffic": dram_traffic(dominant, args.workload)},
+        "frac_of_peak_fwd_bwd": value / world / peak,
+        "clocks": clocks,
+        "outputs_finite": finite,
+    }
+    if cpu:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    shape = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference_arm(args, shape, rank, world)
+        return 0
+
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_gpu_arm(args, shape, rank, world, local_rank)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

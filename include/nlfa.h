@@ -95,6 +95,21 @@ int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, cons
              int B, int T, int H, int Hkv, int D, float scale, int window, int sinks, int dtype,
              int path, void* stream);
 
+/* The backward's three passes, individually selectable so that each kernel can be
+ * timed or profiled on its own: `passes` is a bit mask of NLFA_PASS_*.  The dQ
+ * and dK/dV passes read the Delta tape in `scratch`, which the Delta pass (or an
+ * earlier call) must have written.  nlfa_bwd is this with every pass selected.
+ * The three kernels are the reference's `flash_delta_kernel`, dQ and dK/dV
+ * kernels (flash_attn_cuda.cu:1234-1262, :806-971, :983-1191). */
+#define NLFA_PASS_DELTA 1
+#define NLFA_PASS_DKV 2
+#define NLFA_PASS_DQ 4
+#define NLFA_PASS_ALL 7
+int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                    const float* lse, void* dq, void* dk, void* dv, void* scratch,
+                    size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
+                    int window, int sinks, int dtype, int path, int passes, void* stream);
+
 /* Bytes of device workspace `nlfa_selftest` needs. */
 size_t nlfa_selftest_workspace_bytes(void);
 

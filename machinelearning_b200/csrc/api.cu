@@ -188,6 +188,15 @@ int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, cons
              const float* lse, void* dq, void* dk, void* dv, void* scratch, size_t scratch_bytes,
              int B, int T, int H, int Hkv, int D, float scale, int window, int sinks, int dtype,
              int path, void* stream) {
+  return nlfa_bwd_passes(dout, q, k, v, o, lse, dq, dk, dv, scratch, scratch_bytes, B, T, H, Hkv,
+                         D, scale, window, sinks, dtype, path, NLFA_PASS_ALL, stream);
+}
+
+int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                    const float* lse, void* dq, void* dk, void* dv, void* scratch,
+                    size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
+                    int window, int sinks, int dtype, int path, int passes, void* stream) {
+  if (passes <= 0 || passes > NLFA_PASS_ALL) return NLFA_ERR_UNSUPPORTED_PATH;
   Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype};
   int st = check_problem(p);
   if (st != NLFA_OK) return st;
@@ -207,11 +216,11 @@ int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, cons
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* delta = static_cast<float*>(scratch);
   if (resolved == NLFA_PATH_SIMT)
-    return launch_bwd_simt(p, dout, q, k, v, o, lse, dq, dk, dv, delta, s);
+    return launch_bwd_simt(p, dout, q, k, v, o, lse, dq, dk, dv, delta, passes, s);
   if (!nlfa_device_supported()) return NLFA_ERR_NOT_SM100;
   unsigned* status = status_word();
   if (!status) return NLFA_ERR_CUDA;
-  return launch_bwd_tc(p, dout, q, k, v, o, lse, dq, dk, dv, delta, status, s);
+  return launch_bwd_tc(p, dout, q, k, v, o, lse, dq, dk, dv, delta, passes, status, s);
 }
 
 int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,

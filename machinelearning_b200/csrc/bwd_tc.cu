@@ -419,21 +419,26 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
 template <typename T, int D, int STAGES>
 int launch_both(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
                 const CUtensorMap& mv, const CUtensorMap& mdo, const float* lse,
-                const float* delta, void* dq, void* dk, void* dv, unsigned* status,
+                const float* delta, void* dq, void* dk, void* dv, int passes, unsigned* status,
                 cudaStream_t stream) {
-  int st = launch_mode<T, D, MODE_DKV, STAGES>(p, mq, mk, mv, mdo, lse, delta, dk, dv, status, stream);
+  int st = NLFA_OK;
+  if (passes & NLFA_PASS_DKV)
+    st = launch_mode<T, D, MODE_DKV, STAGES>(p, mq, mk, mv, mdo, lse, delta, dk, dv, status, stream);
   if (st != NLFA_OK) return st;
-  return launch_mode<T, D, MODE_DQ, STAGES>(p, mq, mk, mv, mdo, lse, delta, dq, nullptr, status, stream);
+  if (passes & NLFA_PASS_DQ)
+    st = launch_mode<T, D, MODE_DQ, STAGES>(p, mq, mk, mv, mdo, lse, delta, dq, nullptr, status, stream);
+  return st;
 }
 
 }  // namespace
 
 int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                   const void* o, const float* lse, void* dq, void* dk, void* dv, float* delta,
-                  unsigned* status, cudaStream_t stream) {
+                  int passes, unsigned* status, cudaStream_t stream) {
   if (p.dtype != NLFA_DTYPE_F16 && p.dtype != NLFA_DTYPE_BF16) return NLFA_ERR_UNSUPPORTED_PATH;
   if (p.D != 64 && p.D != 128) return NLFA_ERR_UNSUPPORTED_PATH;
-  int st = launch_delta(p, dout, o, delta, stream);
+  int st = NLFA_OK;
+  if (passes & NLFA_PASS_DELTA) st = launch_delta(p, dout, o, delta, stream);
   if (st != NLFA_OK) return st;
   CUtensorMap mq, mk, mv, mdo;
   st = make_tile_map(&mq, q, p.dtype, p.B, p.T, p.H, p.D, kTile);
@@ -443,11 +448,11 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D == 64) {
-    return bf16 ? launch_both<__nv_bfloat16, 64, 3>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, status, stream)
-                : launch_both<__half, 64, 3>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, status, stream);
+    return bf16 ? launch_both<__nv_bfloat16, 64, 3>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
+                : launch_both<__half, 64, 3>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
   }
-  return bf16 ? launch_both<__nv_bfloat16, 128, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, status, stream)
-              : launch_both<__half, 128, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, status, stream);
+  return bf16 ? launch_both<__nv_bfloat16, 128, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
+              : launch_both<__half, 128, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
 }
 
 }  // namespace nlfa

@@ -71,14 +71,14 @@ int launch_fwd_simt(const Problem& p, const void* q, const void* k, const void* 
                     float* lse, cudaStream_t stream);
 int launch_bwd_simt(const Problem& p, const void* dout, const void* q, const void* k,
                     const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
-                    float* delta, cudaStream_t stream);
+                    float* delta, int passes, cudaStream_t stream);
 int launch_delta(const Problem& p, const void* dout, const void* o, float* delta,
                  cudaStream_t stream);
 int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v, void* o,
                   float* lse, unsigned* status, cudaStream_t stream);
 int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                   const void* o, const float* lse, void* dq, void* dk, void* dv, float* delta,
-                  unsigned* status, cudaStream_t stream);
+                  int passes, unsigned* status, cudaStream_t stream);
 int launch_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,
                           float* s_out, float* o_out, unsigned* status, cudaStream_t stream);
 

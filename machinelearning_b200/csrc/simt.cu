@@ -271,16 +271,19 @@ int delta_t(const Problem& p, const void* dout, const void* o, float* delta, cud
 
 template <typename T, int D>
 int bwd_t(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
-          const float* lse, void* dq, void* dk, void* dv, const float* delta, cudaStream_t s) {
+          const float* lse, void* dq, void* dk, void* dv, const float* delta, int passes,
+          cudaStream_t s) {
   const long long qrows = static_cast<long long>(p.B) * p.H * p.T;
   const long long krows = static_cast<long long>(p.B) * p.Hkv * p.T;
-  dq_simt_kernel<T, D><<<blocks_for(qrows), kWarpsPerBlock * 32, 0, s>>>(
-      p, static_cast<const T*>(dout), static_cast<const T*>(q), static_cast<const T*>(k),
-      static_cast<const T*>(v), lse, delta, static_cast<T*>(dq));
+  if (passes & NLFA_PASS_DQ)
+    dq_simt_kernel<T, D><<<blocks_for(qrows), kWarpsPerBlock * 32, 0, s>>>(
+        p, static_cast<const T*>(dout), static_cast<const T*>(q), static_cast<const T*>(k),
+        static_cast<const T*>(v), lse, delta, static_cast<T*>(dq));
   if (cudaGetLastError() != cudaSuccess) return NLFA_ERR_CUDA;
-  dkv_simt_kernel<T, D><<<blocks_for(krows), kWarpsPerBlock * 32, 0, s>>>(
-      p, static_cast<const T*>(dout), static_cast<const T*>(q), static_cast<const T*>(k),
-      static_cast<const T*>(v), lse, delta, static_cast<T*>(dk), static_cast<T*>(dv));
+  if (passes & NLFA_PASS_DKV)
+    dkv_simt_kernel<T, D><<<blocks_for(krows), kWarpsPerBlock * 32, 0, s>>>(
+        p, static_cast<const T*>(dout), static_cast<const T*>(q), static_cast<const T*>(k),
+        static_cast<const T*>(v), lse, delta, static_cast<T*>(dk), static_cast<T*>(dv));
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
@@ -330,10 +333,12 @@ int launch_delta(const Problem& p, const void* dout, const void* o, float* delta
 
 int launch_bwd_simt(const Problem& p, const void* dout, const void* q, const void* k,
                     const void* v, const void* o, const float* lse, void* dq, void* dk, void* dv,
-                    float* delta, cudaStream_t stream) {
-  int st = launch_delta(p, dout, o, delta, stream);
-  if (st != NLFA_OK) return st;
-#define CALL(T, DD) bwd_t<T, DD>(p, dout, q, k, v, lse, dq, dk, dv, delta, stream)
+                    float* delta, int passes, cudaStream_t stream) {
+  if (passes & NLFA_PASS_DELTA) {
+    int st = launch_delta(p, dout, o, delta, stream);
+    if (st != NLFA_OK) return st;
+  }
+#define CALL(T, DD) bwd_t<T, DD>(p, dout, q, k, v, lse, dq, dk, dv, delta, passes, stream)
   NLFA_DISPATCH(p, CALL);
 #undef CALL
 }

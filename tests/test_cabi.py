@@ -1,0 +1,84 @@
+"""The C-ABI library on a machine without a GPU: it builds, loads, exports every
+declared symbol, and its host-side argument checks answer before any launch."""
+import ctypes
+import pathlib
+import re
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "nlfa.h"
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from machinelearning_b200 import _build, _lib
+    _build.build()
+    return _lib.load()
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(nlfa_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for must in ("nlfa_fwd", "nlfa_bwd", "nlfa_bwd_scratch_bytes", "nlfa_selftest",
+                 "nlfa_strerror", "nlfa_device_status", "nlfa_resolve_path"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for name in declared_symbols():
+        assert hasattr(lib, name), f"{name} is declared in nlfa.h but not exported"
+
+
+def test_ctypes_signatures_cover_the_header():
+    from machinelearning_b200 import _lib
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+
+
+def test_strerror_and_version(lib):
+    assert lib.nlfa_version() >= 1
+    assert lib.nlfa_strerror(0) == b"ok"
+    for code in range(1, 13):
+        assert lib.nlfa_strerror(code) not in (b"", b"ok", b"unknown status")
+    assert lib.nlfa_strerror(999) == b"unknown status"
+
+
+def test_path_resolution_mirrors_use_mma(lib):
+    from machinelearning_b200 import _lib as L
+    assert lib.nlfa_resolve_path(L.DTYPE_BF16, 64, L.PATH_AUTO) == L.PATH_TENSOR
+    assert lib.nlfa_resolve_path(L.DTYPE_F16, 128, L.PATH_AUTO) == L.PATH_TENSOR
+    assert lib.nlfa_resolve_path(L.DTYPE_F32, 64, L.PATH_AUTO) == L.PATH_SIMT
+    assert lib.nlfa_resolve_path(L.DTYPE_BF16, 32, L.PATH_AUTO) == L.PATH_SIMT
+    assert lib.nlfa_resolve_path(L.DTYPE_BF16, 64, L.PATH_SIMT) == L.PATH_SIMT
+    assert lib.nlfa_resolve_path(L.DTYPE_F32, 64, L.PATH_TENSOR) == -7     # use_mma=True on fp32
+    assert lib.nlfa_resolve_path(L.DTYPE_BF16, 48, L.PATH_AUTO) == -4
+    assert lib.nlfa_resolve_path(7, 64, L.PATH_AUTO) == -3
+
+
+def test_argument_checks_answer_without_a_gpu(lib):
+    from machinelearning_b200 import _lib as L
+    one = ctypes.c_void_p(16)       # non-null, aligned; never dereferenced by the checks below
+    fwd = lambda **kw: lib.nlfa_fwd(
+        kw.get("q", one), one, one, one, one, kw.get("B", 1), kw.get("T", 8), kw.get("H", 2),
+        kw.get("Hkv", 1), kw.get("D", 64), 0.125, kw.get("window", 0), kw.get("sinks", 0),
+        kw.get("dtype", L.DTYPE_F32), kw.get("path", L.PATH_AUTO), None)
+    assert fwd(Hkv=0) == 2 and fwd(H=3, Hkv=2) == 2 and fwd(B=-1) == 2
+    assert fwd(dtype=9) == 3
+    assert fwd(D=48) == 4
+    assert fwd(window=4, sinks=4) == 5 and fwd(window=0, sinks=1) == 5 and fwd(window=-2) == 5
+    assert fwd(path=L.PATH_TENSOR) == 7
+    assert fwd(B=0) == 0 and fwd(T=0) == 0                 # empty problem: successful no-op
+    assert fwd(q=None) == 1
+    assert fwd(q=ctypes.c_void_p(24)) == 6                 # not 16-byte aligned
+    assert lib.nlfa_bwd_scratch_bytes(2, 100, 4) == 2 * 100 * 4 * 4
+    assert lib.nlfa_bwd_scratch_bytes(0, 100, 4) == 0
+    bwd = lib.nlfa_bwd(one, one, one, one, one, one, one, one, one, one, 8, 1, 8, 2, 1, 64,
+                       0.125, 0, 0, L.DTYPE_F32, L.PATH_AUTO, None)
+    assert bwd == 11                                        # scratch too small
+    errs = (ctypes.c_float * 2)()
+    assert lib.nlfa_selftest(L.DTYPE_BF16, 64, one, 16, errs, None) == 11
+    assert lib.nlfa_selftest(L.DTYPE_F32, 64, one, 1 << 20, errs, None) == 7

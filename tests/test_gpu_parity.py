@@ -1,0 +1,241 @@
+"""Parity of the CUDA kernels with the CPU oracle (needs a B200).
+
+Tolerances: float32 inputs max-abs <= 1e-5 for O and LSE (2e-5 for gradients,
+whose magnitudes are several times larger); 16-bit inputs <= 2e-2 relative,
+where relative means max|x - ref| / max|ref| per tensor.  The oracle always gets
+the same rounded inputs, upcast to float64 (as nanolab/tests.py:386, :456 do).
+"""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_paths, load_golden
+from oracle import attention_f64 as orc
+
+pytestmark = pytest.mark.gpu
+
+REL_16BIT = 2e-2
+ABS_F32 = 1e-5
+
+
+@pytest.fixture(scope="module")
+def fc():
+    from machinelearning_b200 import flash_cuda
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    assert flash_cuda.is_available(), flash_cuda.unavailable_reason()
+    assert flash_cuda.mma_available(), flash_cuda.mma_unavailable_reason()
+    return flash_cuda
+
+
+def rel(got, ref):
+    got = got.detach().double().cpu().numpy()
+    return float(np.abs(got - ref).max() / np.abs(ref).max())
+
+
+def mabs(got, ref):
+    return float(np.abs(got.detach().double().cpu().numpy() - ref).max())
+
+
+def device_status_ok():
+    from machinelearning_b200 import _lib
+    raw = ctypes.c_uint(0)
+    return _lib.load().nlfa_device_status(ctypes.byref(raw)) == 0 and raw.value == 0
+
+
+def run_fwd_bwd(fc, q, k, v, do, scale, use_mma, window=0, sinks=0):
+    q, k, v = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    y = fc.flash_attn(q, k, v, scale, use_mma=use_mma, window=window, sinks=sinks)
+    dq, dk, dv = torch.autograd.grad(y, (q, k, v), do)
+    return y, dq, dk, dv
+
+
+def test_selftest_passes_for_every_tensor_core_variant(fc):
+    from machinelearning_b200 import _lib
+    lib = _lib.load()
+    ws = torch.empty(lib.nlfa_selftest_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    errs = (ctypes.c_float * 2)()
+    for code in (_lib.DTYPE_BF16, _lib.DTYPE_F16):
+        for d in (64, 128):
+            st = lib.nlfa_selftest(code, d, ws.data_ptr(), ws.numel(), errs,
+                                   torch.cuda.current_stream().cuda_stream)
+            assert st == 0, (code, d, _lib.strerror(st), errs[0], errs[1])
+            assert errs[0] < 1e-3 and errs[1] < 1e-3
+
+
+@pytest.mark.parametrize("path", golden_paths(), ids=lambda p: p.stem)
+def test_simt_fp32_matches_reference_golden(fc, path):
+    g = load_golden(path)
+    q, k, v, do = (torch.from_numpy(g[n]).cuda() for n in ("q", "k", "v", "dout"))
+    o, lse = fc.fwd(q, k, v, g["scale"], False, g["window"], g["sinks"])
+    dq, dk, dv = fc.bwd(do, q, k, v, o, lse, g["scale"], False, g["window"], g["sinks"])
+    assert mabs(o, g["o"]) <= ABS_F32
+    assert mabs(lse, g["lse"]) <= ABS_F32
+    for got, name in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert mabs(got, g[name]) <= 2 * ABS_F32, name
+
+
+@pytest.mark.parametrize("path", [p for p in golden_paths() if "_d64" in p.stem or "_d128" in p.stem
+                                  or "w256" in p.stem], ids=lambda p: p.stem)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tensor_core_matches_reference_golden(fc, path, dtype):
+    g = load_golden(path)
+    # golden inputs are bf16-exact; for float16 the oracle is re-run on the float16-rounded inputs
+    q, k, v, do = (torch.from_numpy(g[n]).cuda().to(dtype) for n in ("q", "k", "v", "dout"))
+    if dtype is torch.bfloat16:
+        ref = {n: g[n] for n in ("o", "lse", "dq", "dk", "dv")}
+    else:
+        o_r, lse_r = orc.attention_fwd(q, k, v, g["scale"], g["window"], g["sinks"])
+        gq, gk, gv = orc.attention_bwd(do, q, k, v, g["scale"], g["window"], g["sinks"])
+        ref = dict(o=o_r, lse=lse_r, dq=gq, dk=gk, dv=gv)
+    o, lse = fc.fwd(q, k, v, g["scale"], True, g["window"], g["sinks"])
+    dq, dk, dv = fc.bwd(do, q, k, v, o, lse, g["scale"], True, g["window"], g["sinks"])
+    assert device_status_ok()
+    assert rel(o, ref["o"]) <= REL_16BIT
+    assert mabs(lse, ref["lse"]) <= 1e-3
+    for got, name in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert rel(got, ref[name]) <= REL_16BIT, name
+
+
+CASES = [
+    # B, T, H, Hkv, D, window, sinks
+    (2, 100, 4, 2, 64, 0, 0),        # the reference's device-test shape (tests.py:364) at D=64
+    (2, 100, 4, 2, 128, 0, 0),
+    (1, 33, 2, 1, 64, 0, 0),         # shorter than one tile
+    (1, 128, 1, 1, 64, 0, 0),        # exactly one tile
+    (1, 129, 2, 2, 128, 0, 0),       # one row into the second tile
+    (1, 640, 3, 1, 64, 0, 0),        # odd tile count, GQA group 3
+    (1, 511, 2, 2, 64, 64, 0),       # tests.py:3513
+    (1, 512, 2, 2, 64, 64, 4),
+    (1, 700, 2, 1, 128, 256, 0),
+    (1, 900, 2, 2, 64, 300, 130),    # sinks spill into a second key block
+    (1, 300, 2, 2, 64, 400, 4),      # window >= T: plain causal
+    (1, 2048, 1, 1, 64, 512, 4),     # tests.py:3511
+]
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D,window,sinks", CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_tensor_core_fwd_bwd_vs_oracle(fc, B, T, H, Hkv, D, window, sinks, dtype):
+    torch.manual_seed(0)
+    q, k, v, do = (torch.randn(B, T, h, D, device="cuda").to(dtype) for h in (H, Hkv, Hkv, H))
+    scale = 1.0 / math.sqrt(D)
+    y, dq, dk, dv = run_fwd_bwd(fc, q, k, v, do, scale, True, window, sinks)
+    assert device_status_ok()
+    o_r, lse_r = orc.attention_fwd(q, k, v, scale, window, sinks)
+    gq, gk, gv = orc.attention_bwd(do, q, k, v, scale, window, sinks)
+    assert rel(y, o_r) <= REL_16BIT
+    for got, want, name in ((dq, gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
+        assert rel(got, want) <= REL_16BIT, name
+    # the logsumexp tape
+    _, lse = fc.fwd(q, k, v, scale, True, window, sinks)
+    assert mabs(lse, lse_r) <= 1e-3
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D,window,sinks", [c for c in CASES if c[1] <= 700])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_simt_fwd_bwd_vs_oracle(fc, B, T, H, Hkv, D, window, sinks, dtype):
+    torch.manual_seed(0)
+    q, k, v, do = (torch.randn(B, T, h, D, device="cuda").to(dtype) for h in (H, Hkv, Hkv, H))
+    scale = 1.0 / math.sqrt(D)
+    y, dq, dk, dv = run_fwd_bwd(fc, q, k, v, do, scale, False, window, sinks)
+    o_r, _ = orc.attention_fwd(q, k, v, scale, window, sinks)
+    gq, gk, gv = orc.attention_bwd(do, q, k, v, scale, window, sinks)
+    if dtype is torch.float32:
+        assert mabs(y, o_r) <= ABS_F32
+        for got, want in ((dq, gq), (dk, gk), (dv, gv)):
+            assert mabs(got, want) <= 2 * ABS_F32
+    else:
+        for got, want in ((y, o_r), (dq, gq), (dk, gk), (dv, gv)):
+            assert rel(got, want) <= REL_16BIT
+
+
+def test_config1_fp32_full_shape(fc):
+    # fp32, B=4, H=4, T=256, D=64, N(0,1) from seed 0, scale 1/8: O, LSE, dQ, dK, dV <= 1e-5
+    torch.manual_seed(0)
+    q, k, v, do = (torch.randn(4, 256, 4, 64) for _ in range(4))
+    o_r, lse_r = orc.attention_fwd(q, k, v, 0.125)
+    gq, gk, gv = orc.attention_bwd(do, q, k, v, 0.125)
+    qc, kc, vc, dc = (t.cuda() for t in (q, k, v, do))
+    o, lse = fc.fwd(qc, kc, vc, 0.125, False)
+    dq, dk, dv = fc.bwd(dc, qc, kc, vc, o, lse, 0.125, False)
+    assert mabs(o, o_r) <= ABS_F32 and mabs(lse, lse_r) <= ABS_F32
+    for got, want in ((dq, gq), (dk, gk), (dv, gv)):
+        assert mabs(got, want) <= 2 * ABS_F32
+
+
+def test_two_kernel_families_agree_and_are_reproducible(fc):
+    # nanolab/tests.py:394-420: mma vs fma forwards within tol/2, backwards within 4 tol,
+    # repeated runs bit-identical
+    torch.manual_seed(0)
+    B, T, H, Hkv, D = 2, 300, 4, 2, 64
+    q, k, v, do = (torch.randn(B, T, h, D, device="cuda").bfloat16() for h in (H, Hkv, Hkv, H))
+    scale = 1.0 / math.sqrt(D)
+    a = run_fwd_bwd(fc, q, k, v, do, scale, True)
+    b = run_fwd_bwd(fc, q, k, v, do, scale, False)
+    assert (a[0].float() - b[0].float()).abs().max() < 4e-2
+    for x, y in zip(a[1:], b[1:]):
+        assert (x.float() - y.float()).abs().max() < 3.2e-1
+    again = run_fwd_bwd(fc, q, k, v, do, scale, True)
+    for x, y in zip(a, again):
+        assert torch.equal(x, y), "tensor-core path is not bit-reproducible"
+    again = run_fwd_bwd(fc, q, k, v, do, scale, False)
+    for x, y in zip(b, again):
+        assert torch.equal(x, y), "SIMT path is not bit-reproducible"
+
+
+def test_unwritten_outputs_are_caught_by_sentinels(fc):
+    # every element of O, LSE, dQ, dK, dV must be written: pre-fill with NaN through the C ABI
+    from machinelearning_b200 import _lib
+    lib = _lib.load()
+    B, T, H, Hkv, D = 1, 333, 2, 1, 64
+    torch.manual_seed(1)
+    q, k, v, do = (torch.randn(B, T, h, D, device="cuda").bfloat16() for h in (H, Hkv, Hkv, H))
+    nan = lambda t: torch.full_like(t, float("nan"))
+    o, dq, dk, dv = nan(q), nan(q), nan(k), nan(v)
+    lse = torch.full((B, H, T), float("nan"), device="cuda")
+    scratch = torch.empty(lib.nlfa_bwd_scratch_bytes(B, T, H), dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    for path in (_lib.PATH_TENSOR, _lib.PATH_SIMT):
+        assert lib.nlfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                            B, T, H, Hkv, D, 0.125, 0, 0, _lib.DTYPE_BF16, path, s) == 0
+        assert lib.nlfa_bwd(do.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                            lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                            scratch.data_ptr(), scratch.numel(), B, T, H, Hkv, D, 0.125, 0, 0,
+                            _lib.DTYPE_BF16, path, s) == 0
+        torch.cuda.synchronize()
+        for t in (o, lse, dq, dk, dv):
+            assert not torch.isnan(t).any()
+            t.fill_(float("nan"))
+
+
+def test_autocast_bridge_and_errors(fc):
+    # nanolab/tests.py:473-482 and :424-429
+    B, T, H, Hkv, D = 2, 100, 4, 2, 64
+    scale = 1.0 / math.sqrt(D)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        q = torch.randn(B, T, H, D, device="cuda", requires_grad=True)
+        k = torch.randn(B, T, Hkv, D, device="cuda", requires_grad=True)
+        v = torch.randn(B, T, Hkv, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        assert fc.supports(q, k, v)
+        y = fc.flash_attn(q, k, v, scale)
+        y_sdpa = fc.sdpa_reference(q, k, v, scale)
+    assert y.dtype is torch.bfloat16
+    assert (y.float() - y_sdpa.float()).abs().max() < 5e-2
+    y.sum().backward()
+    assert q.grad is not None and q.grad.dtype is torch.float32
+    q32 = torch.randn(1, 32, 2, 64, device="cuda")
+    with pytest.raises(ValueError):
+        fc.flash_attn(q32, q32, q32, scale, use_mma=True)
+    with pytest.raises(ValueError):
+        fc.flash_attn(q32, q32, q32, scale, window=4, sinks=4)
+    with pytest.raises(ValueError):
+        fc.flash_attn(q32[..., :48], q32[..., :48], q32[..., :48], scale)
+    # non-contiguous inputs are normalised, not refused (flash_cuda.py:184-186)
+    qt = torch.randn(1, 2, 32, 64, device="cuda").transpose(1, 2)
+    assert fc.flash_attn(qt, qt, qt, scale).shape == qt.shape
+    # empty batch is a no-op
+    e = torch.empty(0, 16, 2, 64, device="cuda")
+    assert fc.flash_attn(e, e, e, scale).shape == e.shape
