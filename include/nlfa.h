@@ -55,6 +55,7 @@ extern "C" {
 #define NLFA_ERR_DEVICE_TIMEOUT 10
 #define NLFA_ERR_SCRATCH_TOO_SMALL 11
 #define NLFA_ERR_SELFTEST_MISMATCH 12
+#define NLFA_ERR_STATIC_SCRATCH_EXCEEDED 13
 
 /* Library version, bumped when the ABI changes. */
 int nlfa_version(void);
@@ -109,6 +110,33 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
                     const float* lse, void* dq, void* dk, void* dv, void* scratch,
                     size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
                     int window, int sinks, int dtype, int path, int passes, void* stream);
+
+/* The backward without a caller-supplied scratch buffer.  No counterpart in the
+ * reference (its backward allocates its own tape with at::empty).
+ *
+ * For callers that cannot give nlfa_bwd a scratch buffer: processes whose device
+ * memory is already committed in full to some other allocator or budget, and
+ * code paths that may not make a call that allocates.  The Delta tape lives in
+ * a fixed 4 MiB array inside the library's device image instead, which every
+ * GPU that loads the library carries until the process exits.
+ *
+ *  - Limit: B * H * T <= nlfa_static_scratch_max_rows() (1,048,576); larger
+ *    problems are refused with NLFA_ERR_STATIC_SCRATCH_EXCEEDED.
+ *  - The first call made with a given device current looks up the array's
+ *    address on that device (cudaGetSymbolAddress) and caches it.  Make that
+ *    first call outside any stream capture.
+ *  - All calls on a device share the one array.  It keeps whatever the last call
+ *    wrote; every call rewrites all rows it later reads, so nothing has to be
+ *    cleared.  Two calls whose kernels can overlap on the GPU (different
+ *    streams, no dependency) race on it: serialise them.
+ *  - Neither this function nor anything it calls uses cudaMalloc, cudaFree or
+ *    an allocating library routine.
+ * Arguments, results and gradients are exactly those of nlfa_bwd. */
+size_t nlfa_static_scratch_max_rows(void);
+int nlfa_bwd_static_scratch(const void* dout, const void* q, const void* k, const void* v,
+                            const void* o, const float* lse, void* dq, void* dk, void* dv, int B,
+                            int T, int H, int Hkv, int D, float scale, int window, int sinks,
+                            int dtype, int path, void* stream);
 
 /* Bytes of device workspace `nlfa_selftest` needs. */
 size_t nlfa_selftest_workspace_bytes(void);

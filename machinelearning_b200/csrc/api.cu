@@ -134,6 +134,8 @@ const char* nlfa_strerror(int status) {
     case NLFA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
     case NLFA_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small";
     case NLFA_ERR_SELFTEST_MISMATCH: return "tensor-core self-test disagrees with the host reference";
+    case NLFA_ERR_STATIC_SCRATCH_EXCEEDED:
+      return "problem too large for the built-in scratch array (need B*H*T <= 1048576)";
   }
   return "unknown status";
 }
