@@ -164,8 +164,13 @@ int nlfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype};
   int st = check_problem(p);
   if (st != NLFA_OK) return st;
-  const int resolved = nlfa_resolve_path(dtype, D, path);
+  int resolved = nlfa_resolve_path(dtype, D, path);
   if (resolved < 0) return -resolved;
+  if (resolved == NLFA_PATH_TENSOR && !(scale > 0.f)) {
+    // the tensor-core forward takes the row maximum before scaling: positive scales only
+    if (path != NLFA_PATH_AUTO) return NLFA_ERR_UNSUPPORTED_PATH;
+    resolved = NLFA_PATH_SIMT;
+  }
   if (B == 0 || T == 0 || H == 0) return NLFA_OK;
   if (!q || !k || !v || !o || !lse) return NLFA_ERR_NULL_POINTER;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return NLFA_ERR_MISALIGNED;

@@ -15,18 +15,28 @@
 //              T0 = K Q^T, T1 = V dO^T           rows = keys, columns = queries
 //              dV += P dO_i,  dK += dS Q_i       (P, dS are already "transposed")
 //
-// T0/T1 are fp32 accumulators in TMEM (columns 0 and 128).  The eight compute
-// warps split each row in two 64-column halves; each thread turns its 64
-// scores into 16-bit P / dS and writes them back over the columns it just read
-// (first 32 columns of its half), from where they are the TMEM A operand of the
-// output products, whose B operand is the streamed tile read MN-major.
-// Outputs accumulate in TMEM at column 256 (dQ, or dV then dK).
+// Persistent: one CTA per SM takes work units (one stationary tile each) from a
+// global counter, heaviest first.  Warps 0-7 compute, warp 8 is the TMA producer
+// and the scheduler, warp 9 issues MMAs and owns TMEM.  The MMA issuer works one
+// streamed tile ahead: as soon as the compute warps have pulled T0/T1 into
+// registers it issues the next tile's T0/T1 products, so the tensor pipe runs
+// while the exponentials are computed; the stationary tiles are double buffered
+// so the next unit's loads and first products overlap the current unit's tail.
 //
-// Warps: 0-7 compute, 8 TMA producer, 9 MMA issuer and TMEM owner.
+// TMEM: T0 at column 0, T1 at 128 (fp32); outputs accumulate at 256 (dQ: D
+// columns; dV then dK: 2 D columns).  The 16-bit P / dS operands of the output
+// products live in their own columns when there is room (everything except
+// dK/dV at D = 128, where they overwrite the columns of T0/T1 just read).
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace nlfa {
+
+// Work counters for the in-kernel scheduler: [slot][0] next unit, [slot][1] CTAs
+// finished.  The last CTA of a launch to finish zeroes its slot again.
+constexpr int kSchedSlots = 256;
+__device__ unsigned g_bwd_sched[kSchedSlots][2];
+
 namespace {
 
 enum { MODE_DQ = 0, MODE_DKV = 1 };
@@ -35,39 +45,96 @@ struct BwdParams {
   int T, H, Hkv;
   int window, sinks;
   int n_tiles;
+  int BH;                // B * H (dQ) or B * Hkv (dK/dV)
+  int total_units;       // n_tiles * BH
   float scale, scale_log2;
   const float* lse;
   const float* delta;
   void* out0;            // dQ  | dK
   void* out1;            // --  | dV
   unsigned* status;
+  unsigned* sched;       // this launch's two counters
 };
 
-template <int D, int STAGES>
+template <int D, int STAGES, int XBUF>
 struct BwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;
-  static constexpr int kX = 0;                                  // X0, X1 stationary
-  static constexpr int kY = kX + 2 * kTileBytes;                // per stage: Y0, Y1
-  static constexpr int kVec = kY + STAGES * 2 * kTileBytes;     // per stage: lse2[128], delta[128]
+  static constexpr int kX = 0;                                  // [XBUF] x (X0, X1)
+  static constexpr int kY = kX + XBUF * 2 * kTileBytes;         // per stage: Y0, Y1
+  static constexpr int kVec = kY + STAGES * 2 * kTileBytes;     // per stage: -lse2[128], -delta[128]
   static constexpr int kBar = kVec + STAGES * 1024;
-  // barriers: x_full, t_full, pd_full, out_full, y_full[S], y_empty[S]
-  static constexpr int kNumBars = 4 + 2 * STAGES;
-  static constexpr int kTmemSlot = kBar + 8 * kNumBars;
+  // barriers: x_full[XBUF], x_empty[XBUF], t_full, t_consumed, pd_full, out_ready,
+  //           sched_full[kRing], y_full[S], y_empty[S]
+  static constexpr int kRing = 8;
+  static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES;
+  static constexpr int kSched = kBar + 8 * kNumBars;            // ring of unit indices
+  static constexpr int kTmemSlot = kSched + 4 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-template <typename T, int D, int MODE, int STAGES>
+// One work unit: a stationary tile and the list of streamed tiles it meets.
+template <int MODE>
+struct BwdUnit {
+  int tile, b, h, hk;          // h: first query head of the unit
+  int s_lo, extra, n_inner, n_iters;
+
+  __device__ __forceinline__ int streamed_index(int inner) const {
+    return inner < extra ? inner : s_lo + (inner - extra);
+  }
+};
+
+template <int MODE>
+__device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p) {
+  BwdUnit<MODE> w;
+  const int rank = u / p.BH;
+  const int bh = u - rank * p.BH;
+  const int group = p.H / p.Hkv;
+  if (MODE == MODE_DQ) {
+    w.tile = p.n_tiles - 1 - rank;              // late query tiles see the most keys
+    w.b = bh / p.H;
+    w.h = bh - w.b * p.H;
+    w.hk = w.h / group;
+    const TileRange r = tile_range(w.tile, p.window, p.sinks);
+    w.s_lo = r.lo;
+    w.extra = r.sink_blocks < r.lo ? r.sink_blocks : r.lo;
+    w.n_inner = w.extra + (r.hi - r.lo + 1);
+    w.n_iters = w.n_inner;
+  } else {
+    w.tile = rank;                              // early key blocks are seen by the most queries
+    w.b = bh / p.Hkv;
+    w.hk = bh - w.b * p.Hkv;
+    w.h = w.hk * group;
+    w.s_lo = w.tile;
+    int s_hi = p.n_tiles - 1;
+    if (p.window > 0 && w.tile >= (p.sinks + kTile - 1) / kTile) {
+      const int last_q = w.tile * kTile + kTile - 1 + (p.window - p.sinks) - 1;
+      const int hi = last_q / kTile;
+      s_hi = hi < s_hi ? hi : s_hi;
+    }
+    w.extra = 0;
+    w.n_inner = s_hi - w.s_lo + 1;
+    w.n_iters = w.n_inner * group;
+  }
+  return w;
+}
+
+template <typename T, int D, int MODE, int STAGES, int XBUF>
 __global__ void __launch_bounds__(320, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
               const BwdParams p) {
-  using L = BwdSmem<D, STAGES>;
+  using L = BwdSmem<D, STAGES, XBUF>;
   constexpr int kBoxes = D / 64;
   constexpr int kBoxBytes = kTile * 128;
   constexpr bool kBf16 = Pack2<T>::kIsBf16;
   constexpr uint32_t kOutCol = 256;
+  constexpr int kOutCols = MODE == MODE_DQ ? D : 2 * D;
+  constexpr bool kSep = (256 + kOutCols + 128) <= 512;        // room for separate P / dS columns
+  constexpr uint32_t kPCol = kSep ? 256 + kOutCols : 0;        // P  (dK/dV only)
+  constexpr uint32_t kDsCol = kSep ? 256 + kOutCols + 64 : 128;
+  constexpr int kRing = L::kRing;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -77,53 +144,25 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
 
   auto bar = [&](int i) -> uint32_t { return base + L::kBar + 8u * i; };
-  constexpr int X_FULL = 0, T_FULL = 1, PD_FULL = 2, OUT_FULL = 3, Y_FULL = 4, Y_EMPTY = 4 + STAGES;
+  constexpr int X_FULL = 0, X_EMPTY = XBUF, T_FULL = 2 * XBUF, T_CONSUMED = T_FULL + 1,
+                PD_FULL = T_FULL + 2, OUT_READY = T_FULL + 3, SCHED_FULL = T_FULL + 4,
+                Y_FULL = SCHED_FULL + kRing, Y_EMPTY = Y_FULL + STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
+  volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
   const WaitCtx wctx{abort_flag, p.status};
-
-  // ---- work owned by this CTA.  blockIdx.x walks tiles heavy-first.
-  //  dQ:    tile = query tile i, blockIdx.y = b * H + h; streams key blocks of tile_range(i)
-  //  dK/dV: tile = key block j,  blockIdx.y = b * Hkv + hk; streams query tiles i >= j that
-  //         see block j, for every head of the GQA group
-  const int group = p.H / p.Hkv;
-  int tile, b, h, hk;
-  int s_lo, s_hi, extra, n_inner, n_iters;     // streamed index list
-  if (MODE == MODE_DQ) {
-    tile = p.n_tiles - 1 - static_cast<int>(blockIdx.x);
-    b = blockIdx.y / p.H;
-    h = blockIdx.y % p.H;
-    hk = h / group;
-    const TileRange r = tile_range(tile, p.window, p.sinks);
-    s_lo = r.lo;
-    s_hi = r.hi;
-    extra = r.sink_blocks < r.lo ? r.sink_blocks : r.lo;
-    n_inner = extra + (s_hi - s_lo + 1);
-    n_iters = n_inner;
-  } else {
-    tile = static_cast<int>(blockIdx.x);       // early key blocks see the most queries
-    b = blockIdx.y / p.Hkv;
-    hk = blockIdx.y % p.Hkv;
-    h = hk * group;
-    s_lo = tile;
-    s_hi = p.n_tiles - 1;
-    if (p.window > 0 && tile >= (p.sinks + kTile - 1) / kTile) {
-      const int last_q = tile * kTile + kTile - 1 + (p.window - p.sinks) - 1;
-      const int hi = last_q / kTile;
-      s_hi = hi < s_hi ? hi : s_hi;
-    }
-    extra = 0;
-    n_inner = s_hi - s_lo + 1;
-    n_iters = n_inner * group;
-  }
-  auto streamed_index = [&](int inner) { return inner < extra ? inner : s_lo + (inner - extra); };
 
   if (threadIdx.x == 0) {
     *abort_flag = (*reinterpret_cast<volatile unsigned*>(p.status) != STATUS_OK) ? 1 : 0;
-    mbar_init(bar(X_FULL), 1);
+    for (int i = 0; i < XBUF; ++i) {
+      mbar_init(bar(X_FULL + i), 1);
+      mbar_init(bar(X_EMPTY + i), 1);
+    }
     mbar_init(bar(T_FULL), 1);
+    mbar_init(bar(T_CONSUMED), 256);
     mbar_init(bar(PD_FULL), 256);
-    mbar_init(bar(OUT_FULL), 1);
+    mbar_init(bar(OUT_READY), 1);
+    for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(Y_FULL + s), 1);
       mbar_init(bar(Y_EMPTY + s), 1);
@@ -140,10 +179,17 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tmem = *tmem_slot;
   const bool dead = *abort_flag != 0;
 
+  // Every role reads the unit index of its uc-th unit from the ring the producer
+  // fills; a negative index means there is no more work.
+  auto next_unit = [&](int uc, bool& ok) -> int {
+    ok = mbar_wait(bar(SCHED_FULL + (uc % kRing)), (uc / kRing) & 1, wctx, 40);
+    return ok ? sched_ring[uc % kRing] : -1;
+  };
+
   if (dead) {
     // straight to the tail
   } else if (warp == 8) {
-    // =============================== TMA producer ============================
+    // ========================= scheduler + TMA producer ======================
     const CUtensorMap* mx0 = MODE == MODE_DQ ? &tm_q : &tm_k;
     const CUtensorMap* mx1 = MODE == MODE_DQ ? &tm_do : &tm_v;
     const CUtensorMap* my0 = MODE == MODE_DQ ? &tm_k : &tm_q;
@@ -153,45 +199,66 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tma_prefetch_desc(mx1);
       tma_prefetch_desc(my0);
       tma_prefetch_desc(my1);
-      const int xh = MODE == MODE_DQ ? h : hk;
-      mbar_arrive_expect_tx(bar(X_FULL), 2 * L::kTileBytes);
-      for (int x = 0; x < kBoxes; ++x) {
-        tma_load_4d(base + L::kX + x * kBoxBytes, mx0, bar(X_FULL), 64 * x, xh, tile * kTile, b);
-        tma_load_4d(base + L::kX + L::kTileBytes + x * kBoxBytes, mx1, bar(X_FULL), 64 * x, xh,
-                    tile * kTile, b);
-      }
     }
     bool ok = true;
-    for (int it = 0; it < n_iters; ++it) {
-      const int s = it % STAGES;
-      const uint32_t ph = (it / STAGES) & 1;
-      const int g = it / n_inner;
-      const int idx = streamed_index(it - g * n_inner);
-      const int yh = MODE == MODE_DQ ? hk : h + g;
-      if (lane == 0) ok = mbar_wait(bar(Y_EMPTY + s), ph ^ 1, wctx, 31);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      if (MODE == MODE_DKV) {
-        // per-query logsumexp (base 2) and Delta of the streamed query tile
-        float* vec = reinterpret_cast<float*>(gen + L::kVec + s * 1024);
-        const long long row0 = (static_cast<long long>(b) * p.H + yh) * p.T;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c = lane * 4 + i;
-          const int qpos = idx * kTile + c;
-          const bool in = qpos < p.T;
-          vec[c] = in ? p.lse[row0 + qpos] * kLog2e : INFINITY;
-          vec[128 + c] = in ? p.delta[row0 + qpos] : 0.f;
-        }
-        __syncwarp();
-      }
+    int git = 0;
+    for (int uc = 0; ok; ++uc) {
+      int u = 0;
       if (lane == 0) {
-        mbar_arrive_expect_tx(bar(Y_FULL + s), 2 * L::kTileBytes);
-        const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes;
-        for (int x = 0; x < kBoxes; ++x) {
-          tma_load_4d(y0 + x * kBoxBytes, my0, bar(Y_FULL + s), 64 * x, yh, idx * kTile, b);
-          tma_load_4d(y0 + L::kTileBytes + x * kBoxBytes, my1, bar(Y_FULL + s), 64 * x, yh,
-                      idx * kTile, b);
+        u = static_cast<int>(atomicAdd(&p.sched[0], 1u));
+        if (u >= p.total_units) u = -1;
+        sched_ring[uc % kRing] = u;
+        mbar_arrive(bar(SCHED_FULL + (uc % kRing)));
+      }
+      u = __shfl_sync(0xffffffffu, u, 0);
+      if (u < 0) break;
+      const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
+      const int xb = uc % XBUF;
+      if (lane == 0) {
+        ok = mbar_wait(bar(X_EMPTY + xb), ((uc / XBUF) & 1) ^ 1, wctx, 30);
+        if (ok) {
+          const int xh = MODE == MODE_DQ ? w.h : w.hk;
+          const uint32_t xa = base + L::kX + xb * 2 * L::kTileBytes;
+          mbar_arrive_expect_tx(bar(X_FULL + xb), 2 * L::kTileBytes);
+          for (int x = 0; x < kBoxes; ++x) {
+            tma_load_4d(xa + x * kBoxBytes, mx0, bar(X_FULL + xb), 64 * x, xh, w.tile * kTile, w.b);
+            tma_load_4d(xa + L::kTileBytes + x * kBoxBytes, mx1, bar(X_FULL + xb), 64 * x, xh,
+                        w.tile * kTile, w.b);
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      for (int it = 0; ok && it < w.n_iters; ++it, ++git) {
+        const int s = git % STAGES;
+        const uint32_t ph = (git / STAGES) & 1;
+        const int g = it / w.n_inner;
+        const int idx = w.streamed_index(it - g * w.n_inner);
+        const int yh = MODE == MODE_DQ ? w.hk : w.h + g;
+        if (lane == 0) ok = mbar_wait(bar(Y_EMPTY + s), ph ^ 1, wctx, 31);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        if (MODE == MODE_DKV) {
+          // negated base-2 logsumexp and negated Delta of the streamed query tile
+          float* vec = reinterpret_cast<float*>(gen + L::kVec + s * 1024);
+          const long long row0 = (static_cast<long long>(w.b) * p.H + yh) * p.T;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int c = lane * 4 + i;
+            const int qpos = idx * kTile + c;
+            const bool in = qpos < p.T;
+            vec[c] = in ? -p.lse[row0 + qpos] * kLog2e : -INFINITY;
+            vec[128 + c] = in ? -p.delta[row0 + qpos] : 0.f;
+          }
+          __syncwarp();
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar(Y_FULL + s), 2 * L::kTileBytes);
+          const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes;
+          for (int x = 0; x < kBoxes; ++x) {
+            tma_load_4d(y0 + x * kBoxBytes, my0, bar(Y_FULL + s), 64 * x, yh, idx * kTile, w.b);
+            tma_load_4d(y0 + L::kTileBytes + x * kBoxBytes, my1, bar(Y_FULL + s), 64 * x, yh,
+                        idx * kTile, w.b);
+          }
         }
       }
     }
@@ -200,14 +267,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t idesc_t = make_idesc(kBf16, 128, 128, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, 128, D, false, true);
-      const uint32_t x0 = base + L::kX, x1 = base + L::kX + L::kTileBytes;
-      bool ok = mbar_wait(bar(X_FULL), 0, wctx, 32);
-      for (int it = 0; ok && it < n_iters; ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
+
+      // T0 = X0 Y0^T, T1 = X1 Y1^T for global iteration `g` of unit buffer `xb`
+      auto issue_t = [&](int xb, int g) {
+        const int s = g % STAGES;
+        const uint32_t x0 = base + L::kX + xb * 2 * L::kTileBytes, x1 = x0 + L::kTileBytes;
         const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes, y1 = y0 + L::kTileBytes;
-        if (!(ok = mbar_wait(bar(Y_FULL + s), ph, wctx, 33))) break;
-        tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
@@ -221,119 +286,220 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                  idesc_t, kk > 0 ? 1u : 0u);
         }
         tc_commit(bar(T_FULL));
-        if (!(ok = mbar_wait(bar(PD_FULL), it & 1, wctx, 34))) break;
-        tc_fence_after();
-        const uint32_t acc = it > 0 ? 1u : 0u;
-        // 16-bit operand of k-step kk: half (kk / 4) of the row, 8 columns per step
+      };
+      auto issue_out = [&](int g, uint32_t acc) {
+        const int s = g % STAGES;
+        const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes, y1 = y0 + L::kTileBytes;
+        // 16-bit operand of k-step kk: 8 TMEM columns per step
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
-          const uint32_t acol = 64 * (kk >> 2) + 8 * (kk & 3);
+          const uint32_t acol = kSep ? 8 * kk : 64 * (kk >> 2) + 8 * (kk & 3);
           if (MODE == MODE_DQ) {
-            mma_ts(tmem + kOutCol, tmem + 128 + acol,
+            mma_ts(tmem + kOutCol, tmem + kDsCol + acol,
                    make_smem_desc(y0 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           } else {
-            mma_ts(tmem + kOutCol, tmem + 0 + acol,
+            mma_ts(tmem + kOutCol, tmem + kPCol + acol,
                    make_smem_desc(y1 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           }
         }
         if (MODE == MODE_DKV) {
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk) {
-            const uint32_t acol = 64 * (kk >> 2) + 8 * (kk & 3);
-            mma_ts(tmem + kOutCol + D, tmem + 128 + acol,
+            const uint32_t acol = kSep ? 8 * kk : 64 * (kk >> 2) + 8 * (kk & 3);
+            mma_ts(tmem + kOutCol + D, tmem + kDsCol + acol,
                    make_smem_desc(y0 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           }
         }
+        tc_commit(bar(OUT_READY));
         tc_commit(bar(Y_EMPTY + s));
+      };
+
+      // cursor over (unit, iteration); `nxt` runs one global iteration ahead of `cur`
+      bool ok = true;
+      int uc = 0;                       // units fetched so far
+      int cur_u = next_unit(uc, ok);
+      int cur_n = 0, cur_it = 0, cur_xb = 0;
+      if (ok && cur_u >= 0) {
+        cur_n = make_bwd_unit<MODE>(cur_u, p).n_iters;
+        cur_xb = uc % XBUF;
+        ok = mbar_wait(bar(X_FULL + cur_xb), (uc / XBUF) & 1, wctx, 32);
+        if (ok) ok = mbar_wait(bar(Y_FULL + 0), 0, wctx, 33);
+        if (ok) {
+          tc_fence_after();
+          issue_t(cur_xb, 0);
+        }
       }
-      if (ok) tc_commit(bar(OUT_FULL));
+      int g = 0;                        // global iteration of `cur`
+      while (ok && cur_u >= 0) {
+        // ---- locate the next global iteration
+        int nxt_u = cur_u, nxt_it = cur_it + 1, nxt_n = cur_n, nxt_xb = cur_xb;
+        bool crossed = false;
+        if (nxt_it == cur_n) {
+          ++uc;
+          nxt_u = next_unit(uc, ok);
+          if (!ok) break;
+          nxt_it = 0;
+          crossed = true;
+          if (nxt_u >= 0) {
+            nxt_n = make_bwd_unit<MODE>(nxt_u, p).n_iters;
+            nxt_xb = uc % XBUF;
+          }
+        }
+        const bool have_next = nxt_u >= 0;
+        auto issue_next_t = [&]() {
+          if (crossed) ok = mbar_wait(bar(X_FULL + nxt_xb), (uc / XBUF) & 1, wctx, 32);
+          if (ok) ok = mbar_wait(bar(Y_FULL + (g + 1) % STAGES), ((g + 1) / STAGES) & 1, wctx, 33);
+          if (ok && kSep) ok = mbar_wait(bar(T_CONSUMED), g & 1, wctx, 37);
+          if (ok) {
+            tc_fence_after();
+            issue_t(nxt_xb, g + 1);
+          }
+        };
+        // With a single stationary buffer the next unit's tiles can only be loaded once this
+        // unit's buffer has been released, i.e. after the output products below are issued.
+        const bool early = kSep && have_next && !(crossed && XBUF == 1);
+        if (early) issue_next_t();
+        if (!ok) break;
+        if (!(ok = mbar_wait(bar(PD_FULL), g & 1, wctx, 34))) break;
+        tc_fence_after();
+        issue_out(g, cur_it > 0 ? 1u : 0u);
+        if (cur_it + 1 == cur_n) tc_commit(bar(X_EMPTY + cur_xb));
+        if (!early && have_next) issue_next_t();
+        if (!ok) break;
+        cur_u = nxt_u;
+        cur_it = nxt_it;
+        cur_n = nxt_n;
+        cur_xb = nxt_xb;
+        ++g;
+      }
     }
   } else {
     // ================================= compute ===============================
     const int half = warp >> 2;                      // which 64 columns of the row
     const uint32_t lane_base = 32u * (warp & 3);
     const int row = 32 * (warp & 3) + lane;          // row of the stationary tile == TMEM lane
-    const int pos = tile * kTile + row;              // query position (dQ) or key position (dK/dV)
     const uint32_t t0 = tmem_addr(tmem, lane_base, 64 * half);
     const uint32_t t1 = tmem_addr(tmem, lane_base, 128 + 64 * half);
-
-    float lse2_row = INFINITY, delta_row = 0.f;
-    if (MODE == MODE_DQ && pos < p.T) {
-      const long long idx = (static_cast<long long>(b) * p.H + h) * p.T + pos;
-      lse2_row = p.lse[idx] * kLog2e;
-      delta_row = p.delta[idx];
-    }
+    const uint32_t p_dst = tmem_addr(tmem, lane_base, kSep ? kPCol + 32 * half : 64 * half);
+    const uint32_t ds_dst = tmem_addr(tmem, lane_base, kSep ? kDsCol + 32 * half : 128 + 64 * half);
+    const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
 
     bool ok = true;
-    for (int it = 0; it < n_iters; ++it) {
-      const int s = it % STAGES;
-      const int g = it / n_inner;
-      const int idx = streamed_index(it - g * n_inner);
-      ok = mbar_wait(bar(T_FULL), it & 1, wctx, 35);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-
-      uint32_t sv[2][32], dv[2][32];
-      tmem_ld32(t0, sv[0]);
-      tmem_ld32(t0 + 32, sv[1]);
-      tmem_ld32(t1, dv[0]);
-      tmem_ld32(t1 + 32, dv[1]);
-      tc_wait_ld();
-
-      const int qtile = MODE == MODE_DQ ? tile : idx;
-      const int kblock = MODE == MODE_DQ ? idx : tile;
-      const bool full = block_fully_visible(qtile, kblock, p.window, p.sinks);
-      const float* vec = reinterpret_cast<const float*>(gen + L::kVec + s * 1024);
-      const int c0 = 64 * half;                      // first column this thread owns
-      const int other0 = idx * kTile + c0;           // position of that column
-
-      uint32_t pp[32], dd[32];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float pv[2], ds[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int cc = 2 * c + e;
-          const float sc = __uint_as_float(sv[cc >> 5][cc & 31]);
-          const float dp = __uint_as_float(dv[cc >> 5][cc & 31]);
-          float l2, dl;
-          if (MODE == MODE_DQ) {
-            l2 = lse2_row;
-            dl = delta_row;
-          } else {
-            l2 = vec[c0 + cc];
-            dl = vec[128 + c0 + cc];
-          }
-          float pe = fast_exp2(fmaf(sc, p.scale_log2, -l2));
-          if (!full) {
-            const int qq = MODE == MODE_DQ ? pos : other0 + cc;
-            const int kk = MODE == MODE_DQ ? other0 + cc : pos;
-            if (!key_visible(qq, kk, p.window, p.sinks)) pe = 0.f;
-          }
-          pv[e] = pe;
-          ds[e] = pe * (dp - dl);
-        }
-        pp[c] = Pack2<T>::pack(pv[0], pv[1]);
-        dd[c] = Pack2<T>::pack(ds[0], ds[1]);
+    int g = 0;                    // global iteration
+    int out_waited = 0;           // OUT_READY phases this thread has observed
+    auto wait_out = [&](int needed) {
+      while (ok && out_waited < needed) {
+        ok = mbar_wait(bar(OUT_READY), out_waited & 1, wctx, 38);
+        ok = __all_sync(0xffffffffu, ok);
+        ++out_waited;
       }
-      if (MODE == MODE_DKV) tmem_st32(t0, pp);
-      tmem_st32(t1, dd);
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar(PD_FULL));
-    }
-
-    if (ok) {
-      ok = mbar_wait(bar(OUT_FULL), 0, wctx, 36);
+    };
+    for (int uc = 0; ok; ++uc) {
+      const int u = next_unit(uc, ok);
       ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
+      if (!ok || u < 0) break;
+      const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
+      const int pos = w.tile * kTile + row;            // query position (dQ) or key position (dK/dV)
+
+      uint64_t negl2_row = pack_f2(-INFINITY, -INFINITY), negd_row = 0ull;
+      if (MODE == MODE_DQ && pos < p.T) {
+        const long long idx = (static_cast<long long>(w.b) * p.H + w.h) * p.T + pos;
+        const float l2 = -p.lse[idx] * kLog2e, dl = -p.delta[idx];
+        negl2_row = pack_f2(l2, l2);
+        negd_row = pack_f2(dl, dl);
+      }
+
+      for (int it = 0; it < w.n_iters; ++it, ++g) {
+        const int s = g % STAGES;
+        const int gg = it / w.n_inner;
+        const int idx = w.streamed_index(it - gg * w.n_inner);
+        ok = mbar_wait(bar(T_FULL), g & 1, wctx, 35);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+
+        uint32_t sv[2][32], dv[2][32];
+        tmem_ld32(t0, sv[0]);
+        tmem_ld32(t0 + 32, sv[1]);
+        tmem_ld32(t1, dv[0]);
+        tmem_ld32(t1 + 32, dv[1]);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar(T_CONSUMED));
+
+        const int qtile = MODE == MODE_DQ ? w.tile : idx;
+        const int kblock = MODE == MODE_DQ ? idx : w.tile;
+        const bool full = block_fully_visible(qtile, kblock, p.window, p.sinks);
+        const ulonglong2* vec2 =
+            reinterpret_cast<const ulonglong2*>(gen + L::kVec + s * 1024) + 16 * half;
+        const int other0 = idx * kTile + 64 * half;      // position of this thread's first column
+
+        uint32_t pp[32], dd[32];
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {                // four columns (two packed pairs) per step
+          uint64_t nl_a, nl_b, nd_a, nd_b;
+          if (MODE == MODE_DQ) {
+            nl_a = nl_b = negl2_row;
+            nd_a = nd_b = negd_row;
+          } else {
+            const ulonglong2 nl = vec2[c4];              // -lse2 of columns 4 c4 .. 4 c4 + 3
+            const ulonglong2 nd = vec2[32 + c4];         // -delta
+            nl_a = nl.x; nl_b = nl.y; nd_a = nd.x; nd_b = nd.y;
+          }
+          const int c = 4 * c4;
+          const uint64_t xa = ffma2(pack_f2(__uint_as_float(sv[c >> 5][c & 31]),
+                                            __uint_as_float(sv[c >> 5][(c & 31) + 1])), scale2, nl_a);
+          const uint64_t xb = ffma2(pack_f2(__uint_as_float(sv[c >> 5][(c & 31) + 2]),
+                                            __uint_as_float(sv[c >> 5][(c & 31) + 3])), scale2, nl_b);
+          float p0, p1, p2, p3;
+          unpack_f2(xa, p0, p1);
+          unpack_f2(xb, p2, p3);
+          p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
+          if (!full) {
+            const int o = other0 + c;
+            if (MODE == MODE_DQ) {
+              if (!key_visible(pos, o + 0, p.window, p.sinks)) p0 = 0.f;
+              if (!key_visible(pos, o + 1, p.window, p.sinks)) p1 = 0.f;
+              if (!key_visible(pos, o + 2, p.window, p.sinks)) p2 = 0.f;
+              if (!key_visible(pos, o + 3, p.window, p.sinks)) p3 = 0.f;
+            } else {
+              if (!key_visible(o + 0, pos, p.window, p.sinks)) p0 = 0.f;
+              if (!key_visible(o + 1, pos, p.window, p.sinks)) p1 = 0.f;
+              if (!key_visible(o + 2, pos, p.window, p.sinks)) p2 = 0.f;
+              if (!key_visible(o + 3, pos, p.window, p.sinks)) p3 = 0.f;
+            }
+          }
+          const uint64_t pa = pack_f2(p0, p1), pb = pack_f2(p2, p3);
+          const uint64_t da = fmul2(pa, fadd2(pack_f2(__uint_as_float(dv[c >> 5][c & 31]),
+                                                      __uint_as_float(dv[c >> 5][(c & 31) + 1])), nd_a));
+          const uint64_t db = fmul2(pb, fadd2(pack_f2(__uint_as_float(dv[c >> 5][(c & 31) + 2]),
+                                                      __uint_as_float(dv[c >> 5][(c & 31) + 3])), nd_b));
+          float d0, d1, d2, d3;
+          unpack_f2(da, d0, d1);
+          unpack_f2(db, d2, d3);
+          pp[2 * c4] = Pack2<T>::pack(p0, p1);
+          pp[2 * c4 + 1] = Pack2<T>::pack(p2, p3);
+          dd[2 * c4] = Pack2<T>::pack(d0, d1);
+          dd[2 * c4 + 1] = Pack2<T>::pack(d2, d3);
+        }
+        // the previous iteration's output products must be done reading P / dS
+        wait_out(g);
+        if (!ok) break;
+        if (MODE == MODE_DKV) tmem_st32(p_dst, pp);
+        tmem_st32(ds_dst, dd);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar(PD_FULL));
+      }
+      if (!ok) break;
+
+      wait_out(g);                 // this unit's last output product
+      if (!ok) break;
       tc_fence_after();
       if (MODE == MODE_DQ) {
         // each half stores D/2 columns of its dQ row
         T* orow = static_cast<T*>(p.out0) +
-                  ((static_cast<long long>(b) * p.T + pos) * p.H + h) * static_cast<long long>(D) +
+                  ((static_cast<long long>(w.b) * p.T + pos) * p.H + w.h) * static_cast<long long>(D) +
                   half * (D / 2);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
@@ -343,12 +509,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (pos < p.T) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * p.scale, __uint_as_float(r[8 * i + 1]) * p.scale);
-              w.y = Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * p.scale, __uint_as_float(r[8 * i + 3]) * p.scale);
-              w.z = Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * p.scale, __uint_as_float(r[8 * i + 5]) * p.scale);
-              w.w = Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * p.scale, __uint_as_float(r[8 * i + 7]) * p.scale);
-              *reinterpret_cast<uint4*>(orow + 32 * c + 8 * i) = w;
+              uint4 v4;
+              v4.x = Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * p.scale, __uint_as_float(r[8 * i + 1]) * p.scale);
+              v4.y = Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * p.scale, __uint_as_float(r[8 * i + 3]) * p.scale);
+              v4.z = Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * p.scale, __uint_as_float(r[8 * i + 5]) * p.scale);
+              v4.w = Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * p.scale, __uint_as_float(r[8 * i + 7]) * p.scale);
+              *reinterpret_cast<uint4*>(orow + 32 * c + 8 * i) = v4;
             }
           }
         }
@@ -356,7 +522,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // half 0 stores the dV row, half 1 the dK row (scaled)
         const float mul = half == 0 ? 1.f : p.scale;
         T* orow = static_cast<T*>(half == 0 ? p.out1 : p.out0) +
-                  ((static_cast<long long>(b) * p.T + pos) * p.Hkv + hk) * static_cast<long long>(D);
+                  ((static_cast<long long>(w.b) * p.T + pos) * p.Hkv + w.hk) * static_cast<long long>(D);
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
@@ -365,16 +531,19 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (pos < p.T) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * mul, __uint_as_float(r[8 * i + 1]) * mul);
-              w.y = Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * mul, __uint_as_float(r[8 * i + 3]) * mul);
-              w.z = Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * mul, __uint_as_float(r[8 * i + 5]) * mul);
-              w.w = Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * mul, __uint_as_float(r[8 * i + 7]) * mul);
-              *reinterpret_cast<uint4*>(orow + 32 * c + 8 * i) = w;
+              uint4 v4;
+              v4.x = Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * mul, __uint_as_float(r[8 * i + 1]) * mul);
+              v4.y = Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * mul, __uint_as_float(r[8 * i + 3]) * mul);
+              v4.z = Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * mul, __uint_as_float(r[8 * i + 5]) * mul);
+              v4.w = Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * mul, __uint_as_float(r[8 * i + 7]) * mul);
+              *reinterpret_cast<uint4*>(orow + 32 * c + 8 * i) = v4;
             }
           }
         }
       }
+      // the next unit's first output product overwrites these columns; it is issued
+      // only after this thread's next PD arrival, which follows in program order
+      tc_fence_before();
     }
   }
 
@@ -385,15 +554,53 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+  // scheduler bookkeeping: the last CTA of the launch to get here re-arms the counters
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned done = atomicAdd(&p.sched[1], 1u);
+    if (done == gridDim.x - 1) {
+      p.sched[0] = 0u;
+      p.sched[1] = 0u;
+      __threadfence();
+    }
+  }
 }
 
-template <typename T, int D, int MODE, int STAGES>
+int sm_count_bwd() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Device address of a fresh pair of scheduler counters on the current device.
+unsigned* sched_slot() {
+  static unsigned* base[64];
+  static unsigned next_slot = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_bwd_sched) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<unsigned*>(ptr);
+  }
+  const unsigned slot = (next_slot++) % kSchedSlots;
+  return base[dev] + 2 * slot;
+}
+
+template <typename T, int D, int MODE, int STAGES, int XBUF>
 int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
                 const CUtensorMap& mv, const CUtensorMap& mdo, const float* lse,
                 const float* delta, void* out0, void* out1, unsigned* status,
                 cudaStream_t stream) {
-  using L = BwdSmem<D, STAGES>;
-  auto kern = bwd_tc_kernel<T, D, MODE, STAGES>;
+  using L = BwdSmem<D, STAGES, XBUF>;
+  auto kern = bwd_tc_kernel<T, D, MODE, STAGES, XBUF>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
       cudaSuccess)
     return NLFA_ERR_CUDA;
@@ -404,6 +611,8 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
   bp.window = p.window;
   bp.sinks = p.sinks;
   bp.n_tiles = (p.T + kTile - 1) / kTile;
+  bp.BH = p.B * (MODE == MODE_DQ ? p.H : p.Hkv);
+  bp.total_units = bp.n_tiles * bp.BH;
   bp.scale = p.scale;
   bp.scale_log2 = p.scale * kLog2e;
   bp.lse = lse;
@@ -411,22 +620,24 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
   bp.out0 = out0;
   bp.out1 = out1;
   bp.status = status;
-  dim3 grid(bp.n_tiles, p.B * (MODE == MODE_DQ ? p.H : p.Hkv));
+  bp.sched = sched_slot();
+  if (bp.sched == nullptr) return NLFA_ERR_CUDA;
+  const int grid = bp.total_units < sm_count_bwd() ? bp.total_units : sm_count_bwd();
   kern<<<grid, 320, L::kDynamic, stream>>>(mq, mk, mv, mdo, bp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
-template <typename T, int D, int STAGES>
+template <typename T, int D, int STAGES, int XBUF>
 int launch_both(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
                 const CUtensorMap& mv, const CUtensorMap& mdo, const float* lse,
                 const float* delta, void* dq, void* dk, void* dv, int passes, unsigned* status,
                 cudaStream_t stream) {
   int st = NLFA_OK;
   if (passes & NLFA_PASS_DKV)
-    st = launch_mode<T, D, MODE_DKV, STAGES>(p, mq, mk, mv, mdo, lse, delta, dk, dv, status, stream);
+    st = launch_mode<T, D, MODE_DKV, STAGES, XBUF>(p, mq, mk, mv, mdo, lse, delta, dk, dv, status, stream);
   if (st != NLFA_OK) return st;
   if (passes & NLFA_PASS_DQ)
-    st = launch_mode<T, D, MODE_DQ, STAGES>(p, mq, mk, mv, mdo, lse, delta, dq, nullptr, status, stream);
+    st = launch_mode<T, D, MODE_DQ, STAGES, XBUF>(p, mq, mk, mv, mdo, lse, delta, dq, nullptr, status, stream);
   return st;
 }
 
@@ -448,11 +659,11 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D == 64) {
-    return bf16 ? launch_both<__nv_bfloat16, 64, 3>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
-                : launch_both<__half, 64, 3>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
+    return bf16 ? launch_both<__nv_bfloat16, 64, 3, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
+                : launch_both<__half, 64, 3, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
   }
-  return bf16 ? launch_both<__nv_bfloat16, 128, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
-              : launch_both<__half, 128, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
+  return bf16 ? launch_both<__nv_bfloat16, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
+              : launch_both<__half, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
 }
 
 }  // namespace nlfa
