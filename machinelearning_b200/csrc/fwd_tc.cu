@@ -1,20 +1,22 @@
 // Tensor-core forward for sm_100a: S = Q K^T and O += P V on tcgen05 with the
 // accumulators in TMEM, tiles brought in by TMA, online softmax in registers.
 //
-// Persistent kernel: one CTA per SM walks a static, heavy-first list of work
-// units.  A unit is NT consecutive 128-row query tiles of one (batch, head); the
-// CTA visits the key blocks those tiles can see.  Warp roles:
+// Persistent kernel: one CTA per SM takes work units from a global counter,
+// heaviest first.  A unit is NT consecutive 128-row query tiles of one (batch,
+// head); the CTA visits the key blocks those tiles can see.  Warp roles:
 //   warps [0, 4 NT)   softmax: warpgroup t owns query tile t, one thread per row
-//   warp  4 NT        TMA producer (one lane): Q per unit, a ring of K and V stages
+//   warp  4 NT        scheduler + TMA producer (one lane): Q per unit, K / V ring
 //   warp  4 NT + 1    MMA issuer (one lane) and owner of the TMEM allocation
 // Hand-offs are mbarriers whose phases run on across units: Q full/empty per Q
-// buffer, K/V full/empty per stage, S ready, P ready, O ready per tile.  While the
-// softmax warps finish a unit (normalise and store O) the producer and the MMA
-// issuer are already on the next one.
+// buffer, K/V full/empty per stage, and per tile S ready, S consumed, P ready, O
+// ready.  While the softmax warps finish a unit (normalise and store O) the
+// producer and the MMA issuer are already on the next one.
 //
-// TMEM columns: S_t at 128 t (fp32, 128 columns; P_t, 16-bit, overwrites its
-// first 64 columns and is read back as the A operand of the PV product);
-// O_t at 128 NT + D t.
+// TMEM columns: S_t at 128 t (fp32, 128 columns), O_t at 128 NT + D t.  P_t (16
+// bit, the A operand of the PV product) has its own 64 columns after the O tiles
+// when they fit (D = 64); the next S product is then issued as soon as the softmax
+// warps have pulled S into registers, so the tensor pipe runs under the
+// exponentials.  Otherwise (D = 128) P_t overwrites the first 64 columns of S_t.
 //
 // Computes what nanolab/csrc/flash_attn_cuda.cu:583-797 computes (softmax in
 // base 2, L = m ln2 + log l at :279), with the sliding-window mask of
@@ -25,22 +27,26 @@
 namespace nlfa {
 
 #ifdef NLFA_TRACE
-// Debug-only timeline of CTA 0: (clock64, tag) pairs per role.
+// Debug-only timeline of CTA 0: (clock64, tag) pairs per role, staged in shared memory.
 __device__ long long g_trace[4][1024];
 __device__ int g_trace_n[4];
 #define NLFA_TRACE_EVENT(role, tag)                                   \
   do {                                                                \
-    if (blockIdx.x == 0) {                                            \
-      const int i_ = g_trace_n[role]++;                               \
-      if (i_ < 512) {                                                 \
-        g_trace[role][2 * i_] = clock64();                            \
-        g_trace[role][2 * i_ + 1] = (tag);                            \
-      }                                                               \
+    if (blockIdx.x == 0 && tr_n < 512) {                              \
+      tr_buf[((role) * 512 + tr_n) * 2] = clock64();                  \
+      tr_buf[((role) * 512 + tr_n) * 2 + 1] = (tag);                  \
+      ++tr_n;                                                         \
+      g_trace_n[role] = tr_n;                                         \
     }                                                                 \
   } while (0)
 #else
 #define NLFA_TRACE_EVENT(role, tag)
 #endif
+
+// Work counters for the in-kernel scheduler: [slot][0] next unit, [slot][1] CTAs
+// finished.  The last CTA of a launch to finish zeroes its slot again.
+constexpr int kFwdSchedSlots = 256;
+__device__ unsigned g_fwd_sched[kFwdSchedSlots][2];
 
 namespace {
 
@@ -54,6 +60,7 @@ struct FwdParams {
   void* o;
   float* lse;
   unsigned* status;
+  unsigned* sched;        // this launch's two counters
 };
 
 template <int D, int NT, int STAGES, int QBUF>
@@ -63,13 +70,20 @@ struct FwdSmem {
   static constexpr int kK = kQ + QBUF * NT * kTileBytes;
   static constexpr int kV = kK + STAGES * kTileBytes;
   static constexpr int kBar = kV + STAGES * kTileBytes;
-  // barriers (8 bytes each): q_full[QBUF], q_empty[QBUF], s_full[NT], p_full[NT], o_full[NT],
-  // k_full[S], k_empty[S], v_full[S], v_empty[S]
-  static constexpr int kNumBars = 2 * QBUF + 3 * NT + 4 * STAGES;
-  static constexpr int kTmemSlot = kBar + 8 * kNumBars;
+  // barriers (8 bytes each): q_full[QBUF], q_empty[QBUF], s_full[NT], s_consumed[NT],
+  // p_full[NT], o_ready[NT], k_full[S], k_empty[S], v_full[S], v_empty[S], sched_full[kRing]
+  static constexpr int kRing = 8;
+  static constexpr int kNumBars = 2 * QBUF + 4 * NT + 4 * STAGES + kRing;
+  static constexpr int kSched = kBar + 8 * kNumBars;        // ring of unit indices
+  static constexpr int kTmemSlot = kSched + 4 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
+#ifdef NLFA_TRACE
+  static constexpr int kTrace = (kTotal + 15) / 16 * 16;
+  static constexpr int kDynamic = kTrace + 4 * 512 * 16 + 1024;
+#else
   static constexpr int kDynamic = kTotal + 1024;            // slack for 1024-byte alignment
+#endif
 };
 
 __device__ __forceinline__ bool tile_sees_block(const TileRange& r, int j) {
@@ -132,6 +146,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr int kBoxBytes = kTile * 128;         // 128 rows x 128 bytes
   constexpr uint32_t kTmemCols = (NT * (128 + D) <= 256) ? 256u : 512u;
   constexpr bool kBf16 = Pack2<T>::kIsBf16;
+  constexpr bool kSepP = NT * (128 + D + 64) <= 512;      // P has columns of its own
+  constexpr uint32_t kPBase = NT * (128 + D);
+  constexpr int kRing = L::kRing;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -140,11 +157,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef NLFA_TRACE
+  long long* tr_buf = reinterpret_cast<long long*>(gen + L::kTrace);
+  int tr_n = 0;
+#endif
 
   auto bar = [&](int i) -> uint32_t { return base + L::kBar + 8u * i; };
-  constexpr int Q_FULL = 0, Q_EMPTY = QBUF, S_FULL = 2 * QBUF, P_FULL = S_FULL + NT,
-                O_FULL = P_FULL + NT, K_FULL = O_FULL + NT, K_EMPTY = K_FULL + STAGES,
-                V_FULL = K_EMPTY + STAGES, V_EMPTY = V_FULL + STAGES;
+  constexpr int Q_FULL = 0, Q_EMPTY = QBUF, S_FULL = 2 * QBUF, S_CONSUMED = S_FULL + NT,
+                P_FULL = S_CONSUMED + NT, O_READY = P_FULL + NT, K_FULL = O_READY + NT,
+                K_EMPTY = K_FULL + STAGES, V_FULL = K_EMPTY + STAGES, V_EMPTY = V_FULL + STAGES,
+                SCHED_FULL = V_EMPTY + STAGES;
+  volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
   const WaitCtx wctx{abort_flag, p.status};
@@ -160,9 +183,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar(S_FULL + t), 1);
+      mbar_init(bar(S_CONSUMED + t), 128);
       mbar_init(bar(P_FULL + t), 128);
-      mbar_init(bar(O_FULL + t), 1);
+      mbar_init(bar(O_READY + t), 1);
     }
+    for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(K_FULL + s), 1);
       mbar_init(bar(K_EMPTY + s), 1);
@@ -181,6 +206,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tmem = *tmem_slot;
   const bool dead = *abort_flag != 0;
 
+  // Every role reads the index of its uc-th unit from the ring the producer fills;
+  // a negative index means there is no more work.
+  auto next_unit = [&](int uc, bool& ok) -> int {
+    ok = mbar_wait(bar(SCHED_FULL + (uc % kRing)), (uc / kRing) & 1, wctx, 11);
+    return ok ? sched_ring[uc % kRing] : -1;
+  };
+
   if (dead) {
     // fall through to the tail
   } else if (warp == 4 * NT) {
@@ -189,9 +221,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      int git = 0, uc = 0;
+      int git = 0;
       bool ok = true;
-      for (int u = blockIdx.x; ok && u < p.total_units; u += gridDim.x, ++uc) {
+      for (int uc = 0; ok; ++uc) {
+        int u = static_cast<int>(atomicAdd(&p.sched[0], 1u));
+        if (u >= p.total_units) u = -1;
+        sched_ring[uc % kRing] = u;
+        mbar_arrive(bar(SCHED_FULL + (uc % kRing)));
+        if (u < 0) break;
         const Unit<NT> w = make_unit<NT>(u, p, BH);
         const int qb = uc % QBUF;
         const uint32_t qph = (uc / QBUF) & 1;
@@ -239,20 +276,34 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       };
       auto issue_pv = [&](int t, int s, bool accumulate) {
         const uint32_t va = base + L::kV + s * L::kTileBytes;
+        const uint32_t pa = kSepP ? kPBase + 64 * t : 128 * t;
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
           // 16 keys per step: 8 packed TMEM columns of P, 16 rows (2048 bytes) of V
-          mma_ts(tmem + 128 * NT + D * t, tmem + 128 * t + 8 * kk,
+          mma_ts(tmem + 128 * NT + D * t, tmem + pa + 8 * kk,
                  make_smem_desc(va + kk * 2048, kBoxBytes, 1024), idesc_pv,
                  (accumulate || kk > 0) ? 1u : 0u);
         }
       };
 
       bool ok = true;
-      int git = 0, uc = 0;
-      int p_count[NT];
-      for (int t = 0; t < NT; ++t) p_count[t] = 0;
-      for (int u = blockIdx.x; ok && u < p.total_units; u += gridDim.x, ++uc) {
+      int git = 0;
+      int p_count[NT], s_issued[NT];
+      for (int t = 0; t < NT; ++t) p_count[t] = s_issued[t] = 0;
+      // S_t may be overwritten once the softmax warps have pulled the previous one into
+      // registers (only needed when P has its own columns; otherwise the P hand-off implies it)
+      auto start_s = [&](int qb, int t, int s) {
+        if (kSepP && s_issued[t] > 0)
+          ok = mbar_wait(bar(S_CONSUMED + t), (s_issued[t] - 1) & 1, wctx, 12);
+        if (!ok) return;
+        tc_fence_after();
+        issue_s(qb, t, s);
+        tc_commit(bar(S_FULL + t));
+        ++s_issued[t];
+      };
+      for (int uc = 0; ok; ++uc) {
+        const int u = next_unit(uc, ok);
+        if (!ok || u < 0) break;
         const Unit<NT> w = make_unit<NT>(u, p, BH);
         const int qb = uc % QBUF;
         NLFA_TRACE_EVENT(2, 1);
@@ -261,13 +312,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         {
           const int s0 = git % STAGES;
           if (!(ok = mbar_wait(bar(K_FULL + s0), (git / STAGES) & 1, wctx, 4))) break;
-          tc_fence_after();
           const int j0 = w.block_at(0);
-          for (int t = 0; t < NT; ++t)
-            if (w.sees(t, j0)) {
-              issue_s(qb, t, s0);
-              tc_commit(bar(S_FULL + t));
-            }
+          for (int t = 0; ok && t < NT; ++t)
+            if (w.sees(t, j0)) start_s(qb, t, s0);
+          if (!ok) break;
           tc_commit(bar(K_EMPTY + s0));
           NLFA_TRACE_EVENT(2, 3);
         }
@@ -281,8 +329,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const int s1 = (git + 1) % STAGES;
           const uint32_t ph1 = ((git + 1) / STAGES) & 1;
           const int j1 = have_next ? w.block_at(it + 1) : 0;
-          if (!(ok = mbar_wait(bar(V_FULL + s), ph, wctx, 5))) break;
           if (have_next && !(ok = mbar_wait(bar(K_FULL + s1), ph1, wctx, 6))) break;
+          if (kSepP && have_next) {
+            // next S products first: they only wait for the softmax warps' loads of S
+            for (int t = 0; ok && t < NT; ++t)
+              if (w.sees(t, j1)) start_s(qb, t, s1);
+            if (!ok) break;
+            tc_commit(bar(K_EMPTY + s1));
+          }
+          if (!(ok = mbar_wait(bar(V_FULL + s), ph, wctx, 5))) break;
           for (int t = 0; t < NT; ++t) {
             if (w.sees(t, j)) {
               NLFA_TRACE_EVENT(2, 10 + t);
@@ -291,22 +346,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               ++p_count[t];
               tc_fence_after();
               issue_pv(t, s, o_started[t]);
+              tc_commit(bar(O_READY + t));
               o_started[t] = true;
             }
-            if (have_next && w.sees(t, j1)) {
-              tc_fence_after();
-              issue_s(qb, t, s1);
-              tc_commit(bar(S_FULL + t));
-            }
+            if (!kSepP && have_next && w.sees(t, j1)) start_s(qb, t, s1);
           }
           if (!ok) break;
           tc_commit(bar(V_EMPTY + s));
-          if (have_next) tc_commit(bar(K_EMPTY + s1));
+          if (!kSepP && have_next) tc_commit(bar(K_EMPTY + s1));
         }
         if (!ok) break;
         tc_commit(bar(Q_EMPTY + qb));
-        for (int t = 0; t < NT; ++t)
-          if (w.valid[t]) tc_commit(bar(O_FULL + t));
       }
     }
   } else {
@@ -316,15 +366,25 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t lane_base = 32u * (warp & 3);
     const uint32_t s_addr = tmem_addr(tmem, lane_base, 128 * t);
     const uint32_t o_addr = tmem_addr(tmem, lane_base, 128 * NT + D * t);
+    const uint32_t p_addr = tmem_addr(tmem, lane_base, kSepP ? kPBase + 64 * t : 128 * t);
     const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
-    int s_count = 0, o_count = 0;
+    int s_count = 0, o_count = 0;      // S_FULL / O_READY phases this thread has observed
     bool ok = true;
-    for (int u = blockIdx.x; ok && u < p.total_units; u += gridDim.x) {
+    for (int uc = 0; ok; ++uc) {
+      const int u = next_unit(uc, ok);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok || u < 0) break;
       const Unit<NT> w = make_unit<NT>(u, p, BH);
       if (!w.valid[t]) continue;
       const int tile = w.tile0 + t;
       const int qpos = tile * kTile + row;
-      float m_ref = -INFINITY, l = 0.f;          // m_ref is in scaled (base-2) units
+      // Online softmax in base 2.  m_ref is the reference exponent (scaled units): P =
+      // 2^(x - m_ref).  It starts at the first block's row maximum and is afterwards only
+      // raised when a later block's maximum exceeds it by more than 2^8; the rescale of O and
+      // l that goes with a raise is applied at the start of the following block, after that
+      // block's PV product has landed (pend_alpha, pend_m).
+      float m_ref = -INFINITY, l = 0.f;
+      float pend_alpha = 1.f, pend_m = 0.f;
       bool first = true;
       for (int it = 0; it < w.n_iters; ++it) {
         const int j = w.block_at(it);
@@ -337,94 +397,142 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         if (row == 0) NLFA_TRACE_EVENT(t, 2);
 
-        float sv[128];
-        {
-          uint32_t sr[4][32];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, sr[c]);
-          tc_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 128; ++c) sv[c] = __uint_as_float(sr[c >> 5][c & 31]);
+        const bool masked = !block_fully_visible(tile, j, p.window, p.sinks);
+        const int k0 = j * kTile;
+        const bool rescale_pending = __any_sync(0xffffffffu, pend_alpha != 1.f);
+        if (pend_alpha != 1.f) {
+          l *= pend_alpha;
+          m_ref = pend_m;
         }
-        if (!block_fully_visible(tile, j, p.window, p.sinks)) {
-          const int k0 = j * kTile;
-#pragma unroll
-          for (int c = 0; c < 128; ++c)
-            if (!key_visible(qpos, k0 + c, p.window, p.sinks)) sv[c] = -INFINITY;
-        }
-        // row maximum of the raw scores: four independent chains of 3-input max
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < 128; c += 8) {
-          m0 = fmax3(m0, sv[c + 0], sv[c + 1]);
-          m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
-          m2 = fmax3(m2, sv[c + 4], sv[c + 5]);
-          m3 = fmax3(m3, sv[c + 6], sv[c + 7]);
-        }
-        const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2;
-        if (row == 0) NLFA_TRACE_EVENT(t, 3);
 
-        // Reference maximum for the exponent.  It is only moved (and O and l
-        // rescaled) when the row maximum has grown by more than 2^8, which keeps
-        // P within 16-bit range and makes the TMEM round trip of O rare.
-        float alpha = 1.f;
-        bool rescale = false;
-        if (first) {
-          m_ref = mx;
-        } else if (mx > m_ref + 8.f) {
-          alpha = fast_exp2(m_ref - mx);     // m_ref == -inf gives 0
-          m_ref = mx;
-          rescale = true;
-        }
-        if (!first && __any_sync(0xffffffffu, rescale)) {
-          l *= alpha;
+        // S is streamed out of TMEM 32 columns at a time (two buffers: the next chunk's load
+        // is in flight while this one is processed), so a row never sits in registers whole.
+        uint32_t buf[2][32];
+        auto mask_chunk = [&](uint32_t (&r)[32], int c) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t orr[32];
-            tmem_ld32(o_addr + 32 * c, orr);
+          for (int i = 0; i < 32; ++i)
+            if (!key_visible(qpos, k0 + 32 * c + i, p.window, p.sinks))
+              r[i] = __float_as_uint(-INFINITY);
+        };
+
+        // The first block of a row (and every block when P shares S's columns, where a second
+        // look at S is impossible once P is being written) gets a separate maximum pass.
+        if (first || !kSepP) {
+          float b0 = -INFINITY, b1 = -INFINITY;
+          tmem_ld32(s_addr, buf[0]);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
             tc_wait_ld();
+            if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), buf[(c + 1) & 1]);
+            uint32_t (&r)[32] = buf[c & 1];
+            if (masked) mask_chunk(r, c);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-            tmem_st32(o_addr + 32 * c, orr);
+            for (int i = 0; i < 32; i += 4) {
+              b0 = fmax3(b0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+              b1 = fmax3(b1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+            }
+          }
+          const float mx = fmaxf(b0, b1) * p.scale_log2;
+          if (first) {
+            m_ref = mx;
+          } else if (mx > m_ref + 8.f) {
+            // raise the reference now: O holds every earlier block (their PV products are
+            // waited for below, before O is touched)
+            pend_alpha *= fast_exp2(m_ref - mx);
+            l *= fast_exp2(m_ref - mx);
+            m_ref = mx;
           }
         }
-        first = false;
-        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        const uint64_t negm2 = pack_f2(-m_use, -m_use);
-        uint64_t acc0 = 0ull, acc1 = 0ull, acc2 = 0ull, acc3 = 0ull;   // packed (0.f, 0.f)
-        uint32_t pk[2][32];
+        if (row == 0) NLFA_TRACE_EVENT(t, 3);
+
+        bool o_synced = first;          // no earlier PV product in this unit to wait for
+        float bmax = -INFINITY;
+        float sum = 0.f;
+        for (int attempt = 0; attempt < 2; ++attempt) {
+          const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+          const uint64_t negm2 = pack_f2(-m_use, -m_use);
+          uint64_t acc0 = 0ull, acc1 = 0ull;            // packed (0.f, 0.f)
+          float b0 = -INFINITY, b1 = -INFINITY;
+          tmem_ld32(s_addr, buf[0]);
 #pragma unroll
-        for (int c = 0; c < 64; c += 4) {
-          uint64_t x0 = ffma2(pack_f2(sv[2 * c + 0], sv[2 * c + 1]), scale2, negm2);
-          uint64_t x1 = ffma2(pack_f2(sv[2 * c + 2], sv[2 * c + 3]), scale2, negm2);
-          uint64_t x2 = ffma2(pack_f2(sv[2 * c + 4], sv[2 * c + 5]), scale2, negm2);
-          uint64_t x3 = ffma2(pack_f2(sv[2 * c + 6], sv[2 * c + 7]), scale2, negm2);
-          float a0, a1, b0, b1, c0, c1, d0, d1;
-          unpack_f2(x0, a0, a1);
-          unpack_f2(x1, b0, b1);
-          unpack_f2(x2, c0, c1);
-          unpack_f2(x3, d0, d1);
-          a0 = fast_exp2(a0); a1 = fast_exp2(a1);
-          b0 = fast_exp2(b0); b1 = fast_exp2(b1);
-          c0 = fast_exp2(c0); c1 = fast_exp2(c1);
-          d0 = fast_exp2(d0); d1 = fast_exp2(d1);
-          acc0 = fadd2(acc0, pack_f2(a0, a1));
-          acc1 = fadd2(acc1, pack_f2(b0, b1));
-          acc2 = fadd2(acc2, pack_f2(c0, c1));
-          acc3 = fadd2(acc3, pack_f2(d0, d1));
-          pk[c >> 5][(c & 31) + 0] = Pack2<T>::pack(a0, a1);
-          pk[c >> 5][(c & 31) + 1] = Pack2<T>::pack(b0, b1);
-          pk[c >> 5][(c & 31) + 2] = Pack2<T>::pack(c0, c1);
-          pk[c >> 5][(c & 31) + 3] = Pack2<T>::pack(d0, d1);
-        }
-        {
+          for (int c = 0; c < 4; ++c) {
+            tc_wait_ld();
+            if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), buf[(c + 1) & 1]);
+            uint32_t (&r)[32] = buf[c & 1];
+            if (masked) mask_chunk(r, c);
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
+              const float s2 = __uint_as_float(r[i + 2]), s3 = __uint_as_float(r[i + 3]);
+              b0 = fmax3(b0, s0, s1);
+              b1 = fmax3(b1, s2, s3);
+              float e0, e1, e2, e3;
+              unpack_f2(ffma2(pack_f2(s0, s1), scale2, negm2), e0, e1);
+              unpack_f2(ffma2(pack_f2(s2, s3), scale2, negm2), e2, e3);
+              e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
+              acc0 = fadd2(acc0, pack_f2(e0, e1));
+              acc1 = fadd2(acc1, pack_f2(e2, e3));
+              pk[i / 2] = Pack2<T>::pack(e0, e1);
+              pk[i / 2 + 1] = Pack2<T>::pack(e2, e3);
+            }
+            if (!o_synced) {
+              // before the first write of P (and before O is rescaled): the previous block's
+              // PV product must be complete; every O_READY phase is observed once, in order
+              ok = mbar_wait(bar(O_READY + t), o_count & 1, wctx, 13);
+              ok = __all_sync(0xffffffffu, ok);
+              ++o_count;
+              o_synced = true;
+              tc_fence_after();
+            }
+            tmem_st16(p_addr + 16 * c, pk);
+          }
+          if (!ok) break;
+          bmax = fmaxf(b0, b1) * p.scale_log2;
           float lo, hi;
-          unpack_f2(fadd2(fadd2(acc0, acc1), fadd2(acc2, acc3)), lo, hi);
-          l += lo + hi;
+          unpack_f2(fadd2(acc0, acc1), lo, hi);
+          sum = lo + hi;
+          // Fast path: P was formed against a reference that may lag this block's maximum.
+          // That is fine up to a point (bf16/f16 P and the fp32 sum have the range); beyond
+          // 2^12 (f16 tops out at 2^16) the block is redone against its own maximum.  Only
+          // possible when P has its own columns, so S is still intact.
+          const bool redo = kSepP && (bmax > m_ref + 12.f);
+          if (!__any_sync(0xffffffffu, redo)) break;
+          if (bmax > m_ref + 8.f) {
+            const float a = fast_exp2(m_ref - bmax);      // m_ref == -inf gives 0
+            pend_alpha *= a;
+            l *= a;
+            m_ref = bmax;
+          }
         }
+        if (!ok) break;
+        tc_fence_before();
+        mbar_arrive(bar(S_CONSUMED + t));          // S_t may be overwritten from here on
+        l += sum;
+
+        // rescale of O decided earlier (rare): all PV products so far are complete
+        if (rescale_pending || __any_sync(0xffffffffu, pend_alpha != 1.f)) {
+          if (!first) {
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld32(o_addr + 32 * c, orr);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                orr[i] = __float_as_uint(__uint_as_float(orr[i]) * pend_alpha);
+              tmem_st32(o_addr + 32 * c, orr);
+            }
+          }
+          pend_alpha = 1.f;
+        }
+        // this block's maximum moves the reference for the blocks after it
+        if (bmax > m_ref + 8.f) {
+          pend_alpha = fast_exp2(m_ref - bmax);
+          pend_m = bmax;
+        }
+        first = false;
         if (row == 0) NLFA_TRACE_EVENT(t, 4);
-        tmem_st32(s_addr, pk[0]);
-        tmem_st32(s_addr + 32, pk[1]);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(P_FULL + t));
@@ -433,7 +541,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok) break;
       if (row == 0) NLFA_TRACE_EVENT(t, 6);
 
-      ok = mbar_wait(bar(O_FULL + t), o_count & 1, wctx, 9);
+      ok = mbar_wait(bar(O_READY + t), o_count & 1, wctx, 9);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ++o_count;
@@ -475,6 +583,35 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
+#ifdef NLFA_TRACE
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < 4 * 1024; i += blockDim.x) (&g_trace[0][0])[i] = tr_buf[i];
+#endif
+  // scheduler bookkeeping: the last CTA of the launch to get here re-arms the counters
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned done = atomicAdd(&p.sched[1], 1u);
+    if (done == gridDim.x - 1) {
+      p.sched[0] = 0u;
+      p.sched[1] = 0u;
+      __threadfence();
+    }
+  }
+}
+
+// Device address of a fresh pair of scheduler counters on the current device.
+unsigned* fwd_sched_slot() {
+  static unsigned* base[64];
+  static unsigned next_slot = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_fwd_sched) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<unsigned*>(ptr);
+  }
+  const unsigned slot = (next_slot++) % kFwdSchedSlots;
+  return base[dev] + 2 * slot;
 }
 
 int sm_count() {
@@ -511,6 +648,8 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
   fp.o = o;
   fp.lse = lse;
   fp.status = status;
+  fp.sched = fwd_sched_slot();
+  if (fp.sched == nullptr) return NLFA_ERR_CUDA;
   const int grid = fp.total_units < sm_count() ? fp.total_units : sm_count();
   kern<<<grid, NT * 128 + 64, L::kDynamic, stream>>>(mq, mk, mv, fp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
