@@ -32,6 +32,23 @@
 
 namespace nlfa {
 
+#ifdef NLFA_TRACE
+// Debug-only timeline of CTA 0: (clock64, tag) pairs per role, staged in shared memory.
+__device__ long long g_btrace[4][1024];
+__device__ int g_btrace_n[4];
+#define NLFA_BTRACE(role, tag)                                        \
+  do {                                                                \
+    if (blockIdx.x == 0 && tr_n < 512) {                              \
+      tr_buf[((role) * 512 + tr_n) * 2] = clock64();                  \
+      tr_buf[((role) * 512 + tr_n) * 2 + 1] = (tag);                  \
+      ++tr_n;                                                         \
+      g_btrace_n[role] = tr_n;                                        \
+    }                                                                 \
+  } while (0)
+#else
+#define NLFA_BTRACE(role, tag)
+#endif
+
 // Work counters for the in-kernel scheduler: [slot][0] next unit, [slot][1] CTAs
 // finished.  The last CTA of a launch to finish zeroes its slot again.
 constexpr int kSchedSlots = 256;
@@ -71,7 +88,12 @@ struct BwdSmem {
   static constexpr int kTmemSlot = kSched + 4 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
+#ifdef NLFA_TRACE
+  static constexpr int kTrace = (kTotal + 15) / 16 * 16;
+  static constexpr int kDynamic = kTrace + 4 * 512 * 16 + 1024;
+#else
   static constexpr int kDynamic = kTotal + 1024;
+#endif
 };
 
 // One work unit: a stationary tile and the list of streamed tiles it meets.
@@ -124,7 +146,8 @@ template <typename T, int D, int MODE, int STAGES, int XBUF>
 __global__ void __launch_bounds__(320, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-              const BwdParams p) {
+              const __grid_constant__ CUtensorMap tm_out0,
+              const __grid_constant__ CUtensorMap tm_out1, const BwdParams p) {
   using L = BwdSmem<D, STAGES, XBUF>;
   constexpr int kBoxes = D / 64;
   constexpr int kBoxBytes = kTile * 128;
@@ -142,6 +165,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   uint8_t* gen = smem_raw + (base - raw);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef NLFA_TRACE
+  long long* tr_buf = reinterpret_cast<long long*>(gen + L::kTrace);
+  int tr_n = 0;
+#endif
 
   auto bar = [&](int i) -> uint32_t { return base + L::kBar + 8u * i; };
   constexpr int X_FULL = 0, X_EMPTY = XBUF, T_FULL = 2 * XBUF, T_CONSUMED = T_FULL + 1,
@@ -156,7 +183,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     *abort_flag = (*reinterpret_cast<volatile unsigned*>(p.status) != STATUS_OK) ? 1 : 0;
     for (int i = 0; i < XBUF; ++i) {
       mbar_init(bar(X_FULL + i), 1);
-      mbar_init(bar(X_EMPTY + i), 1);
+      mbar_init(bar(X_EMPTY + i), 2);      // the MMA issuer's commit + the epilogue's store
     }
     mbar_init(bar(T_FULL), 1);
     mbar_init(bar(T_CONSUMED), 256);
@@ -202,33 +229,44 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
     bool ok = true;
     int git = 0;
-    for (int uc = 0; ok; ++uc) {
+    // Takes the uc-th unit of this CTA from the global counter, publishes it to the other
+    // roles and starts the loads of its stationary tiles.  Returns the unit (-1: none left).
+    auto fetch_unit = [&](int uc) -> int {
       int u = 0;
       if (lane == 0) {
         u = static_cast<int>(atomicAdd(&p.sched[0], 1u));
         if (u >= p.total_units) u = -1;
         sched_ring[uc % kRing] = u;
         mbar_arrive(bar(SCHED_FULL + (uc % kRing)));
-      }
-      u = __shfl_sync(0xffffffffu, u, 0);
-      if (u < 0) break;
-      const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
-      const int xb = uc % XBUF;
-      if (lane == 0) {
-        ok = mbar_wait(bar(X_EMPTY + xb), ((uc / XBUF) & 1) ^ 1, wctx, 30);
-        if (ok) {
-          const int xh = MODE == MODE_DQ ? w.h : w.hk;
-          const uint32_t xa = base + L::kX + xb * 2 * L::kTileBytes;
-          mbar_arrive_expect_tx(bar(X_FULL + xb), 2 * L::kTileBytes);
-          for (int x = 0; x < kBoxes; ++x) {
-            tma_load_4d(xa + x * kBoxBytes, mx0, bar(X_FULL + xb), 64 * x, xh, w.tile * kTile, w.b);
-            tma_load_4d(xa + L::kTileBytes + x * kBoxBytes, mx1, bar(X_FULL + xb), 64 * x, xh,
-                        w.tile * kTile, w.b);
+        if (u >= 0) {
+          const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
+          const int xb = uc % XBUF;
+          ok = mbar_wait(bar(X_EMPTY + xb), ((uc / XBUF) & 1) ^ 1, wctx, 30);
+          if (ok) {
+            const int xh = MODE == MODE_DQ ? w.h : w.hk;
+            const uint32_t xa = base + L::kX + xb * 2 * L::kTileBytes;
+            mbar_arrive_expect_tx(bar(X_FULL + xb), 2 * L::kTileBytes);
+            for (int x = 0; x < kBoxes; ++x) {
+              tma_load_4d(xa + x * kBoxBytes, mx0, bar(X_FULL + xb), 64 * x, xh, w.tile * kTile, w.b);
+              tma_load_4d(xa + L::kTileBytes + x * kBoxBytes, mx1, bar(X_FULL + xb), 64 * x, xh,
+                          w.tile * kTile, w.b);
+            }
           }
         }
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      return __shfl_sync(0xffffffffu, u, 0);
+    };
+    int u = fetch_unit(0);
+    for (int uc = 0; ok && u >= 0; ++uc) {
+      const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
+      // The next unit's stationary tiles are requested once this unit's first streamed tiles
+      // are on their way (with one stationary buffer: only when this unit has released it).
+      int u_next = -2;
+      const int prefetch_at = XBUF > 1 ? (w.n_iters < STAGES ? w.n_iters : STAGES) : w.n_iters;
       for (int it = 0; ok && it < w.n_iters; ++it, ++git) {
+        if (it == prefetch_at) u_next = fetch_unit(uc + 1);
+        if (!ok) break;
         const int s = git % STAGES;
         const uint32_t ph = (git / STAGES) & 1;
         const int g = it / w.n_inner;
@@ -261,6 +299,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
         }
       }
+      if (ok && u_next == -2) u_next = fetch_unit(uc + 1);
+      u = u_next;
     }
   } else if (warp == 9) {
     // ================================ MMA issuer =============================
@@ -353,6 +393,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (ok) {
             tc_fence_after();
             issue_t(nxt_xb, g + 1);
+            NLFA_BTRACE(2, 20);
           }
         };
         // With a single stationary buffer the next unit's tiles can only be loaded once this
@@ -360,7 +401,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const bool early = kSep && have_next && !(crossed && XBUF == 1);
         if (early) issue_next_t();
         if (!ok) break;
+        NLFA_BTRACE(2, 10);
         if (!(ok = mbar_wait(bar(PD_FULL), g & 1, wctx, 34))) break;
+        NLFA_BTRACE(2, 11);
         tc_fence_after();
         issue_out(g, cur_it > 0 ? 1u : 0u);
         if (cur_it + 1 == cur_n) tc_commit(bar(X_EMPTY + cur_xb));
@@ -413,10 +456,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const int s = g % STAGES;
         const int gg = it / w.n_inner;
         const int idx = w.streamed_index(it - gg * w.n_inner);
+        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 1);
         ok = mbar_wait(bar(T_FULL), g & 1, wctx, 35);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 2);
 
         uint32_t sv[2][32], dv[2][32];
         tmem_ld32(t0, sv[0]);
@@ -426,6 +471,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_wait_ld();
         tc_fence_before();
         mbar_arrive(bar(T_CONSUMED));
+        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 3);
 
         const int qtile = MODE == MODE_DQ ? w.tile : idx;
         const int kblock = MODE == MODE_DQ ? idx : w.tile;
@@ -482,6 +528,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           dd[2 * c4] = Pack2<T>::pack(d0, d1);
           dd[2 * c4 + 1] = Pack2<T>::pack(d2, d3);
         }
+        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 4);
         // the previous iteration's output products must be done reading P / dS
         wait_out(g);
         if (!ok) break;
@@ -490,57 +537,67 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(PD_FULL));
+        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 5);
       }
       if (!ok) break;
 
+      if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 6);
       wait_out(g);                 // this unit's last output product
       if (!ok) break;
       tc_fence_after();
-      if (MODE == MODE_DQ) {
-        // each half stores D/2 columns of its dQ row
-        T* orow = static_cast<T*>(p.out0) +
-                  ((static_cast<long long>(w.b) * p.T + pos) * p.H + w.h) * static_cast<long long>(D) +
-                  half * (D / 2);
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_addr(tmem, lane_base, kOutCol + half * (D / 2) + 32 * c), r);
-          tc_wait_ld();
-          if (pos < p.T) {
+      // The unit's stationary tiles are dead now (every product that read them has
+      // completed), so their shared memory stages the output tiles, in the same swizzled
+      // layout the loads use, for coalesced TMA stores: dQ over the Q tile, dK over K, dV over V.
+      {
+        const int xb = uc % XBUF;
+        const uint32_t stage0 = base + L::kX + xb * 2 * L::kTileBytes;       // X0 region
+        const uint32_t sw = static_cast<uint32_t>(row & 7);
+        auto stage_cols = [&](uint32_t tile_base, uint32_t tmem_col, int col0, int ncols, float mul) {
+          // converts fp32 columns [col0, col0 + ncols) of this thread's row and writes them
+          for (int c = 0; c < ncols; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_addr(tmem, lane_base, tmem_col + c), r);
+            tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              uint4 v4;
-              v4.x = Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * p.scale, __uint_as_float(r[8 * i + 1]) * p.scale);
-              v4.y = Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * p.scale, __uint_as_float(r[8 * i + 3]) * p.scale);
-              v4.z = Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * p.scale, __uint_as_float(r[8 * i + 5]) * p.scale);
-              v4.w = Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * p.scale, __uint_as_float(r[8 * i + 7]) * p.scale);
-              *reinterpret_cast<uint4*>(orow + 32 * c + 8 * i) = v4;
+              const int col = col0 + c + 8 * i;                   // first of 8 columns = one 16 B chunk
+              const uint32_t box = static_cast<uint32_t>(col >> 6);
+              const uint32_t chunk = static_cast<uint32_t>((col & 63) >> 3);
+              const uint32_t addr = tile_base + box * kBoxBytes + static_cast<uint32_t>(row) * 128u +
+                                    ((chunk ^ sw) << 4);
+              st_shared_v4(addr,
+                           Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * mul, __uint_as_float(r[8 * i + 1]) * mul),
+                           Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * mul, __uint_as_float(r[8 * i + 3]) * mul),
+                           Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * mul, __uint_as_float(r[8 * i + 5]) * mul),
+                           Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * mul, __uint_as_float(r[8 * i + 7]) * mul));
             }
           }
+        };
+        if (MODE == MODE_DQ) {
+          // each half converts D/2 columns of its dQ row
+          stage_cols(stage0, kOutCol + half * (D / 2), half * (D / 2), D / 2, p.scale);
+        } else if (half == 0) {
+          stage_cols(stage0 + L::kTileBytes, kOutCol, 0, D, 1.f);           // dV over the V tile
+        } else {
+          stage_cols(stage0, kOutCol + D, 0, D, p.scale);                   // dK over the K tile
         }
-      } else {
-        // half 0 stores the dV row, half 1 the dK row (scaled)
-        const float mul = half == 0 ? 1.f : p.scale;
-        T* orow = static_cast<T*>(half == 0 ? p.out1 : p.out0) +
-                  ((static_cast<long long>(w.b) * p.T + pos) * p.Hkv + w.hk) * static_cast<long long>(D);
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_addr(tmem, lane_base, kOutCol + half * D + 32 * c), r);
-          tc_wait_ld();
-          if (pos < p.T) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 v4;
-              v4.x = Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * mul, __uint_as_float(r[8 * i + 1]) * mul);
-              v4.y = Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * mul, __uint_as_float(r[8 * i + 3]) * mul);
-              v4.z = Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * mul, __uint_as_float(r[8 * i + 5]) * mul);
-              v4.w = Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * mul, __uint_as_float(r[8 * i + 7]) * mul);
-              *reinterpret_cast<uint4*>(orow + 32 * c + 8 * i) = v4;
-            }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        named_barrier(1, 256);
+        if (threadIdx.x == 0) {
+          const int oh = MODE == MODE_DQ ? w.h : w.hk;
+          for (int x = 0; x < kBoxes; ++x) {
+            tma_store_4d(&tm_out0, stage0 + x * kBoxBytes, 64 * x, oh, w.tile * kTile, w.b);
+            if (MODE == MODE_DKV)
+              tma_store_4d(&tm_out1, stage0 + L::kTileBytes + x * kBoxBytes, 64 * x, oh,
+                           w.tile * kTile, w.b);
           }
+          tma_store_commit();
+          tma_store_wait_read();
+          mbar_arrive(bar(X_EMPTY + xb));        // second arrival: the buffer may be reloaded
         }
       }
+      if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 7);
       // the next unit's first output product overwrites these columns; it is issued
       // only after this thread's next PD arrival, which follows in program order
       tc_fence_before();
@@ -554,6 +611,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+#ifdef NLFA_TRACE
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < 4 * 1024; i += blockDim.x) (&g_btrace[0][0])[i] = tr_buf[i];
+#endif
   // scheduler bookkeeping: the last CTA of the launch to get here re-arms the counters
   if (threadIdx.x == 0) {
     __threadfence();
@@ -599,6 +660,13 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
                 const CUtensorMap& mv, const CUtensorMap& mdo, const float* lse,
                 const float* delta, void* out0, void* out1, unsigned* status,
                 cudaStream_t stream) {
+  // output tiles leave through TMA stores: dQ is [B,T,H,D], dK and dV are [B,T,Hkv,D]
+  CUtensorMap mo0, mo1;
+  const int out_heads = MODE == MODE_DQ ? p.H : p.Hkv;
+  int mst = make_tile_map(&mo0, out0, p.dtype, p.B, p.T, out_heads, p.D, kTile);
+  if (mst == NLFA_OK)
+    mst = make_tile_map(&mo1, MODE == MODE_DQ ? out0 : out1, p.dtype, p.B, p.T, out_heads, p.D, kTile);
+  if (mst != NLFA_OK) return mst;
   using L = BwdSmem<D, STAGES, XBUF>;
   auto kern = bwd_tc_kernel<T, D, MODE, STAGES, XBUF>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
@@ -623,7 +691,7 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
   bp.sched = sched_slot();
   if (bp.sched == nullptr) return NLFA_ERR_CUDA;
   const int grid = bp.total_units < sm_count_bwd() ? bp.total_units : sm_count_bwd();
-  kern<<<grid, 320, L::kDynamic, stream>>>(mq, mk, mv, mdo, bp);
+  kern<<<grid, 320, L::kDynamic, stream>>>(mq, mk, mv, mdo, mo0, mo1, bp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
@@ -665,5 +733,17 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   return bf16 ? launch_both<__nv_bfloat16, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
               : launch_both<__half, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
 }
+
+#ifdef NLFA_TRACE
+extern "C" int nlfa_btrace_read(long long* events, int* counts) {
+  int zero[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return NLFA_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(events, g_btrace, sizeof(long long) * 4 * 1024) != cudaSuccess ||
+      cudaMemcpyFromSymbol(counts, g_btrace_n, sizeof(int) * 4) != cudaSuccess ||
+      cudaMemcpyToSymbol(g_btrace_n, zero, sizeof(zero)) != cudaSuccess)
+    return NLFA_ERR_CUDA;
+  return NLFA_OK;
+}
+#endif
 
 }  // namespace nlfa

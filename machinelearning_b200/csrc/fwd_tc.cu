@@ -24,6 +24,10 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
+#ifndef NLFA_VARIANT
+#define NLFA_VARIANT 0
+#endif
+
 namespace nlfa {
 
 #ifdef NLFA_TRACE
@@ -223,16 +227,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tma_prefetch_desc(&tm_v);
       int git = 0;
       bool ok = true;
-      for (int uc = 0; ok; ++uc) {
+      // Takes the uc-th unit of this CTA from the global counter, publishes it to the other
+      // roles and starts the loads of its Q tiles.  Returns the unit (-1: none left).
+      auto fetch_unit = [&](int uc) -> int {
         int u = static_cast<int>(atomicAdd(&p.sched[0], 1u));
         if (u >= p.total_units) u = -1;
         sched_ring[uc % kRing] = u;
         mbar_arrive(bar(SCHED_FULL + (uc % kRing)));
-        if (u < 0) break;
+        if (u < 0) return u;
         const Unit<NT> w = make_unit<NT>(u, p, BH);
         const int qb = uc % QBUF;
         const uint32_t qph = (uc / QBUF) & 1;
-        if (!(ok = mbar_wait(bar(Q_EMPTY + qb), qph ^ 1, wctx, 10))) break;
+        if (!(ok = mbar_wait(bar(Q_EMPTY + qb), qph ^ 1, wctx, 10))) return u;
         mbar_arrive_expect_tx(bar(Q_FULL + qb), w.n_valid * L::kTileBytes);
         for (int t = 0; t < NT; ++t) {
           if (!w.valid[t]) continue;
@@ -240,7 +246,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             tma_load_4d(base + L::kQ + (qb * NT + t) * L::kTileBytes + x * kBoxBytes, &tm_q,
                         bar(Q_FULL + qb), 64 * x, w.h, (w.tile0 + t) * kTile, w.b);
         }
+        return u;
+      };
+      int u = fetch_unit(0);
+      for (int uc = 0; ok && u >= 0; ++uc) {
+        const Unit<NT> w = make_unit<NT>(u, p, BH);
+        // the next unit's Q is requested once this unit's first K/V blocks are on their way
+        // (with a single Q buffer: only when this unit has released it)
+        int u_next = -2;
+        const int prefetch_at = QBUF > 1 ? (w.n_iters < STAGES ? w.n_iters : STAGES) : w.n_iters;
         for (int it = 0; it < w.n_iters; ++it, ++git) {
+          if (it == prefetch_at) u_next = fetch_unit(uc + 1);
+          if (!ok) break;
           const int s = git % STAGES;
           const uint32_t ph = (git / STAGES) & 1;
           const int j = w.block_at(it);
@@ -256,6 +273,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             tma_load_4d(base + L::kV + s * L::kTileBytes + x * kBoxBytes, &tm_v, bar(V_FULL + s),
                         64 * x, w.hk, j * kTile, w.b);
         }
+        if (ok && u_next == -2) u_next = fetch_unit(uc + 1);
+        u = u_next;
       }
     }
   } else if (warp == 4 * NT + 1) {
@@ -452,30 +471,59 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
           const uint64_t negm2 = pack_f2(-m_use, -m_use);
           uint64_t acc0 = 0ull, acc1 = 0ull;            // packed (0.f, 0.f)
+#if NLFA_VARIANT == 1
+          float sum_a = 0.f, sum_b = 0.f;
+#endif
           float b0 = -INFINITY, b1 = -INFINITY;
+#if NLFA_VARIANT != 7
           tmem_ld32(s_addr, buf[0]);
+#endif
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
+#if NLFA_VARIANT != 7
             tc_wait_ld();
             if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), buf[(c + 1) & 1]);
+#endif
             uint32_t (&r)[32] = buf[c & 1];
             if (masked) mask_chunk(r, c);
             uint32_t pk[16];
+#if NLFA_VARIANT >= 5
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = r[2 * i];
+#else
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
               const float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
               const float s2 = __uint_as_float(r[i + 2]), s3 = __uint_as_float(r[i + 3]);
+#if NLFA_VARIANT != 2
               b0 = fmax3(b0, s0, s1);
               b1 = fmax3(b1, s2, s3);
+#endif
               float e0, e1, e2, e3;
+#if NLFA_VARIANT == 1
+              e0 = fmaf(s0, p.scale_log2, -m_use); e1 = fmaf(s1, p.scale_log2, -m_use);
+              e2 = fmaf(s2, p.scale_log2, -m_use); e3 = fmaf(s3, p.scale_log2, -m_use);
+#else
               unpack_f2(ffma2(pack_f2(s0, s1), scale2, negm2), e0, e1);
               unpack_f2(ffma2(pack_f2(s2, s3), scale2, negm2), e2, e3);
+#endif
+#if NLFA_VARIANT != 4
               e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
+#endif
+#if NLFA_VARIANT == 1
+              sum_a += e0 + e1; sum_b += e2 + e3;
+#else
               acc0 = fadd2(acc0, pack_f2(e0, e1));
               acc1 = fadd2(acc1, pack_f2(e2, e3));
+#endif
+#if NLFA_VARIANT != 3
               pk[i / 2] = Pack2<T>::pack(e0, e1);
               pk[i / 2 + 1] = Pack2<T>::pack(e2, e3);
+#else
+              pk[i / 2] = __float_as_uint(e0); pk[i / 2 + 1] = __float_as_uint(e2);
+#endif
             }
+#endif
             if (!o_synced) {
               // before the first write of P (and before O is rescaled): the previous block's
               // PV product must be complete; every O_READY phase is observed once, in order
@@ -485,13 +533,20 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               o_synced = true;
               tc_fence_after();
             }
+#if NLFA_VARIANT != 6
             tmem_st16(p_addr + 16 * c, pk);
+#else
+            if (pk[0] == 0x12345u) tmem_st16(p_addr + 16 * c, pk);
+#endif
           }
           if (!ok) break;
           bmax = fmaxf(b0, b1) * p.scale_log2;
           float lo, hi;
           unpack_f2(fadd2(acc0, acc1), lo, hi);
           sum = lo + hi;
+#if NLFA_VARIANT == 1
+          sum = sum_a + sum_b;
+#endif
           // Fast path: P was formed against a reference that may lag this block's maximum.
           // That is fine up to a point (bf16/f16 P and the fp32 sum have the range); beyond
           // 2^12 (f16 tops out at 2^16) the block is redone against its own maximum.  Only

@@ -152,6 +152,30 @@ def test_simt_fwd_bwd_vs_oracle(fc, B, T, H, Hkv, D, window, sinks, dtype):
             assert rel(got, want) <= REL_16BIT
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("gain", [4.0, 12.0])
+def test_tensor_core_peaky_scores_exercise_the_rescale_paths(fc, D, gain):
+    # large, growing scores: the row maximum jumps by far more than 2^8 from block to block, so
+    # the forward has to raise its reference exponent (deferred O rescale and block redo)
+    torch.manual_seed(3)
+    B, T, H = 1, 700, 2
+    ramp = torch.linspace(0.2, 1.0, T, device="cuda").view(1, T, 1, 1)
+    q = (torch.randn(B, T, H, D, device="cuda") * gain).bfloat16()
+    k = (torch.randn(B, T, H, D, device="cuda") * gain * ramp).bfloat16()
+    v, do = (torch.randn(B, T, H, D, device="cuda").bfloat16() for _ in range(2))
+    scale = 1.0 / math.sqrt(D)
+    y, dq, dk, dv = run_fwd_bwd(fc, q, k, v, do, scale, True)
+    assert device_status_ok()
+    o_r, lse_r = orc.attention_fwd(q, k, v, scale)
+    gq, gk, gv = orc.attention_bwd(do, q, k, v, scale)
+    assert torch.isfinite(y).all()
+    assert rel(y, o_r) <= REL_16BIT
+    _, lse = fc.fwd(q, k, v, scale, True)
+    assert float(np.abs(lse.double().cpu().numpy() - lse_r).max() / np.abs(lse_r).max()) <= 1e-3
+    for got, want, name in ((dq, gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
+        assert rel(got, want) <= REL_16BIT, name
+
+
 def test_config1_fp32_full_shape(fc):
     # fp32, B=4, H=4, T=256, D=64, N(0,1) from seed 0, scale 1/8: O, LSE, dQ, dK, dV <= 1e-5
     torch.manual_seed(0)
