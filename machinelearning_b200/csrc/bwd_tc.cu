@@ -143,7 +143,7 @@ __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p
 }
 
 template <typename T, int D, int MODE, int STAGES, int XBUF>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_out0,
@@ -206,6 +206,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tmem = *tmem_slot;
   const bool dead = *abort_flag != 0;
 
+  // The launch gives every thread 168 registers (384 threads).  Inside its role's branch
+  // each warp of the third warpgroup (producer, MMA issuer, two spare warps) drops to 104 and
+  // the two compute warpgroups take 200 each.
+
   // Every role reads the unit index of its uc-th unit from the ring the producer
   // fills; a negative index means there is no more work.
   auto next_unit = [&](int uc, bool& ok) -> int {
@@ -213,8 +217,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     return ok ? sched_ring[uc % kRing] : -1;
   };
 
-  if (dead) {
-    // straight to the tail
+  if (warp >= 8) {
+  setmaxnreg_dec<104>();
+  if (dead || warp >= 10) {
+    // nothing to do (spare warps only complete the third warpgroup)
   } else if (warp == 8) {
     // ========================= scheduler + TMA producer ======================
     const CUtensorMap* mx0 = MODE == MODE_DQ ? &tm_q : &tm_k;
@@ -302,7 +308,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok && u_next == -2) u_next = fetch_unit(uc + 1);
       u = u_next;
     }
-  } else if (warp == 9) {
+  } else {
     // ================================ MMA issuer =============================
     if (lane == 0) {
       constexpr uint32_t idesc_t = make_idesc(kBf16, 128, 128, false, false);
@@ -416,8 +422,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ++g;
       }
     }
+  }
   } else {
     // ================================= compute ===============================
+    setmaxnreg_inc<200>();
+    if (!dead) {
     const int half = warp >> 2;                      // which 64 columns of the row
     const uint32_t lane_base = 32u * (warp & 3);
     const int row = 32 * (warp & 3) + lane;          // row of the stationary tile == TMEM lane
@@ -602,6 +611,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // only after this thread's next PD arrival, which follows in program order
       tc_fence_before();
     }
+    }
   }
 
   __syncwarp();
@@ -691,7 +701,7 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
   bp.sched = sched_slot();
   if (bp.sched == nullptr) return NLFA_ERR_CUDA;
   const int grid = bp.total_units < sm_count_bwd() ? bp.total_units : sm_count_bwd();
-  kern<<<grid, 320, L::kDynamic, stream>>>(mq, mk, mv, mdo, mo0, mo1, bp);
+  kern<<<grid, 384, L::kDynamic, stream>>>(mq, mk, mv, mdo, mo0, mo1, bp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 

@@ -83,7 +83,7 @@ struct WaitCtx {
   unsigned* status;           // global memory
 };
 
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+static __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                             unsigned where) {
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t spins = 1;; ++spins) {
@@ -148,6 +148,17 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                                              uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
                : "memory");
+}
+
+// Register reallocation between the warpgroups of a CTA.  Every warp of a warpgroup (four
+// consecutive warps) must execute the same one; N is a multiple of 8.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ----------------------------------------------------------------- tcgen05 --
