@@ -27,8 +27,14 @@
 // columns; dV then dK: 2 D columns).  The 16-bit P / dS operands of the output
 // products live in their own columns when there is room (everything except
 // dK/dV at D = 128, where they overwrite the columns of T0/T1 just read).
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
+
+#ifndef NLFA_VARIANT
+#define NLFA_VARIANT 0
+#endif
 
 namespace nlfa {
 
@@ -404,7 +410,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         };
         // With a single stationary buffer the next unit's tiles can only be loaded once this
         // unit's buffer has been released, i.e. after the output products below are issued.
-        const bool early = kSep && have_next && !(crossed && XBUF == 1);
+        // At a unit's last iteration the output products go first, so that the epilogue (which
+        // has to wait for them) can start as early as possible.
+        const bool early = kSep && have_next && !crossed;
         if (early) issue_next_t();
         if (!ok) break;
         NLFA_BTRACE(2, 10);
@@ -453,6 +461,20 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
       const int pos = w.tile * kTile + row;            // query position (dQ) or key position (dK/dV)
 
+      // Columns this row can see, as positions of the streamed index: [va, va + vw], plus
+      // positions below vsink (sink keys; dQ orientation only).
+      int va, vsink = 0;
+      unsigned vw;
+      if (MODE == MODE_DQ) {                           // row = query `pos`, columns = keys
+        const int lo = p.window > 0 ? pos - (p.window - p.sinks) + 1 : 0;
+        va = lo > 0 ? lo : 0;
+        vw = static_cast<unsigned>(pos - va);
+        vsink = p.window > 0 ? (p.sinks < pos + 1 ? p.sinks : pos + 1) : 0;   // sinks are causal too
+      } else {                                         // row = key `pos`, columns = queries
+        va = pos;
+        vw = (p.window > 0 && pos >= p.sinks) ? static_cast<unsigned>(p.window - p.sinks - 1)
+                                               : 0x7fffffffu;
+      }
       uint64_t negl2_row = pack_f2(-INFINITY, -INFINITY), negd_row = 0ull;
       if (MODE == MODE_DQ && pos < p.T) {
         const long long idx = (static_cast<long long>(w.b) * p.H + w.h) * p.T + pos;
@@ -490,53 +512,87 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const int other0 = idx * kTile + 64 * half;      // position of this thread's first column
 
         uint32_t pp[32], dd[32];
+        // One 32-column chunk (8 groups of 4 columns).  kMasked: apply the per-element
+        // visibility test; the test is one unsigned compare against the row's visible interval
+        // [va, va + vw] (plus the sink prefix for the dQ orientation).
+        auto do_chunk = [&](auto ch_c, auto masked_c) {
+          constexpr int ch = decltype(ch_c)::value;
+          constexpr bool kMasked = decltype(masked_c)::value;
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {                // four columns (two packed pairs) per step
-          uint64_t nl_a, nl_b, nd_a, nd_b;
-          if (MODE == MODE_DQ) {
-            nl_a = nl_b = negl2_row;
-            nd_a = nd_b = negd_row;
-          } else {
-            const ulonglong2 nl = vec2[c4];              // -lse2 of columns 4 c4 .. 4 c4 + 3
-            const ulonglong2 nd = vec2[32 + c4];         // -delta
-            nl_a = nl.x; nl_b = nl.y; nd_a = nd.x; nd_b = nd.y;
-          }
-          const int c = 4 * c4;
-          const uint64_t xa = ffma2(pack_f2(__uint_as_float(sv[c >> 5][c & 31]),
-                                            __uint_as_float(sv[c >> 5][(c & 31) + 1])), scale2, nl_a);
-          const uint64_t xb = ffma2(pack_f2(__uint_as_float(sv[c >> 5][(c & 31) + 2]),
-                                            __uint_as_float(sv[c >> 5][(c & 31) + 3])), scale2, nl_b);
-          float p0, p1, p2, p3;
-          unpack_f2(xa, p0, p1);
-          unpack_f2(xb, p2, p3);
-          p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
-          if (!full) {
-            const int o = other0 + c;
+          for (int c8 = 0; c8 < 8; ++c8) {
+            const int c4 = 8 * ch + c8;
+            uint64_t nl_a, nl_b, nd_a, nd_b;
             if (MODE == MODE_DQ) {
-              if (!key_visible(pos, o + 0, p.window, p.sinks)) p0 = 0.f;
-              if (!key_visible(pos, o + 1, p.window, p.sinks)) p1 = 0.f;
-              if (!key_visible(pos, o + 2, p.window, p.sinks)) p2 = 0.f;
-              if (!key_visible(pos, o + 3, p.window, p.sinks)) p3 = 0.f;
+              nl_a = nl_b = negl2_row;
+              nd_a = nd_b = negd_row;
             } else {
-              if (!key_visible(o + 0, pos, p.window, p.sinks)) p0 = 0.f;
-              if (!key_visible(o + 1, pos, p.window, p.sinks)) p1 = 0.f;
-              if (!key_visible(o + 2, pos, p.window, p.sinks)) p2 = 0.f;
-              if (!key_visible(o + 3, pos, p.window, p.sinks)) p3 = 0.f;
+              const ulonglong2 nl = vec2[c4];              // -lse2 of columns 4 c4 .. 4 c4 + 3
+              const ulonglong2 nd = vec2[32 + c4];         // -delta
+              nl_a = nl.x; nl_b = nl.y; nd_a = nd.x; nd_b = nd.y;
             }
+            const int c = 4 * c4;
+            const uint64_t xa = ffma2(pack_f2(__uint_as_float(sv[c >> 5][c & 31]),
+                                              __uint_as_float(sv[c >> 5][(c & 31) + 1])), scale2, nl_a);
+            const uint64_t xb = ffma2(pack_f2(__uint_as_float(sv[c >> 5][(c & 31) + 2]),
+                                              __uint_as_float(sv[c >> 5][(c & 31) + 3])), scale2, nl_b);
+            float p0, p1, p2, p3;
+            unpack_f2(xa, p0, p1);
+            unpack_f2(xb, p2, p3);
+#if NLFA_VARIANT != 4
+            p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
+#endif
+            if (kMasked) {
+              const unsigned o = static_cast<unsigned>(other0 + c - va);   // wraps below va
+              const int ox = other0 + c;
+              if (!(o + 0u <= vw || ox + 0 < vsink)) p0 = 0.f;
+              if (!(o + 1u <= vw || ox + 1 < vsink)) p1 = 0.f;
+              if (!(o + 2u <= vw || ox + 2 < vsink)) p2 = 0.f;
+              if (!(o + 3u <= vw || ox + 3 < vsink)) p3 = 0.f;
+            }
+            const uint64_t pa = pack_f2(p0, p1), pb = pack_f2(p2, p3);
+            const uint64_t da = fmul2(pa, fadd2(pack_f2(__uint_as_float(dv[c >> 5][c & 31]),
+                                                        __uint_as_float(dv[c >> 5][(c & 31) + 1])), nd_a));
+            const uint64_t db = fmul2(pb, fadd2(pack_f2(__uint_as_float(dv[c >> 5][(c & 31) + 2]),
+                                                        __uint_as_float(dv[c >> 5][(c & 31) + 3])), nd_b));
+            float d0, d1, d2, d3;
+            unpack_f2(da, d0, d1);
+            unpack_f2(db, d2, d3);
+            pp[2 * c4] = Pack2<T>::pack(p0, p1);
+            pp[2 * c4 + 1] = Pack2<T>::pack(p2, p3);
+            dd[2 * c4] = Pack2<T>::pack(d0, d1);
+            dd[2 * c4 + 1] = Pack2<T>::pack(d2, d3);
           }
-          const uint64_t pa = pack_f2(p0, p1), pb = pack_f2(p2, p3);
-          const uint64_t da = fmul2(pa, fadd2(pack_f2(__uint_as_float(dv[c >> 5][c & 31]),
-                                                      __uint_as_float(dv[c >> 5][(c & 31) + 1])), nd_a));
-          const uint64_t db = fmul2(pb, fadd2(pack_f2(__uint_as_float(dv[c >> 5][(c & 31) + 2]),
-                                                      __uint_as_float(dv[c >> 5][(c & 31) + 3])), nd_b));
-          float d0, d1, d2, d3;
-          unpack_f2(da, d0, d1);
-          unpack_f2(db, d2, d3);
-          pp[2 * c4] = Pack2<T>::pack(p0, p1);
-          pp[2 * c4 + 1] = Pack2<T>::pack(p2, p3);
-          dd[2 * c4] = Pack2<T>::pack(d0, d1);
-          dd[2 * c4 + 1] = Pack2<T>::pack(d2, d3);
-        }
+        };
+        auto zero_chunk = [&](auto ch_c) {
+          constexpr int ch = decltype(ch_c)::value;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pp[16 * ch + i] = dd[16 * ch + i] = 0u;
+        };
+        // Boundary blocks: each 32-column chunk is, for the whole warp, either entirely
+        // visible (plain path), entirely masked (zeros, no arithmetic) or mixed.
+        auto chunk = [&](auto ch_c) {
+          constexpr int ch = decltype(ch_c)::value;
+          if (full) {
+            do_chunk(ch_c, std::false_type{});
+            return;
+          }
+          const int x0 = other0 + 32 * ch, x1 = x0 + 31;
+          const long long hi = static_cast<long long>(va) + vw;          // last visible position
+          const bool in = (x0 >= va && x1 <= hi) || x1 < vsink;
+          const bool out = (x1 < va || x0 > hi) && x0 >= vsink;
+          const bool all_in = __all_sync(0xffffffffu, in);
+          const bool all_out = __all_sync(0xffffffffu, out);
+          if (all_in) do_chunk(ch_c, std::false_type{});
+          else if (all_out) zero_chunk(ch_c);
+          else do_chunk(ch_c, std::true_type{});
+        };
+#if NLFA_VARIANT == 5
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { pp[i] = sv[i >> 4][2 * (i & 15)]; dd[i] = dv[i >> 4][2 * (i & 15)]; }
+#else
+        chunk(std::integral_constant<int, 0>{});
+        chunk(std::integral_constant<int, 1>{});
+#endif
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 4);
         // the previous iteration's output products must be done reading P / dS
         wait_out(g);

@@ -142,7 +142,7 @@ __device__ __forceinline__ Unit<NT> make_unit(int u, const FwdParams& p, int BH)
 }
 
 template <typename T, int D, int NT, int STAGES, int QBUF>
-__global__ void __launch_bounds__(NT * 128 + 64, 1)
+__global__ void __launch_bounds__(NT * 128 + 128, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using L = FwdSmem<D, NT, STAGES, QBUF>;
@@ -217,8 +217,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     return ok ? sched_ring[uc % kRing] : -1;
   };
 
-  if (dead) {
-    // fall through to the tail
+  // Register reallocation (NT = 2: 384 threads launch with 168 registers each): the
+  // warpgroup of the producer, the MMA issuer and two spare warps drops to 104, the softmax
+  // warpgroups take 200 each.
+  if (warp >= 4 * NT) {
+  if (NT == 2) setmaxnreg_dec<104>();
+  if (dead || warp >= 4 * NT + 2) {
+    // nothing to do (spare warps only complete the warpgroup)
   } else if (warp == 4 * NT) {
     // =============================== TMA producer ============================
     if (lane == 0) {
@@ -378,8 +383,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_commit(bar(Q_EMPTY + qb));
       }
     }
+  }
   } else {
     // ================================= softmax ===============================
+    if (NT == 2) setmaxnreg_inc<200>();
+    if (!dead) {
     const int t = warp >> 2;                       // query tile of this warpgroup
     const int row = threadIdx.x - 128 * t;         // row inside the tile == TMEM lane
     const uint32_t lane_base = 32u * (warp & 3);
@@ -628,6 +636,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // thread's next P arrival, which follows these loads in program order
       tc_fence_before();
     }
+    }
   }
 
   // ---- tail: everyone meets here (all waits above are bounded), TMEM is freed
@@ -706,7 +715,7 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
   fp.sched = fwd_sched_slot();
   if (fp.sched == nullptr) return NLFA_ERR_CUDA;
   const int grid = fp.total_units < sm_count() ? fp.total_units : sm_count();
-  kern<<<grid, NT * 128 + 64, L::kDynamic, stream>>>(mq, mk, mv, fp);
+  kern<<<grid, NT * 128 + 128, L::kDynamic, stream>>>(mq, mk, mv, fp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
