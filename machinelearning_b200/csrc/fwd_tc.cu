@@ -218,10 +218,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   };
 
   // Register reallocation (NT = 2: 384 threads launch with 168 registers each): the
-  // warpgroup of the producer, the MMA issuer and two spare warps drops to 104, the softmax
-  // warpgroups take 200 each.
+  // warpgroup of the producer, the MMA issuer and two spare warps drops to 72, the softmax
+  // warpgroups take 216 each.
   if (warp >= 4 * NT) {
-  if (NT == 2) setmaxnreg_dec<104>();
+  if (NT == 2) setmaxnreg_dec<72>();
   if (dead || warp >= 4 * NT + 2) {
     // nothing to do (spare warps only complete the warpgroup)
   } else if (warp == 4 * NT) {
@@ -386,7 +386,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   } else {
     // ================================= softmax ===============================
-    if (NT == 2) setmaxnreg_inc<200>();
+    if (NT == 2) setmaxnreg_inc<216>();
     if (!dead) {
     const int t = warp >> 2;                       // query tile of this warpgroup
     const int row = threadIdx.x - 128 * t;         // row inside the tile == TMEM lane
@@ -407,12 +407,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const int qpos = tile * kTile + row;
       // Online softmax in base 2.  m_ref is the reference exponent (scaled units): P =
       // 2^(x - m_ref).  It starts at the first block's row maximum and is afterwards only
-      // raised when a later block's maximum exceeds it by more than 2^8; the rescale of O and
-      // l that goes with a raise is applied at the start of the following block, after that
-      // block's PV product has landed (pend_alpha, pend_m).
+      // raised (with O and l rescaled) when a block's maximum exceeds it by more than 2^8,
+      // which keeps P within 16-bit range and makes the TMEM round trip of O rare.
       float m_ref = -INFINITY, l = 0.f;
-      float pend_alpha = 1.f, pend_m = 0.f;
       bool first = true;
+      // keys this row can see: [va, qpos] plus the sink prefix [0, vsink)
+      int va = 0, vsink = 0;
+      if (p.window > 0) {
+        const int lo = qpos - (p.window - p.sinks) + 1;
+        va = lo > 0 ? lo : 0;
+        vsink = p.sinks < qpos + 1 ? p.sinks : qpos + 1;
+      }
+      const unsigned vw = static_cast<unsigned>(qpos - va);
       for (int it = 0; it < w.n_iters; ++it) {
         const int j = w.block_at(it);
         if (!tile_sees_block(w.tr[t], j)) continue;
@@ -424,177 +430,111 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         if (row == 0) NLFA_TRACE_EVENT(t, 2);
 
-        const bool masked = !block_fully_visible(tile, j, p.window, p.sinks);
-        const int k0 = j * kTile;
-        const bool rescale_pending = __any_sync(0xffffffffu, pend_alpha != 1.f);
-        if (pend_alpha != 1.f) {
-          l *= pend_alpha;
-          m_ref = pend_m;
-        }
-
-        // S is streamed out of TMEM 32 columns at a time (two buffers: the next chunk's load
-        // is in flight while this one is processed), so a row never sits in registers whole.
-        uint32_t buf[2][32];
-        auto mask_chunk = [&](uint32_t (&r)[32], int c) {
+        // the whole row of S into registers; from then on S_t belongs to the MMA issuer again
+        uint32_t sv[4][32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (!key_visible(qpos, k0 + 32 * c + i, p.window, p.sinks))
-              r[i] = __float_as_uint(-INFINITY);
-        };
+        for (int c = 0; c < 4; ++c) tmem_ld32(s_addr + 32 * c, sv[c]);
+        tc_wait_ld();
+        tc_fence_before();
+        mbar_arrive(bar(S_CONSUMED + t));
 
-        // The first block of a row (and every block when P shares S's columns, where a second
-        // look at S is impossible once P is being written) gets a separate maximum pass.
-        if (first || !kSepP) {
-          float b0 = -INFINITY, b1 = -INFINITY;
-          tmem_ld32(s_addr, buf[0]);
+        // Boundary blocks: each 32-column chunk is, for the whole warp, entirely visible (0),
+        // mixed (1: masked entries become -inf) or entirely masked (2: skipped).
+        const int k0 = j * kTile;
+        int cls[4] = {0, 0, 0, 0};
+        if (!block_fully_visible(tile, j, p.window, p.sinks)) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            tc_wait_ld();
-            if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), buf[(c + 1) & 1]);
-            uint32_t (&r)[32] = buf[c & 1];
-            if (masked) mask_chunk(r, c);
+            const int x0 = k0 + 32 * c, x1 = x0 + 31;
+            const bool in = (x0 >= va && x1 <= qpos) || x1 < vsink;
+            const bool out = (x1 < va || x0 > qpos) && x0 >= vsink;
+            cls[c] = __all_sync(0xffffffffu, in) ? 0 : (__all_sync(0xffffffffu, out) ? 2 : 1);
+            if (cls[c] == 1) {
+              const unsigned o = static_cast<unsigned>(x0 - va);          // wraps below va
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              b0 = fmax3(b0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-              b1 = fmax3(b1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+              for (int i = 0; i < 32; ++i)
+                if (!(o + static_cast<unsigned>(i) <= vw || x0 + i < vsink))
+                  sv[c][i] = __float_as_uint(-INFINITY);
             }
           }
-          const float mx = fmaxf(b0, b1) * p.scale_log2;
-          if (first) {
-            m_ref = mx;
-          } else if (mx > m_ref + 8.f) {
-            // raise the reference now: O holds every earlier block (their PV products are
-            // waited for below, before O is touched)
-            pend_alpha *= fast_exp2(m_ref - mx);
-            l *= fast_exp2(m_ref - mx);
-            m_ref = mx;
+        }
+        // row maximum of the raw scores: two chains of 3-input max per chunk
+        float b0 = -INFINITY, b1 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (cls[c] == 2) continue;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            b0 = fmax3(b0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+            b1 = fmax3(b1, __uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3]));
           }
         }
+        const float mx = fmaxf(b0, b1) * p.scale_log2;
         if (row == 0) NLFA_TRACE_EVENT(t, 3);
 
-        bool o_synced = first;          // no earlier PV product in this unit to wait for
-        float bmax = -INFINITY;
-        float sum = 0.f;
-        for (int attempt = 0; attempt < 2; ++attempt) {
-          const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-          const uint64_t negm2 = pack_f2(-m_use, -m_use);
-          uint64_t acc0 = 0ull, acc1 = 0ull;            // packed (0.f, 0.f)
-#if NLFA_VARIANT == 1
-          float sum_a = 0.f, sum_b = 0.f;
-#endif
-          float b0 = -INFINITY, b1 = -INFINITY;
-#if NLFA_VARIANT != 7
-          tmem_ld32(s_addr, buf[0]);
-#endif
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-#if NLFA_VARIANT != 7
-            tc_wait_ld();
-            if (c < 3) tmem_ld32(s_addr + 32 * (c + 1), buf[(c + 1) & 1]);
-#endif
-            uint32_t (&r)[32] = buf[c & 1];
-            if (masked) mask_chunk(r, c);
-            uint32_t pk[16];
-#if NLFA_VARIANT >= 5
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = r[2 * i];
-#else
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              const float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-              const float s2 = __uint_as_float(r[i + 2]), s3 = __uint_as_float(r[i + 3]);
-#if NLFA_VARIANT != 2
-              b0 = fmax3(b0, s0, s1);
-              b1 = fmax3(b1, s2, s3);
-#endif
-              float e0, e1, e2, e3;
-#if NLFA_VARIANT == 1
-              e0 = fmaf(s0, p.scale_log2, -m_use); e1 = fmaf(s1, p.scale_log2, -m_use);
-              e2 = fmaf(s2, p.scale_log2, -m_use); e3 = fmaf(s3, p.scale_log2, -m_use);
-#else
-              unpack_f2(ffma2(pack_f2(s0, s1), scale2, negm2), e0, e1);
-              unpack_f2(ffma2(pack_f2(s2, s3), scale2, negm2), e2, e3);
-#endif
-#if NLFA_VARIANT != 4
-              e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
-#endif
-#if NLFA_VARIANT == 1
-              sum_a += e0 + e1; sum_b += e2 + e3;
-#else
-              acc0 = fadd2(acc0, pack_f2(e0, e1));
-              acc1 = fadd2(acc1, pack_f2(e2, e3));
-#endif
-#if NLFA_VARIANT != 3
-              pk[i / 2] = Pack2<T>::pack(e0, e1);
-              pk[i / 2 + 1] = Pack2<T>::pack(e2, e3);
-#else
-              pk[i / 2] = __float_as_uint(e0); pk[i / 2 + 1] = __float_as_uint(e2);
-#endif
-            }
-#endif
-            if (!o_synced) {
-              // before the first write of P (and before O is rescaled): the previous block's
-              // PV product must be complete; every O_READY phase is observed once, in order
-              ok = mbar_wait(bar(O_READY + t), o_count & 1, wctx, 13);
-              ok = __all_sync(0xffffffffu, ok);
-              ++o_count;
-              o_synced = true;
-              tc_fence_after();
-            }
-#if NLFA_VARIANT != 6
-            tmem_st16(p_addr + 16 * c, pk);
-#else
-            if (pk[0] == 0x12345u) tmem_st16(p_addr + 16 * c, pk);
-#endif
+        float alpha = 1.f;
+        bool rescale = false;
+        if (first) {
+          m_ref = mx;
+        } else {
+          if (mx > m_ref + 8.f) {
+            alpha = fast_exp2(m_ref - mx);     // m_ref == -inf gives 0
+            m_ref = mx;
+            rescale = true;
           }
+          // the previous block's PV product must be complete before O is rescaled or P is
+          // overwritten; every O_READY phase is observed exactly once, in order
+          ok = mbar_wait(bar(O_READY + t), o_count & 1, wctx, 13);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          bmax = fmaxf(b0, b1) * p.scale_log2;
-          float lo, hi;
-          unpack_f2(fadd2(acc0, acc1), lo, hi);
-          sum = lo + hi;
-#if NLFA_VARIANT == 1
-          sum = sum_a + sum_b;
-#endif
-          // Fast path: P was formed against a reference that may lag this block's maximum.
-          // That is fine up to a point (bf16/f16 P and the fp32 sum have the range); beyond
-          // 2^12 (f16 tops out at 2^16) the block is redone against its own maximum.  Only
-          // possible when P has its own columns, so S is still intact.
-          const bool redo = kSepP && (bmax > m_ref + 12.f);
-          if (!__any_sync(0xffffffffu, redo)) break;
-          if (bmax > m_ref + 8.f) {
-            const float a = fast_exp2(m_ref - bmax);      // m_ref == -inf gives 0
-            pend_alpha *= a;
-            l *= a;
-            m_ref = bmax;
-          }
-        }
-        if (!ok) break;
-        tc_fence_before();
-        mbar_arrive(bar(S_CONSUMED + t));          // S_t may be overwritten from here on
-        l += sum;
-
-        // rescale of O decided earlier (rare): all PV products so far are complete
-        if (rescale_pending || __any_sync(0xffffffffu, pend_alpha != 1.f)) {
-          if (!first) {
+          ++o_count;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, rescale)) {
+            l *= alpha;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t orr[32];
               tmem_ld32(o_addr + 32 * c, orr);
               tc_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                orr[i] = __float_as_uint(__uint_as_float(orr[i]) * pend_alpha);
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
               tmem_st32(o_addr + 32 * c, orr);
             }
           }
-          pend_alpha = 1.f;
-        }
-        // this block's maximum moves the reference for the blocks after it
-        if (bmax > m_ref + 8.f) {
-          pend_alpha = fast_exp2(m_ref - bmax);
-          pend_m = bmax;
         }
         first = false;
+
+        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+        const uint64_t negm2 = pack_f2(-m_use, -m_use);
+        uint64_t acc0 = 0ull, acc1 = 0ull;              // packed (0.f, 0.f)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+          if (cls[c] == 2) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = 0u;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              float e0, e1, e2, e3;
+              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])),
+                              scale2, negm2), e0, e1);
+              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3])),
+                              scale2, negm2), e2, e3);
+              e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
+              acc0 = fadd2(acc0, pack_f2(e0, e1));
+              acc1 = fadd2(acc1, pack_f2(e2, e3));
+              pk[i / 2] = Pack2<T>::pack(e0, e1);
+              pk[i / 2 + 1] = Pack2<T>::pack(e2, e3);
+            }
+          }
+          tmem_st16(p_addr + 16 * c, pk);
+        }
+        {
+          float lo, hi;
+          unpack_f2(fadd2(acc0, acc1), lo, hi);
+          l += lo + hi;
+        }
         if (row == 0) NLFA_TRACE_EVENT(t, 4);
         tc_wait_st();
         tc_fence_before();
