@@ -144,7 +144,8 @@ __device__ __forceinline__ Unit<NT> make_unit(int u, const FwdParams& p, int BH)
 template <typename T, int D, int NT, int STAGES, int QBUF>
 __global__ void __launch_bounds__(NT * 128 + 128, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+              const FwdParams p) {
   using L = FwdSmem<D, NT, STAGES, QBUF>;
   constexpr int kBoxes = D / 64;                 // 64-element column boxes per tile
   constexpr int kBoxBytes = kTile * 128;         // 128 rows x 128 bytes
@@ -183,7 +184,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     *abort_flag = (*reinterpret_cast<volatile unsigned*>(p.status) != STATUS_OK) ? 1 : 0;
     for (int i = 0; i < QBUF; ++i) {
       mbar_init(bar(Q_FULL + i), 1);
-      mbar_init(bar(Q_EMPTY + i), 1);
+      mbar_init(bar(Q_EMPTY + i), 1 + NT);   // the MMA issuer's commit + one arrival per tile's store
     }
     for (int t = 0; t < NT; ++t) {
       mbar_init(bar(S_FULL + t), 1);
@@ -402,7 +403,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ok = __all_sync(0xffffffffu, ok);
       if (!ok || u < 0) break;
       const Unit<NT> w = make_unit<NT>(u, p, BH);
-      if (!w.valid[t]) continue;
+      if (!w.valid[t]) {
+        if (row == 0) mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));    // nothing to store for this tile
+        continue;
+      }
       const int tile = w.tile0 + t;
       const int qpos = tile * kTile + row;
       // Online softmax in base 2.  m_ref is the reference exponent (scaled units): P =
@@ -549,25 +553,39 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok) break;
       ++o_count;
       tc_fence_after();
+      // The unit's Q tile is dead (every S product that read it has completed), so its shared
+      // memory stages the normalised O tile, in the swizzled layout of the loads, for one
+      // coalesced TMA store per 64-column box.
       const float inv = 1.f / l;
-      T* orow = static_cast<T*>(p.o) +
-                ((static_cast<long long>(w.b) * p.T + qpos) * p.H + w.h) * static_cast<long long>(D);
+      const uint32_t stage = base + L::kQ + ((uc % QBUF) * NT + t) * L::kTileBytes;
+      const uint32_t sw = static_cast<uint32_t>(row & 7);
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t orr[32];
         tmem_ld32(o_addr + 32 * c, orr);
         tc_wait_ld();
-        if (qpos < p.T) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 v4;
-            v4.x = Pack2<T>::pack(__uint_as_float(orr[8 * i + 0]) * inv, __uint_as_float(orr[8 * i + 1]) * inv);
-            v4.y = Pack2<T>::pack(__uint_as_float(orr[8 * i + 2]) * inv, __uint_as_float(orr[8 * i + 3]) * inv);
-            v4.z = Pack2<T>::pack(__uint_as_float(orr[8 * i + 4]) * inv, __uint_as_float(orr[8 * i + 5]) * inv);
-            v4.w = Pack2<T>::pack(__uint_as_float(orr[8 * i + 6]) * inv, __uint_as_float(orr[8 * i + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + 32 * c + 8 * i) = v4;
-          }
+        for (int i = 0; i < 4; ++i) {
+          const int col = 32 * c + 8 * i;                       // first of 8 columns = one 16 B chunk
+          const uint32_t addr = stage + static_cast<uint32_t>(col >> 6) * kBoxBytes +
+                                static_cast<uint32_t>(row) * 128u +
+                                ((static_cast<uint32_t>((col & 63) >> 3) ^ sw) << 4);
+          st_shared_v4(addr,
+                       Pack2<T>::pack(__uint_as_float(orr[8 * i + 0]) * inv, __uint_as_float(orr[8 * i + 1]) * inv),
+                       Pack2<T>::pack(__uint_as_float(orr[8 * i + 2]) * inv, __uint_as_float(orr[8 * i + 3]) * inv),
+                       Pack2<T>::pack(__uint_as_float(orr[8 * i + 4]) * inv, __uint_as_float(orr[8 * i + 5]) * inv),
+                       Pack2<T>::pack(__uint_as_float(orr[8 * i + 6]) * inv, __uint_as_float(orr[8 * i + 7]) * inv));
         }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      named_barrier(1 + t, 128);
+      if (row == 0) {
+        for (int x = 0; x < kBoxes; ++x)
+          tma_store_4d(&tm_o, stage + x * kBoxBytes, 64 * x, w.h, tile * kTile, w.b);
+        tma_store_commit();
+        tma_store_wait_read();
+        mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));                // this tile's share of the buffer
       }
       if (qpos < p.T)
         p.lse[(static_cast<long long>(w.b) * p.H + w.h) * p.T + qpos] = (m_ref + log2f(l)) * kLn2;
@@ -633,7 +651,7 @@ int sm_count() {
 
 template <typename T, int D, int NT, int STAGES, int QBUF>
 int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-             void* o, float* lse, unsigned* status, cudaStream_t stream) {
+             const CUtensorMap& mo, void* o, float* lse, unsigned* status, cudaStream_t stream) {
   using L = FwdSmem<D, NT, STAGES, QBUF>;
   auto kern = fwd_tc_kernel<T, D, NT, STAGES, QBUF>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
@@ -655,7 +673,7 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
   fp.sched = fwd_sched_slot();
   if (fp.sched == nullptr) return NLFA_ERR_CUDA;
   const int grid = fp.total_units < sm_count() ? fp.total_units : sm_count();
-  kern<<<grid, NT * 128 + 128, L::kDynamic, stream>>>(mq, mk, mv, fp);
+  kern<<<grid, NT * 128 + 128, L::kDynamic, stream>>>(mq, mk, mv, mo, fp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
@@ -666,18 +684,19 @@ int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v,
   if (p.dtype != NLFA_DTYPE_F16 && p.dtype != NLFA_DTYPE_BF16) return NLFA_ERR_UNSUPPORTED_PATH;
   if (p.D != 64 && p.D != 128) return NLFA_ERR_UNSUPPORTED_PATH;
   if (!(p.scale > 0.f)) return NLFA_ERR_UNSUPPORTED_PATH;     // row max is taken before scaling
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   int st = make_tile_map(&mq, q, p.dtype, p.B, p.T, p.H, p.D, kTile);
   if (st == NLFA_OK) st = make_tile_map(&mk, k, p.dtype, p.B, p.T, p.Hkv, p.D, kTile);
   if (st == NLFA_OK) st = make_tile_map(&mv, v, p.dtype, p.B, p.T, p.Hkv, p.D, kTile);
+  if (st == NLFA_OK) st = make_tile_map(&mo, o, p.dtype, p.B, p.T, p.H, p.D, kTile);
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D == 64) {
-    return bf16 ? launch_t<__nv_bfloat16, 64, 2, 3, 2>(p, mq, mk, mv, o, lse, status, stream)
-                : launch_t<__half, 64, 2, 3, 2>(p, mq, mk, mv, o, lse, status, stream);
+    return bf16 ? launch_t<__nv_bfloat16, 64, 2, 3, 2>(p, mq, mk, mv, mo, o, lse, status, stream)
+                : launch_t<__half, 64, 2, 3, 2>(p, mq, mk, mv, mo, o, lse, status, stream);
   }
-  return bf16 ? launch_t<__nv_bfloat16, 128, 2, 2, 1>(p, mq, mk, mv, o, lse, status, stream)
-              : launch_t<__half, 128, 2, 2, 1>(p, mq, mk, mv, o, lse, status, stream);
+  return bf16 ? launch_t<__nv_bfloat16, 128, 2, 2, 1>(p, mq, mk, mv, mo, o, lse, status, stream)
+              : launch_t<__half, 128, 2, 2, 1>(p, mq, mk, mv, mo, o, lse, status, stream);
 }
 
 #ifdef NLFA_TRACE

@@ -122,6 +122,43 @@ delta_kernel(Problem p, const T* __restrict__ dout, const T* __restrict__ o,
   if (lane == 0) delta[(static_cast<long long>(b) * p.H + h) * p.T + t] = s;
 }
 
+// Delta for 16-bit tensors: pure streaming, so every thread moves 16 bytes of dO and of O
+// per load (8 elements); D / 8 consecutive lanes share a row and combine with shuffles.
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+delta_vec_kernel(Problem p, const T* __restrict__ dout, const T* __restrict__ o,
+                 float* __restrict__ delta) {
+  constexpr int kLanesPerRow = D / 8;                      // 8 (D = 64) or 16 (D = 128)
+  constexpr int kRowsPerWarp = 32 / kLanesPerRow;
+  const int lane = threadIdx.x & 31;
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long rows = static_cast<long long>(p.B) * p.T * p.H;     // rows index [B,T,H]
+  const long long row = warp_id * kRowsPerWarp + lane / kLanesPerRow;
+  float part = 0.f;
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(dout + row * D + 8 * (lane % kLanesPerRow));
+    const uint4 b = *reinterpret_cast<const uint4*>(o + row * D + 8 * (lane % kLanesPerRow));
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      T a2[2], b2[2];
+      *reinterpret_cast<uint32_t*>(a2) = aw[i];
+      *reinterpret_cast<uint32_t*>(b2) = bw[i];
+      part = fmaf(to_f32(a2[0]), to_f32(b2[0]), part);
+      part = fmaf(to_f32(a2[1]), to_f32(b2[1]), part);
+    }
+  }
+#pragma unroll
+  for (int off = kLanesPerRow / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+  if (row < rows && (lane % kLanesPerRow) == 0) {
+    const int h = static_cast<int>(row % p.H);
+    const long long bt = row / p.H;
+    const int t = static_cast<int>(bt % p.T);
+    const int b = static_cast<int>(bt / p.T);
+    delta[(static_cast<long long>(b) * p.H + h) * p.T + t] = part;
+  }
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 dq_simt_kernel(Problem p, const T* __restrict__ dout, const T* __restrict__ q,
@@ -264,8 +301,15 @@ int fwd_t(const Problem& p, const void* q, const void* k, const void* v, void* o
 template <typename T, int D>
 int delta_t(const Problem& p, const void* dout, const void* o, float* delta, cudaStream_t s) {
   const long long rows = static_cast<long long>(p.B) * p.H * p.T;
-  delta_kernel<T, D><<<blocks_for(rows), kWarpsPerBlock * 32, 0, s>>>(
-      p, static_cast<const T*>(dout), static_cast<const T*>(o), delta);
+  if constexpr (sizeof(T) == 2 && (D == 64 || D == 128)) {
+    constexpr int kRowsPerBlock = 8 * (32 / (D / 8));           // 8 warps per block
+    const unsigned blocks = static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock);
+    delta_vec_kernel<T, D><<<blocks, 256, 0, s>>>(p, static_cast<const T*>(dout),
+                                                  static_cast<const T*>(o), delta);
+  } else {
+    delta_kernel<T, D><<<blocks_for(rows), kWarpsPerBlock * 32, 0, s>>>(
+        p, static_cast<const T*>(dout), static_cast<const T*>(o), delta);
+  }
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
