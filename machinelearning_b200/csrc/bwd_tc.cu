@@ -412,7 +412,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // unit's buffer has been released, i.e. after the output products below are issued.
         // At a unit's last iteration the output products go first, so that the epilogue (which
         // has to wait for them) can start as early as possible.
+#if NLFA_VARIANT == 6
+        const bool early = false;
+#else
         const bool early = kSep && have_next && !crossed;
+#endif
         if (early) issue_next_t();
         if (!ok) break;
         NLFA_BTRACE(2, 10);
@@ -446,6 +450,17 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
     bool ok = true;
     int g = 0;                    // global iteration
+    // With two stationary buffers the thread that issued a unit's TMA stores does not wait for
+    // them on the spot (that would hold up every warp at the next hand-off); it releases the
+    // buffer a little later, when the stores have long finished reading shared memory.
+    int pending_xb = -1;
+    auto release_pending = [&]() {
+      if (pending_xb >= 0) {
+        tma_store_wait_read();
+        mbar_arrive(bar(X_EMPTY + pending_xb));
+        pending_xb = -1;
+      }
+    };
     int out_waited = 0;           // OUT_READY phases this thread has observed
     auto wait_out = [&](int needed) {
       while (ok && out_waited < needed) {
@@ -602,6 +617,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(PD_FULL));
+        if (XBUF > 1 && it == 0 && threadIdx.x == 0) release_pending();
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 5);
       }
       if (!ok) break;
@@ -658,8 +674,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                            w.tile * kTile, w.b);
           }
           tma_store_commit();
-          tma_store_wait_read();
-          mbar_arrive(bar(X_EMPTY + xb));        // second arrival: the buffer may be reloaded
+          if (XBUF > 1) {
+            pending_xb = xb;                     // released after the next unit's first iteration
+          } else {
+            tma_store_wait_read();
+            mbar_arrive(bar(X_EMPTY + xb));      // second arrival: the buffer may be reloaded
+          }
         }
       }
       if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 7);
@@ -667,6 +687,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // only after this thread's next PD arrival, which follows in program order
       tc_fence_before();
     }
+    if (threadIdx.x == 0) release_pending();
     }
   }
 

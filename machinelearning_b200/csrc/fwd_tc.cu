@@ -397,6 +397,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t p_addr = tmem_addr(tmem, lane_base, kSepP ? kPBase + 64 * t : 128 * t);
     const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
     int s_count = 0, o_count = 0;      // S_FULL / O_READY phases this thread has observed
+    // With two Q buffers the thread that issued a tile's TMA store does not wait for it on the
+    // spot (that would hold up its whole warpgroup); it releases the buffer one block later,
+    // when the store has long finished reading shared memory.
+    int pending_qb = -1;
+    auto release_pending = [&]() {
+      if (pending_qb >= 0) {
+        tma_store_wait_read();
+        mbar_arrive(bar(Q_EMPTY + pending_qb));
+        pending_qb = -1;
+      }
+    };
     bool ok = true;
     for (int uc = 0; ok; ++uc) {
       const int u = next_unit(uc, ok);
@@ -404,7 +415,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok || u < 0) break;
       const Unit<NT> w = make_unit<NT>(u, p, BH);
       if (!w.valid[t]) {
-        if (row == 0) mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));    // nothing to store for this tile
+        if (row == 0) {
+          release_pending();
+          mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));                // nothing to store for this tile
+        }
         continue;
       }
       const int tile = w.tile0 + t;
@@ -543,6 +557,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(P_FULL + t));
+        if (QBUF > 1 && row == 0) release_pending();
         if (row == 0) NLFA_TRACE_EVENT(t, 5);
       }
       if (!ok) break;
@@ -584,8 +599,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int x = 0; x < kBoxes; ++x)
           tma_store_4d(&tm_o, stage + x * kBoxBytes, 64 * x, w.h, tile * kTile, w.b);
         tma_store_commit();
-        tma_store_wait_read();
-        mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));                // this tile's share of the buffer
+        if (QBUF > 1) {
+          pending_qb = uc % QBUF;                               // released after the next block
+        } else {
+          tma_store_wait_read();
+          mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));              // this tile's share of the buffer
+        }
       }
       if (qpos < p.T)
         p.lse[(static_cast<long long>(w.b) * p.H + w.h) * p.T + qpos] = (m_ref + log2f(l)) * kLn2;
@@ -594,6 +613,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // thread's next P arrival, which follows these loads in program order
       tc_fence_before();
     }
+    if (row == 0) release_pending();
     }
   }
 
