@@ -346,39 +346,76 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         bool o_started[NT];
         for (int t = 0; t < NT; ++t) o_started[t] = false;
-        for (int it = 0; ok && it < w.n_iters; ++it, ++git) {
-          const int s = git % STAGES;
-          const uint32_t ph = (git / STAGES) & 1;
-          const int j = w.block_at(it);
-          const bool have_next = it + 1 < w.n_iters;
-          const int s1 = (git + 1) % STAGES;
-          const uint32_t ph1 = ((git + 1) / STAGES) & 1;
-          const int j1 = have_next ? w.block_at(it + 1) : 0;
-          if (have_next && !(ok = mbar_wait(bar(K_FULL + s1), ph1, wctx, 6))) break;
-          if (kSepP && have_next) {
-            // next S products first: they only wait for the softmax warps' loads of S
-            for (int t = 0; ok && t < NT; ++t)
-              if (w.sees(t, j1)) start_s(qb, t, s1);
+        auto do_pv = [&](int t, int stage) {
+          NLFA_TRACE_EVENT(2, 10 + t);
+          if (!(ok = mbar_wait(bar(P_FULL + t), p_count[t] & 1, wctx, 7))) return;
+          NLFA_TRACE_EVENT(2, 20 + t);
+          ++p_count[t];
+          tc_fence_after();
+          issue_pv(t, stage, o_started[t]);
+          tc_commit(bar(O_READY + t));
+          o_started[t] = true;
+        };
+        if (kSepP && NT == 2) {
+          // Two tiles, P in its own columns.  The issue order per key block is
+          //   S_1(next), PV_0(previous), S_0(next), PV_1(this)
+          // so the first tile's products trail the second tile's by half a step.  That lets the
+          // two softmax warpgroups run out of phase -- one in its exponentials while the other
+          // loads, reduces and stores -- instead of contending for the exponential unit together.
+          for (int it = 0; ok && it < w.n_iters; ++it, ++git) {
+            const int s = git % STAGES;
+            const uint32_t ph = (git / STAGES) & 1;
+            const int j = w.block_at(it);
+            const bool have_next = it + 1 < w.n_iters;
+            const int s1 = (git + 1) % STAGES;
+            const uint32_t ph1 = ((git + 1) / STAGES) & 1;
+            const int j1 = have_next ? w.block_at(it + 1) : 0;
+            const int sp = (git + STAGES - 1) % STAGES;              // stage of the previous block
+            if (have_next && !(ok = mbar_wait(bar(K_FULL + s1), ph1, wctx, 6))) break;
+            if (have_next && w.sees(1, j1)) start_s(qb, 1, s1);
             if (!ok) break;
-            tc_commit(bar(K_EMPTY + s1));
-          }
-          if (!(ok = mbar_wait(bar(V_FULL + s), ph, wctx, 5))) break;
-          for (int t = 0; t < NT; ++t) {
-            if (w.sees(t, j)) {
-              NLFA_TRACE_EVENT(2, 10 + t);
-              if (!(ok = mbar_wait(bar(P_FULL + t), p_count[t] & 1, wctx, 7))) break;
-              NLFA_TRACE_EVENT(2, 20 + t);
-              ++p_count[t];
-              tc_fence_after();
-              issue_pv(t, s, o_started[t]);
-              tc_commit(bar(O_READY + t));
-              o_started[t] = true;
+            if (it > 0) {
+              if (w.sees(0, w.block_at(it - 1))) do_pv(0, sp);
+              if (!ok) break;
+              tc_commit(bar(V_EMPTY + sp));                          // both tiles are done with it
             }
-            if (!kSepP && have_next && w.sees(t, j1)) start_s(qb, t, s1);
+            if (have_next && w.sees(0, j1)) start_s(qb, 0, s1);
+            if (!ok) break;
+            if (have_next) tc_commit(bar(K_EMPTY + s1));
+            if (!(ok = mbar_wait(bar(V_FULL + s), ph, wctx, 5))) break;
+            if (w.sees(1, j)) do_pv(1, s);
           }
-          if (!ok) break;
-          tc_commit(bar(V_EMPTY + s));
-          if (!kSepP && have_next) tc_commit(bar(K_EMPTY + s1));
+          if (ok) {
+            const int sl = (git + STAGES - 1) % STAGES;              // the unit's last block
+            if (w.sees(0, w.block_at(w.n_iters - 1))) do_pv(0, sl);
+            if (ok) tc_commit(bar(V_EMPTY + sl));
+          }
+        } else {
+          for (int it = 0; ok && it < w.n_iters; ++it, ++git) {
+            const int s = git % STAGES;
+            const uint32_t ph = (git / STAGES) & 1;
+            const int j = w.block_at(it);
+            const bool have_next = it + 1 < w.n_iters;
+            const int s1 = (git + 1) % STAGES;
+            const uint32_t ph1 = ((git + 1) / STAGES) & 1;
+            const int j1 = have_next ? w.block_at(it + 1) : 0;
+            if (have_next && !(ok = mbar_wait(bar(K_FULL + s1), ph1, wctx, 6))) break;
+            if (kSepP && have_next) {
+              // next S products first: they only wait for the softmax warps' loads of S
+              for (int t = 0; ok && t < NT; ++t)
+                if (w.sees(t, j1)) start_s(qb, t, s1);
+              if (!ok) break;
+              tc_commit(bar(K_EMPTY + s1));
+            }
+            if (!(ok = mbar_wait(bar(V_FULL + s), ph, wctx, 5))) break;
+            for (int t = 0; ok && t < NT; ++t) {
+              if (w.sees(t, j)) do_pv(t, s);
+              if (ok && !kSepP && have_next && w.sees(t, j1)) start_s(qb, t, s1);
+            }
+            if (!ok) break;
+            tc_commit(bar(V_EMPTY + s));
+            if (!kSepP && have_next) tc_commit(bar(K_EMPTY + s1));
+          }
         }
         if (!ok) break;
         tc_commit(bar(Q_EMPTY + qb));
@@ -423,6 +460,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       const int tile = w.tile0 + t;
       const int qpos = tile * kTile + row;
+#ifndef NLFA_STAGGER_NS
+#define NLFA_STAGGER_NS 650
+#endif
+      // The two softmax warpgroups share the exponential unit.  Left alone they fall into
+      // step, both in their exponentials and then both out of them, and the unit idles half
+      // the time.  The first tile of a pair sees one key block fewer than the second, so it
+      // can afford to start each unit half a block late, which puts the two out of phase.
+      if (NT == 2 && t == 0 && w.valid[1] && NLFA_STAGGER_NS > 0) __nanosleep(NLFA_STAGGER_NS);
       // Online softmax in base 2.  m_ref is the reference exponent (scaled units): P =
       // 2^(x - m_ref).  It starts at the first block's row maximum and is afterwards only
       // raised (with O and l rescaled) when a block's maximum exceeds it by more than 2^8,
@@ -494,21 +539,55 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         bool rescale = false;
         if (first) {
           m_ref = mx;
-        } else {
-          if (mx > m_ref + 8.f) {
-            alpha = fast_exp2(m_ref - mx);     // m_ref == -inf gives 0
-            m_ref = mx;
-            rescale = true;
+        } else if (mx > m_ref + 8.f) {
+          alpha = fast_exp2(m_ref - mx);       // m_ref == -inf gives 0
+          m_ref = mx;
+          rescale = true;
+          l *= alpha;
+        }
+        if (row == 0) NLFA_TRACE_EVENT(t, 31);
+
+        // all exponentials of the row first (P stays in registers) ...
+        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+        const uint64_t negm2 = pack_f2(-m_use, -m_use);
+        uint64_t acc0 = 0ull, acc1 = 0ull;              // packed (0.f, 0.f)
+        uint32_t pk[4][16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (cls[c] == 2) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[c][i] = 0u;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              float e0, e1, e2, e3;
+              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])),
+                              scale2, negm2), e0, e1);
+              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3])),
+                              scale2, negm2), e2, e3);
+              e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
+              acc0 = fadd2(acc0, pack_f2(e0, e1));
+              acc1 = fadd2(acc1, pack_f2(e2, e3));
+              pk[c][i / 2] = Pack2<T>::pack(e0, e1);
+              pk[c][i / 2 + 1] = Pack2<T>::pack(e2, e3);
+            }
           }
-          // the previous block's PV product must be complete before O is rescaled or P is
-          // overwritten; every O_READY phase is observed exactly once, in order
+        }
+        {
+          float lo, hi;
+          unpack_f2(fadd2(acc0, acc1), lo, hi);
+          l += lo + hi;
+        }
+        // ... and only then the hand-off that needs the previous block's PV product to be
+        // complete (O may be rescaled, P's columns may be overwritten); by now it long is.
+        // Every O_READY phase is observed exactly once, in order.
+        if (!first) {
           ok = mbar_wait(bar(O_READY + t), o_count & 1, wctx, 13);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           ++o_count;
           tc_fence_after();
           if (__any_sync(0xffffffffu, rescale)) {
-            l *= alpha;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t orr[32];
@@ -521,38 +600,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
         }
         first = false;
-
-        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        const uint64_t negm2 = pack_f2(-m_use, -m_use);
-        uint64_t acc0 = 0ull, acc1 = 0ull;              // packed (0.f, 0.f)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-          if (cls[c] == 2) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = 0u;
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              float e0, e1, e2, e3;
-              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])),
-                              scale2, negm2), e0, e1);
-              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3])),
-                              scale2, negm2), e2, e3);
-              e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
-              acc0 = fadd2(acc0, pack_f2(e0, e1));
-              acc1 = fadd2(acc1, pack_f2(e2, e3));
-              pk[i / 2] = Pack2<T>::pack(e0, e1);
-              pk[i / 2 + 1] = Pack2<T>::pack(e2, e3);
-            }
-          }
-          tmem_st16(p_addr + 16 * c, pk);
-        }
-        {
-          float lo, hi;
-          unpack_f2(fadd2(acc0, acc1), lo, hi);
-          l += lo + hi;
-        }
+        for (int c = 0; c < 4; ++c) tmem_st16(p_addr + 16 * c, pk[c]);
         if (row == 0) NLFA_TRACE_EVENT(t, 4);
         tc_wait_st();
         tc_fence_before();
