@@ -342,7 +342,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       auto issue_out = [&](int g, uint32_t acc) {
         const int s = g % STAGES;
         const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes, y1 = y0 + L::kTileBytes;
-        // 16-bit operand of k-step kk: 8 TMEM columns per step
+        // 16-bit operand of k-step kk: 8 TMEM columns per step.  The dV and dK steps alternate,
+        // so consecutive instructions never update the same accumulator.
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
           const uint32_t acol = kSep ? 8 * kk : 64 * (kk >> 2) + 8 * (kk & 3);
@@ -352,12 +353,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           } else {
             mma_ts(tmem + kOutCol, tmem + kPCol + acol,
                    make_smem_desc(y1 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
-          }
-        }
-        if (MODE == MODE_DKV) {
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk) {
-            const uint32_t acol = kSep ? 8 * kk : 64 * (kk >> 2) + 8 * (kk & 3);
             mma_ts(tmem + kOutCol + D, tmem + kDsCol + acol,
                    make_smem_desc(y0 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           }
