@@ -32,10 +32,6 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
-#ifndef NLFA_VARIANT
-#define NLFA_VARIANT 0
-#endif
-
 namespace nlfa {
 
 #ifdef NLFA_TRACE
@@ -407,11 +403,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // unit's buffer has been released, i.e. after the output products below are issued.
         // At a unit's last iteration the output products go first, so that the epilogue (which
         // has to wait for them) can start as early as possible.
-#if NLFA_VARIANT == 6
-        const bool early = false;
-#else
         const bool early = kSep && have_next && !crossed;
-#endif
         if (early) issue_next_t();
         if (!ok) break;
         NLFA_BTRACE(2, 10);
@@ -548,9 +540,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             float p0, p1, p2, p3;
             unpack_f2(xa, p0, p1);
             unpack_f2(xb, p2, p3);
-#if NLFA_VARIANT != 4
             p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
-#endif
             if (kMasked) {
               const unsigned o = static_cast<unsigned>(other0 + c - va);   // wraps below va
               const int ox = other0 + c;
@@ -596,13 +586,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           else if (all_out) zero_chunk(ch_c);
           else do_chunk(ch_c, std::true_type{});
         };
-#if NLFA_VARIANT == 5
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { pp[i] = sv[i >> 4][2 * (i & 15)]; dd[i] = dv[i >> 4][2 * (i & 15)]; }
-#else
         chunk(std::integral_constant<int, 0>{});
         chunk(std::integral_constant<int, 1>{});
-#endif
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 4);
         // the previous iteration's output products must be done reading P / dS
         wait_out(g);

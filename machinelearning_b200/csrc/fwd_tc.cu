@@ -24,10 +24,6 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
-#ifndef NLFA_VARIANT
-#define NLFA_VARIANT 0
-#endif
-
 namespace nlfa {
 
 #ifdef NLFA_TRACE
@@ -460,14 +456,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       const int tile = w.tile0 + t;
       const int qpos = tile * kTile + row;
-#ifndef NLFA_STAGGER_NS
-#define NLFA_STAGGER_NS 650
-#endif
-      // The two softmax warpgroups share the exponential unit.  Left alone they fall into
-      // step, both in their exponentials and then both out of them, and the unit idles half
-      // the time.  The first tile of a pair sees one key block fewer than the second, so it
-      // can afford to start each unit half a block late, which puts the two out of phase.
-      if (NT == 2 && t == 0 && w.valid[1] && NLFA_STAGGER_NS > 0) __nanosleep(NLFA_STAGGER_NS);
       // Online softmax in base 2.  m_ref is the reference exponent (scaled units): P =
       // 2^(x - m_ref).  It starts at the first block's row maximum and is afterwards only
       // raised (with O and l rescaled) when a block's maximum exceeds it by more than 2^8,
