@@ -312,7 +312,19 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else {
     // ================================ MMA issuer =============================
-    if (lane == 0) {
+    // The whole warp runs this loop and waits on every barrier together; `leader` marks the one
+    // lane that issues.  All values that feed a descriptor are made provably warp-uniform.
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
+      const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+      auto wait_all = [&](uint32_t b, uint32_t parity, unsigned where) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(b, parity, wctx, where));
+      };
+      auto next_unit_all = [&](int uc, bool& ok) -> int {
+        const int u = __shfl_sync(0xffffffffu, next_unit(uc, ok), 0);
+        ok = __all_sync(0xffffffffu, ok);
+        return u;
+      };
       constexpr uint32_t idesc_t = make_idesc(kBf16, 128, 128, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, 128, D, false, true);
 
@@ -324,16 +336,16 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          mma_ss(tmem + 0, make_smem_desc(x0 + off, 16, 1024), make_smem_desc(y0 + off, 16, 1024),
+          umma_ss(leader, tmem + 0, make_smem_desc(x0 + off, 16, 1024), make_smem_desc(y0 + off, 16, 1024),
                  idesc_t, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          mma_ss(tmem + 128, make_smem_desc(x1 + off, 16, 1024), make_smem_desc(y1 + off, 16, 1024),
+          umma_ss(leader, tmem + 128, make_smem_desc(x1 + off, 16, 1024), make_smem_desc(y1 + off, 16, 1024),
                  idesc_t, kk > 0 ? 1u : 0u);
         }
-        tc_commit(bar(T_FULL));
+        umma_commit(leader, bar(T_FULL));
       };
       auto issue_out = [&](int g, uint32_t acc) {
         const int s = g % STAGES;
@@ -344,29 +356,29 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int kk = 0; kk < kTile / 16; ++kk) {
           const uint32_t acol = kSep ? 8 * kk : 64 * (kk >> 2) + 8 * (kk & 3);
           if (MODE == MODE_DQ) {
-            mma_ts(tmem + kOutCol, tmem + kDsCol + acol,
+            umma_ts(leader, tmem + kOutCol, tmem + kDsCol + acol,
                    make_smem_desc(y0 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           } else {
-            mma_ts(tmem + kOutCol, tmem + kPCol + acol,
+            umma_ts(leader, tmem + kOutCol, tmem + kPCol + acol,
                    make_smem_desc(y1 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
-            mma_ts(tmem + kOutCol + D, tmem + kDsCol + acol,
+            umma_ts(leader, tmem + kOutCol + D, tmem + kDsCol + acol,
                    make_smem_desc(y0 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           }
         }
-        tc_commit(bar(OUT_READY));
-        tc_commit(bar(Y_EMPTY + s));
+        umma_commit(leader, bar(OUT_READY));
+        umma_commit(leader, bar(Y_EMPTY + s));
       };
 
       // cursor over (unit, iteration); `nxt` runs one global iteration ahead of `cur`
       bool ok = true;
       int uc = 0;                       // units fetched so far
-      int cur_u = next_unit(uc, ok);
+      int cur_u = next_unit_all(uc, ok);
       int cur_n = 0, cur_it = 0, cur_xb = 0;
       if (ok && cur_u >= 0) {
         cur_n = make_bwd_unit<MODE>(cur_u, p).n_iters;
         cur_xb = uc % XBUF;
-        ok = mbar_wait(bar(X_FULL + cur_xb), (uc / XBUF) & 1, wctx, 32);
-        if (ok) ok = mbar_wait(bar(Y_FULL + 0), 0, wctx, 33);
+        ok = wait_all(bar(X_FULL + cur_xb), (uc / XBUF) & 1, 32);
+        if (ok) ok = wait_all(bar(Y_FULL + 0), 0, 33);
         if (ok) {
           tc_fence_after();
           issue_t(cur_xb, 0);
@@ -379,7 +391,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         bool crossed = false;
         if (nxt_it == cur_n) {
           ++uc;
-          nxt_u = next_unit(uc, ok);
+          nxt_u = next_unit_all(uc, ok);
           if (!ok) break;
           nxt_it = 0;
           crossed = true;
@@ -390,13 +402,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         const bool have_next = nxt_u >= 0;
         auto issue_next_t = [&]() {
-          if (crossed) ok = mbar_wait(bar(X_FULL + nxt_xb), (uc / XBUF) & 1, wctx, 32);
-          if (ok) ok = mbar_wait(bar(Y_FULL + (g + 1) % STAGES), ((g + 1) / STAGES) & 1, wctx, 33);
-          if (ok && kSep) ok = mbar_wait(bar(T_CONSUMED), g & 1, wctx, 37);
+          if (crossed) ok = wait_all(bar(X_FULL + nxt_xb), (uc / XBUF) & 1, 32);
+          if (ok) ok = wait_all(bar(Y_FULL + (g + 1) % STAGES), ((g + 1) / STAGES) & 1, 33);
+          if (ok && kSep) ok = wait_all(bar(T_CONSUMED), g & 1, 37);
           if (ok) {
             tc_fence_after();
             issue_t(nxt_xb, g + 1);
-            NLFA_BTRACE(2, 20);
+            if (leader) NLFA_BTRACE(2, 20);
           }
         };
         // With a single stationary buffer the next unit's tiles can only be loaded once this
@@ -406,12 +418,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const bool early = kSep && have_next && !crossed;
         if (early) issue_next_t();
         if (!ok) break;
-        NLFA_BTRACE(2, 10);
-        if (!(ok = mbar_wait(bar(PD_FULL), g & 1, wctx, 34))) break;
-        NLFA_BTRACE(2, 11);
+        if (leader) NLFA_BTRACE(2, 10);
+        if (!(ok = wait_all(bar(PD_FULL), g & 1, 34))) break;
+        if (leader) NLFA_BTRACE(2, 11);
         tc_fence_after();
         issue_out(g, cur_it > 0 ? 1u : 0u);
-        if (cur_it + 1 == cur_n) tc_commit(bar(X_EMPTY + cur_xb));
+        if (cur_it + 1 == cur_n) umma_commit(leader, bar(X_EMPTY + cur_xb));
         if (!early && have_next) issue_next_t();
         if (!ok) break;
         cur_u = nxt_u;
@@ -572,10 +584,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // visible (plain path), entirely masked (zeros, no arithmetic) or mixed.
         auto chunk = [&](auto ch_c) {
           constexpr int ch = decltype(ch_c)::value;
-          if (full) {
-            do_chunk(ch_c, std::false_type{});
-            return;
-          }
           const int x0 = other0 + 32 * ch, x1 = x0 + 31;
           const long long hi = static_cast<long long>(va) + vw;          // last visible position
           const bool in = (x0 >= va && x1 <= hi) || x1 < vsink;
@@ -586,8 +594,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           else if (all_out) zero_chunk(ch_c);
           else do_chunk(ch_c, std::true_type{});
         };
-        chunk(std::integral_constant<int, 0>{});
-        chunk(std::integral_constant<int, 1>{});
+        if (full) {
+          // interior blocks: one straight-line pass over all 64 columns (branches between the
+          // chunks would drain the exponential unit's pipeline at every chunk)
+          do_chunk(std::integral_constant<int, 0>{}, std::false_type{});
+          do_chunk(std::integral_constant<int, 1>{}, std::false_type{});
+        } else {
+          chunk(std::integral_constant<int, 0>{});
+          chunk(std::integral_constant<int, 1>{});
+        }
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 4);
         // the previous iteration's output products must be done reading P / dS
         wait_out(g);

@@ -73,7 +73,7 @@ struct FwdSmem {
   // barriers (8 bytes each): q_full[QBUF], q_empty[QBUF], s_full[NT], s_consumed[NT],
   // p_full[NT], o_ready[NT], k_full[S], k_empty[S], v_full[S], v_empty[S], sched_full[kRing]
   static constexpr int kRing = 8;
-  static constexpr int kNumBars = 2 * QBUF + 4 * NT + 4 * STAGES + kRing;
+  static constexpr int kNumBars = 2 * QBUF + 5 * NT + 4 * STAGES + kRing;
   static constexpr int kSched = kBar + 8 * kNumBars;        // ring of unit indices
   static constexpr int kTmemSlot = kSched + 4 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
@@ -150,6 +150,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr bool kSepP = NT * (128 + D + 64) <= 512;      // P has columns of its own
   constexpr uint32_t kPBase = NT * (128 + D);
   constexpr int kRing = L::kRing;
+#ifndef NLFA_PINGPONG
+#define NLFA_PINGPONG 0
+#endif
+  constexpr bool kPingPong = NT == 2 && NLFA_PINGPONG;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -167,7 +171,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr int Q_FULL = 0, Q_EMPTY = QBUF, S_FULL = 2 * QBUF, S_CONSUMED = S_FULL + NT,
                 P_FULL = S_CONSUMED + NT, O_READY = P_FULL + NT, K_FULL = O_READY + NT,
                 K_EMPTY = K_FULL + STAGES, V_FULL = K_EMPTY + STAGES, V_EMPTY = V_FULL + STAGES,
-                SCHED_FULL = V_EMPTY + STAGES;
+                SCHED_FULL = V_EMPTY + STAGES, XU_TOKEN = SCHED_FULL + kRing;
   volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
@@ -189,6 +193,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(bar(O_READY + t), 1);
     }
     for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
+    for (int t = 0; t < NT; ++t) mbar_init(bar(XU_TOKEN + t), 4);     // one arrival per warp
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(K_FULL + s), 1);
       mbar_init(bar(K_EMPTY + s), 1);
@@ -281,7 +286,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else if (warp == 4 * NT + 1) {
     // ================================ MMA issuer =============================
-    if (lane == 0) {
+    // The whole warp runs this loop and waits on every barrier together; `leader` marks the one
+    // lane that issues.  All values that feed a descriptor are made provably warp-uniform.
+    {
+      const uint32_t leader = elect_one() ? 1u : 0u;
+#ifdef NLFA_NO_MMA
+      const uint32_t mma_leader = 0u;      // timing experiment: hand-offs without the products
+#else
+      const uint32_t mma_leader = leader;
+#endif
+      const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+      auto wait_all = [&](uint32_t b, uint32_t parity, unsigned where) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait(b, parity, wctx, where));
+      };
       constexpr uint32_t idesc_qk = make_idesc(kBf16, 128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc(kBf16, 128, D, false, true);
 
@@ -291,7 +308,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          mma_ss(tmem + 128 * t, make_smem_desc(qa + off, 16, 1024),
+          umma_ss(mma_leader, tmem + 128 * t, make_smem_desc(qa + off, 16, 1024),
                  make_smem_desc(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
@@ -301,7 +318,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
           // 16 keys per step: 8 packed TMEM columns of P, 16 rows (2048 bytes) of V
-          mma_ts(tmem + 128 * NT + D * t, tmem + pa + 8 * kk,
+          umma_ts(mma_leader, tmem + 128 * NT + D * t, tmem + pa + 8 * kk,
                  make_smem_desc(va + kk * 2048, kBoxBytes, 1024), idesc_pv,
                  (accumulate || kk > 0) ? 1u : 0u);
         }
@@ -315,41 +332,45 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // registers (only needed when P has its own columns; otherwise the P hand-off implies it)
       auto start_s = [&](int qb, int t, int s) {
         if (kSepP && s_issued[t] > 0)
-          ok = mbar_wait(bar(S_CONSUMED + t), (s_issued[t] - 1) & 1, wctx, 12);
+          ok = wait_all(bar(S_CONSUMED + t), (s_issued[t] - 1) & 1, 12);
         if (!ok) return;
         tc_fence_after();
+        if (leader) NLFA_TRACE_EVENT(2, 40 + t);
         issue_s(qb, t, s);
-        tc_commit(bar(S_FULL + t));
+        if (leader) NLFA_TRACE_EVENT(2, 50 + t);
+        umma_commit(leader, bar(S_FULL + t));
         ++s_issued[t];
       };
       for (int uc = 0; ok; ++uc) {
-        const int u = next_unit(uc, ok);
+        const int u = __shfl_sync(0xffffffffu, next_unit(uc, ok), 0);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok || u < 0) break;
         const Unit<NT> w = make_unit<NT>(u, p, BH);
         const int qb = uc % QBUF;
-        NLFA_TRACE_EVENT(2, 1);
-        if (!(ok = mbar_wait(bar(Q_FULL + qb), (uc / QBUF) & 1, wctx, 3))) break;
-        NLFA_TRACE_EVENT(2, 2);
+        if (leader) NLFA_TRACE_EVENT(2, 1);
+        if (!(ok = wait_all(bar(Q_FULL + qb), (uc / QBUF) & 1, 3))) break;
+        if (leader) NLFA_TRACE_EVENT(2, 2);
         {
           const int s0 = git % STAGES;
-          if (!(ok = mbar_wait(bar(K_FULL + s0), (git / STAGES) & 1, wctx, 4))) break;
+          if (!(ok = wait_all(bar(K_FULL + s0), (git / STAGES) & 1, 4))) break;
           const int j0 = w.block_at(0);
           for (int t = 0; ok && t < NT; ++t)
             if (w.sees(t, j0)) start_s(qb, t, s0);
           if (!ok) break;
-          tc_commit(bar(K_EMPTY + s0));
-          NLFA_TRACE_EVENT(2, 3);
+          umma_commit(leader, bar(K_EMPTY + s0));
+          if (leader) NLFA_TRACE_EVENT(2, 3);
         }
         bool o_started[NT];
         for (int t = 0; t < NT; ++t) o_started[t] = false;
         auto do_pv = [&](int t, int stage) {
-          NLFA_TRACE_EVENT(2, 10 + t);
-          if (!(ok = mbar_wait(bar(P_FULL + t), p_count[t] & 1, wctx, 7))) return;
-          NLFA_TRACE_EVENT(2, 20 + t);
+          if (leader) NLFA_TRACE_EVENT(2, 10 + t);
+          if (!(ok = wait_all(bar(P_FULL + t), p_count[t] & 1, 7))) return;
+          if (leader) NLFA_TRACE_EVENT(2, 20 + t);
           ++p_count[t];
           tc_fence_after();
           issue_pv(t, stage, o_started[t]);
-          tc_commit(bar(O_READY + t));
+          if (leader) NLFA_TRACE_EVENT(2, 30 + t);
+          umma_commit(leader, bar(O_READY + t));
           o_started[t] = true;
         };
         if (kSepP && NT == 2) {
@@ -367,24 +388,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const uint32_t ph1 = ((git + 1) / STAGES) & 1;
             const int j1 = have_next ? w.block_at(it + 1) : 0;
             const int sp = (git + STAGES - 1) % STAGES;              // stage of the previous block
-            if (have_next && !(ok = mbar_wait(bar(K_FULL + s1), ph1, wctx, 6))) break;
+            if (have_next && !(ok = wait_all(bar(K_FULL + s1), ph1, 6))) break;
             if (have_next && w.sees(1, j1)) start_s(qb, 1, s1);
             if (!ok) break;
             if (it > 0) {
               if (w.sees(0, w.block_at(it - 1))) do_pv(0, sp);
               if (!ok) break;
-              tc_commit(bar(V_EMPTY + sp));                          // both tiles are done with it
+              umma_commit(leader, bar(V_EMPTY + sp));                          // both tiles are done with it
             }
             if (have_next && w.sees(0, j1)) start_s(qb, 0, s1);
             if (!ok) break;
-            if (have_next) tc_commit(bar(K_EMPTY + s1));
-            if (!(ok = mbar_wait(bar(V_FULL + s), ph, wctx, 5))) break;
+            if (have_next) umma_commit(leader, bar(K_EMPTY + s1));
+            if (!(ok = wait_all(bar(V_FULL + s), ph, 5))) break;
             if (w.sees(1, j)) do_pv(1, s);
           }
           if (ok) {
             const int sl = (git + STAGES - 1) % STAGES;              // the unit's last block
             if (w.sees(0, w.block_at(w.n_iters - 1))) do_pv(0, sl);
-            if (ok) tc_commit(bar(V_EMPTY + sl));
+            if (ok) umma_commit(leader, bar(V_EMPTY + sl));
           }
         } else {
           for (int it = 0; ok && it < w.n_iters; ++it, ++git) {
@@ -395,26 +416,26 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const int s1 = (git + 1) % STAGES;
             const uint32_t ph1 = ((git + 1) / STAGES) & 1;
             const int j1 = have_next ? w.block_at(it + 1) : 0;
-            if (have_next && !(ok = mbar_wait(bar(K_FULL + s1), ph1, wctx, 6))) break;
+            if (have_next && !(ok = wait_all(bar(K_FULL + s1), ph1, 6))) break;
             if (kSepP && have_next) {
               // next S products first: they only wait for the softmax warps' loads of S
               for (int t = 0; ok && t < NT; ++t)
                 if (w.sees(t, j1)) start_s(qb, t, s1);
               if (!ok) break;
-              tc_commit(bar(K_EMPTY + s1));
+              umma_commit(leader, bar(K_EMPTY + s1));
             }
-            if (!(ok = mbar_wait(bar(V_FULL + s), ph, wctx, 5))) break;
+            if (!(ok = wait_all(bar(V_FULL + s), ph, 5))) break;
             for (int t = 0; ok && t < NT; ++t) {
               if (w.sees(t, j)) do_pv(t, s);
               if (ok && !kSepP && have_next && w.sees(t, j1)) start_s(qb, t, s1);
             }
             if (!ok) break;
-            tc_commit(bar(V_EMPTY + s));
-            if (!kSepP && have_next) tc_commit(bar(K_EMPTY + s1));
+            umma_commit(leader, bar(V_EMPTY + s));
+            if (!kSepP && have_next) umma_commit(leader, bar(K_EMPTY + s1));
           }
         }
         if (!ok) break;
-        tc_commit(bar(Q_EMPTY + qb));
+        umma_commit(leader, bar(Q_EMPTY + qb));
       }
     }
   }
@@ -442,6 +463,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     };
     bool ok = true;
+    // The two softmax warpgroups share the exponential unit, and a block's exponentials are
+    // most of its work.  Left alone the warpgroups fall into step -- both in their exponentials,
+    // then both out of them -- and the unit idles half the time.  A token makes them take
+    // strict turns instead: a warpgroup computes its exponentials only while it holds the token
+    // and hands it over as soon as they are done, so one loads, reduces and stores while the
+    // other exponentiates.  Turns follow the MMA issuer's order (kLead first), one turn per
+    // (unit, key block) whether or not the tile sees the block.
+    constexpr int kLead = kSepP ? 1 : 0;
+    int turn = 0;
+    auto token_acquire = [&]() {
+      if (!kPingPong) return;
+      if (t == kLead) {
+        if (turn > 0) ok = mbar_wait(bar(XU_TOKEN + t), (turn - 1) & 1, wctx, 14);
+      } else {
+        ok = mbar_wait(bar(XU_TOKEN + t), turn & 1, wctx, 14);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+    };
+    auto token_release = [&]() {
+      if (!kPingPong) return;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(XU_TOKEN + (t ^ 1)));
+      ++turn;
+    };
     for (int uc = 0; ok; ++uc) {
       const int u = next_unit(uc, ok);
       ok = __all_sync(0xffffffffu, ok);
@@ -451,6 +496,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (row == 0) {
           release_pending();
           mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));                // nothing to store for this tile
+        }
+        for (int it = 0; ok && it < w.n_iters; ++it) {
+          token_acquire();
+          token_release();
         }
         continue;
       }
@@ -472,7 +521,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const unsigned vw = static_cast<unsigned>(qpos - va);
       for (int it = 0; it < w.n_iters; ++it) {
         const int j = w.block_at(it);
-        if (!tile_sees_block(w.tr[t], j)) continue;
+        if (!tile_sees_block(w.tr[t], j)) {
+          token_acquire();
+          token_release();
+          if (!ok) break;
+          continue;
+        }
         if (row == 0) NLFA_TRACE_EVENT(t, 1);
         ok = mbar_wait(bar(S_FULL + t), s_count & 1, wctx, 8);
         ok = __all_sync(0xffffffffu, ok);
@@ -489,31 +543,30 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_before();
         mbar_arrive(bar(S_CONSUMED + t));
 
-        // Boundary blocks: each 32-column chunk is, for the whole warp, entirely visible (0),
-        // mixed (1: masked entries become -inf) or entirely masked (2: skipped).
+        // Boundary blocks: a 32-column chunk that the whole warp sees entirely is left alone,
+        // the others pay per-element tests.  Masked scores
+        // become -inf and flow through the straight-line code below as zeros: skipping them
+        // instead would put branches between the chunks, and the exponentials of a chunk on
+        // its own are too few to cover the unit's latency (measured: 1760 clocks per row with
+        // per-chunk branches against 1130 without).
         const int k0 = j * kTile;
-        int cls[4] = {0, 0, 0, 0};
         if (!block_fully_visible(tile, j, p.window, p.sinks)) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int x0 = k0 + 32 * c, x1 = x0 + 31;
             const bool in = (x0 >= va && x1 <= qpos) || x1 < vsink;
-            const bool out = (x1 < va || x0 > qpos) && x0 >= vsink;
-            cls[c] = __all_sync(0xffffffffu, in) ? 0 : (__all_sync(0xffffffffu, out) ? 2 : 1);
-            if (cls[c] == 1) {
-              const unsigned o = static_cast<unsigned>(x0 - va);          // wraps below va
+            if (__all_sync(0xffffffffu, in)) continue;
+            const unsigned o = static_cast<unsigned>(x0 - va);            // wraps below va
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (!(o + static_cast<unsigned>(i) <= vw || x0 + i < vsink))
-                  sv[c][i] = __float_as_uint(-INFINITY);
-            }
+            for (int i = 0; i < 32; ++i)
+              if (!(o + static_cast<unsigned>(i) <= vw || x0 + i < vsink))
+                sv[c][i] = __float_as_uint(-INFINITY);
           }
         }
-        // row maximum of the raw scores: two chains of 3-input max per chunk
+        // row maximum of the raw scores: two chains of 3-input max
         float b0 = -INFINITY, b1 = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          if (cls[c] == 2) continue;
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             b0 = fmax3(b0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
@@ -533,32 +586,37 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           rescale = true;
           l *= alpha;
         }
+        token_acquire();
+        if (!ok) break;
         if (row == 0) NLFA_TRACE_EVENT(t, 31);
 
         // all exponentials of the row first (P stays in registers) ...
         const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        const uint64_t negm2 = pack_f2(-m_use, -m_use);
+        uint64_t negm2 = pack_f2(-m_use, -m_use);
         uint64_t acc0 = 0ull, acc1 = 0ull;              // packed (0.f, 0.f)
         uint32_t pk[4][16];
+#ifndef NLFA_EXP_GROUP
+#define NLFA_EXP_GROUP 2
+#endif
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          if (cls[c] == 2) {
+          // Scheduling fence between groups of chunks: the next group's inputs are made to
+          // depend on the last word of the previous one.  Without it the compiler interleaves
+          // all 128 elements and runs out of registers; with a fence after every chunk (or a
+          // branch) the exponential unit drains four times per row.
+          if (c > 0 && c % NLFA_EXP_GROUP == 0) asm volatile("" : "+l"(negm2) : "r"(pk[c - 1][15]));
 #pragma unroll
-            for (int i = 0; i < 16; ++i) pk[c][i] = 0u;
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              float e0, e1, e2, e3;
-              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])),
-                              scale2, negm2), e0, e1);
-              unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3])),
-                              scale2, negm2), e2, e3);
-              e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
-              acc0 = fadd2(acc0, pack_f2(e0, e1));
-              acc1 = fadd2(acc1, pack_f2(e2, e3));
-              pk[c][i / 2] = Pack2<T>::pack(e0, e1);
-              pk[c][i / 2 + 1] = Pack2<T>::pack(e2, e3);
-            }
+          for (int i = 0; i < 32; i += 4) {
+            float e0, e1, e2, e3;
+            unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1])),
+                            scale2, negm2), e0, e1);
+            unpack_f2(ffma2(pack_f2(__uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3])),
+                            scale2, negm2), e2, e3);
+            e0 = fast_exp2(e0); e1 = fast_exp2(e1); e2 = fast_exp2(e2); e3 = fast_exp2(e3);
+            acc0 = fadd2(acc0, pack_f2(e0, e1));
+            acc1 = fadd2(acc1, pack_f2(e2, e3));
+            pk[c][i / 2] = Pack2<T>::pack(e0, e1);
+            pk[c][i / 2 + 1] = Pack2<T>::pack(e2, e3);
           }
         }
         {
@@ -566,6 +624,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           unpack_f2(fadd2(acc0, acc1), lo, hi);
           l += lo + hi;
         }
+        token_release();
+        if (row == 0) NLFA_TRACE_EVENT(t, 32);
         // ... and only then the hand-off that needs the previous block's PV product to be
         // complete (O may be rescaled, P's columns may be overwritten); by now it long is.
         // Every O_READY phase is observed exactly once, in order.
