@@ -283,6 +283,17 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (lane == 0) ok = mbar_wait(bar(Y_EMPTY + s), ph ^ 1, wctx, 31);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
         if (!ok) break;
+        // The tile loads go out first; the per-row vectors (plain loads, a full memory latency)
+        // follow while they are in flight, and the arrival that completes the stage comes last.
+        if (lane == 0) {
+          mbar_expect_tx(bar(Y_FULL + s), 2 * L::kTileBytes);
+          const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes;
+          for (int x = 0; x < kBoxes; ++x) {
+            tma_load_4d(y0 + x * kBoxBytes, my0, bar(Y_FULL + s), 64 * x, yh, idx * kTile, w.b);
+            tma_load_4d(y0 + L::kTileBytes + x * kBoxBytes, my1, bar(Y_FULL + s), 64 * x, yh,
+                        idx * kTile, w.b);
+          }
+        }
         if (MODE == MODE_DKV) {
           // negated base-2 logsumexp and negated Delta of the streamed query tile
           float* vec = reinterpret_cast<float*>(gen + L::kVec + s * 1024);
@@ -297,15 +308,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
           __syncwarp();
         }
-        if (lane == 0) {
-          mbar_arrive_expect_tx(bar(Y_FULL + s), 2 * L::kTileBytes);
-          const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes;
-          for (int x = 0; x < kBoxes; ++x) {
-            tma_load_4d(y0 + x * kBoxBytes, my0, bar(Y_FULL + s), 64 * x, yh, idx * kTile, w.b);
-            tma_load_4d(y0 + L::kTileBytes + x * kBoxBytes, my1, bar(Y_FULL + s), 64 * x, yh,
-                        idx * kTile, w.b);
-          }
-        }
+        if (lane == 0) mbar_arrive(bar(Y_FULL + s));
       }
       if (ok && u_next == -2) u_next = fetch_unit(uc + 1);
       u = u_next;
@@ -809,8 +812,8 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D == 64) {
-    return bf16 ? launch_both<__nv_bfloat16, 64, 3, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
-                : launch_both<__half, 64, 3, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
+    return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
+                : launch_both<__half, 64, 4, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
   }
   return bf16 ? launch_both<__nv_bfloat16, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
               : launch_both<__half, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
