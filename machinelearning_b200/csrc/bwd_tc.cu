@@ -40,9 +40,9 @@ __device__ long long g_btrace[4][1024];
 __device__ int g_btrace_n[4];
 #define NLFA_BTRACE(role, tag)                                        \
   do {                                                                \
-    if (blockIdx.x == 0 && tr_n < 512) {                              \
-      tr_buf[((role) * 512 + tr_n) * 2] = clock64();                  \
-      tr_buf[((role) * 512 + tr_n) * 2 + 1] = (tag);                  \
+    if (blockIdx.x == 0 && tr_n < 256) {                              \
+      tr_buf[((role) * 256 + tr_n) * 2] = clock64();                  \
+      tr_buf[((role) * 256 + tr_n) * 2 + 1] = (tag);                  \
       ++tr_n;                                                         \
       g_btrace_n[role] = tr_n;                                        \
     }                                                                 \
@@ -86,13 +86,13 @@ struct BwdSmem {
   //           sched_full[kRing], y_full[S], y_empty[S]
   static constexpr int kRing = 8;
   static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES;
-  static constexpr int kSched = kBar + 8 * kNumBars;            // ring of unit indices
-  static constexpr int kTmemSlot = kSched + 4 * kRing;
+  static constexpr int kSched = (kBar + 8 * kNumBars + 15) / 16 * 16;   // ring of unit descriptors (8 ints each)
+  static constexpr int kTmemSlot = kSched + 32 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
 #ifdef NLFA_TRACE
   static constexpr int kTrace = (kTotal + 15) / 16 * 16;
-  static constexpr int kDynamic = kTrace + 4 * 512 * 16 + 1024;
+  static constexpr int kDynamic = kTrace + 4 * 256 * 16 + 1024;
 #else
   static constexpr int kDynamic = kTotal + 1024;
 #endif
@@ -214,9 +214,18 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   // Every role reads the unit index of its uc-th unit from the ring the producer
   // fills; a negative index means there is no more work.
-  auto next_unit = [&](int uc, bool& ok) -> int {
+  // The producer works the descriptor out once (it takes several integer divisions) and
+  // publishes all of it: {u, tile, b, h, hk, s_lo, n_inner, extra (dQ) | n_iters (dK/dV)}.
+  auto next_unit = [&](int uc, bool& ok, BwdUnit<MODE>& w) -> int {
     ok = mbar_wait(bar(SCHED_FULL + (uc % kRing)), (uc / kRing) & 1, wctx, 40);
-    return ok ? sched_ring[uc % kRing] : -1;
+    if (!ok) return -1;
+    const int4 a = *reinterpret_cast<const int4*>(const_cast<const int*>(sched_ring) + 8 * (uc % kRing));
+    const int4 b = *reinterpret_cast<const int4*>(const_cast<const int*>(sched_ring) + 8 * (uc % kRing) + 4);
+    w.tile = a.y; w.b = a.z; w.h = a.w;
+    w.hk = b.x; w.s_lo = b.y; w.n_inner = b.z;
+    w.extra = MODE == MODE_DQ ? b.w : 0;
+    w.n_iters = MODE == MODE_DQ ? b.z : b.w;
+    return a.x;
   };
 
   if (warp >= 8) {
@@ -244,10 +253,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (lane == 0) {
         u = static_cast<int>(atomicAdd(&p.sched[0], 1u));
         if (u >= p.total_units) u = -1;
-        sched_ring[uc % kRing] = u;
+        BwdUnit<MODE> w{};
+        if (u >= 0) w = make_bwd_unit<MODE>(u, p);
+        volatile int* e = sched_ring + 8 * (uc % kRing);
+        e[0] = u; e[1] = w.tile; e[2] = w.b; e[3] = w.h;
+        e[4] = w.hk; e[5] = w.s_lo; e[6] = w.n_inner; e[7] = MODE == MODE_DQ ? w.extra : w.n_iters;
         mbar_arrive(bar(SCHED_FULL + (uc % kRing)));
         if (u >= 0) {
-          const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
           const int xb = uc % XBUF;
           ok = mbar_wait(bar(X_EMPTY + xb), ((uc / XBUF) & 1) ^ 1, wctx, 30);
           if (ok) {
@@ -267,18 +279,21 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     };
     int u = fetch_unit(0);
     for (int uc = 0; ok && u >= 0; ++uc) {
-      const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
+      BwdUnit<MODE> w;
+      next_unit(uc, ok, w);                      // published by this warp: never waits
+      if (!ok) break;
       // The next unit's stationary tiles are requested once this unit's first streamed tiles
       // are on their way (with one stationary buffer: only when this unit has released it).
       int u_next = -2;
       const int prefetch_at = XBUF > 1 ? (w.n_iters < STAGES ? w.n_iters : STAGES) : w.n_iters;
-      for (int it = 0; ok && it < w.n_iters; ++it, ++git) {
+      int inner = 0, g = 0;                       // it = g * n_inner + inner
+      for (int it = 0; ok && it < w.n_iters; ++it, ++git, ++inner) {
         if (it == prefetch_at) u_next = fetch_unit(uc + 1);
         if (!ok) break;
+        if (inner == w.n_inner) { inner = 0; ++g; }
         const int s = git % STAGES;
         const uint32_t ph = (git / STAGES) & 1;
-        const int g = it / w.n_inner;
-        const int idx = w.streamed_index(it - g * w.n_inner);
+        const int idx = w.streamed_index(inner);
         const int yh = MODE == MODE_DQ ? w.hk : w.h + g;
         if (lane == 0) ok = mbar_wait(bar(Y_EMPTY + s), ph ^ 1, wctx, 31);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -323,8 +338,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       auto wait_all = [&](uint32_t b, uint32_t parity, unsigned where) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(b, parity, wctx, where));
       };
-      auto next_unit_all = [&](int uc, bool& ok) -> int {
-        const int u = __shfl_sync(0xffffffffu, next_unit(uc, ok), 0);
+      auto next_unit_all = [&](int uc, bool& ok, int& n_iters) -> int {
+        BwdUnit<MODE> w{};
+        const int u = __shfl_sync(0xffffffffu, next_unit(uc, ok, w), 0);
+        n_iters = __shfl_sync(0xffffffffu, w.n_iters, 0);
         ok = __all_sync(0xffffffffu, ok);
         return u;
       };
@@ -375,10 +392,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // cursor over (unit, iteration); `nxt` runs one global iteration ahead of `cur`
       bool ok = true;
       int uc = 0;                       // units fetched so far
-      int cur_u = next_unit_all(uc, ok);
       int cur_n = 0, cur_it = 0, cur_xb = 0;
+      int cur_u = next_unit_all(uc, ok, cur_n);
       if (ok && cur_u >= 0) {
-        cur_n = make_bwd_unit<MODE>(cur_u, p).n_iters;
         cur_xb = uc % XBUF;
         ok = wait_all(bar(X_FULL + cur_xb), (uc / XBUF) & 1, 32);
         if (ok) ok = wait_all(bar(Y_FULL + 0), 0, 33);
@@ -394,14 +410,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         bool crossed = false;
         if (nxt_it == cur_n) {
           ++uc;
-          nxt_u = next_unit_all(uc, ok);
+          nxt_u = next_unit_all(uc, ok, nxt_n);
           if (!ok) break;
           nxt_it = 0;
           crossed = true;
-          if (nxt_u >= 0) {
-            nxt_n = make_bwd_unit<MODE>(nxt_u, p).n_iters;
-            nxt_xb = uc % XBUF;
-          }
+          if (nxt_u >= 0) nxt_xb = uc % XBUF;
         }
         const bool have_next = nxt_u >= 0;
         auto issue_next_t = [&]() {
@@ -463,6 +476,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         pending_xb = -1;
       }
     };
+    float pre_lse = 0.f, pre_delta = 0.f;     // dQ: row statistics of the next unit
     int out_waited = 0;           // OUT_READY phases this thread has observed
     auto wait_out = [&](int needed) {
       while (ok && out_waited < needed) {
@@ -472,10 +486,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     };
     for (int uc = 0; ok; ++uc) {
-      const int u = next_unit(uc, ok);
+      BwdUnit<MODE> w;
+      const int u = next_unit(uc, ok, w);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok || u < 0) break;
-      const BwdUnit<MODE> w = make_bwd_unit<MODE>(u, p);
       const int pos = w.tile * kTile + row;            // query position (dQ) or key position (dK/dV)
 
       // Columns this row can see, as positions of the streamed index: [va, va + vw], plus
@@ -494,16 +508,22 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       uint64_t negl2_row = pack_f2(-INFINITY, -INFINITY), negd_row = 0ull;
       if (MODE == MODE_DQ && pos < p.T) {
-        const long long idx = (static_cast<long long>(w.b) * p.H + w.h) * p.T + pos;
-        const float l2 = -p.lse[idx] * kLog2e, dl = -p.delta[idx];
-        negl2_row = pack_f2(l2, l2);
-        negd_row = pack_f2(dl, dl);
+        if (uc > 0) {                       // fetched during the previous unit's epilogue
+          negl2_row = pack_f2(-pre_lse * kLog2e, -pre_lse * kLog2e);
+          negd_row = pack_f2(-pre_delta, -pre_delta);
+        } else {
+          const long long idx = (static_cast<long long>(w.b) * p.H + w.h) * p.T + pos;
+          const float l2 = -p.lse[idx] * kLog2e, dl = -p.delta[idx];
+          negl2_row = pack_f2(l2, l2);
+          negd_row = pack_f2(dl, dl);
+        }
       }
 
-      for (int it = 0; it < w.n_iters; ++it, ++g) {
+      int inner = 0;
+      for (int it = 0; it < w.n_iters; ++it, ++g, ++inner) {
+        if (inner == w.n_inner) inner = 0;
         const int s = g % STAGES;
-        const int gg = it / w.n_inner;
-        const int idx = w.streamed_index(it - gg * w.n_inner);
+        const int idx = w.streamed_index(inner);
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 1);
         ok = mbar_wait(bar(T_FULL), g & 1, wctx, 35);
         ok = __all_sync(0xffffffffu, ok);
@@ -621,6 +641,20 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok) break;
 
       if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 6);
+      if (MODE == MODE_DQ) {
+        // The next unit's row statistics are requested now (its descriptor is published well
+        // ahead), so that their memory latency passes during this unit's epilogue.
+        BwdUnit<MODE> wn;
+        const int un = next_unit(uc + 1, ok, wn);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int pos_n = wn.tile * kTile + row;
+        if (un >= 0 && pos_n < p.T) {
+          const long long idx = (static_cast<long long>(wn.b) * p.H + wn.h) * p.T + pos_n;
+          pre_lse = p.lse[idx];
+          pre_delta = p.delta[idx];
+        }
+      }
       wait_out(g);                 // this unit's last output product
       if (!ok) break;
       tc_fence_after();
@@ -698,7 +732,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
 #ifdef NLFA_TRACE
   if (blockIdx.x == 0)
-    for (int i = threadIdx.x; i < 4 * 1024; i += blockDim.x) (&g_btrace[0][0])[i] = tr_buf[i];
+    for (int i = threadIdx.x; i < 4 * 512; i += blockDim.x) (&g_btrace[0][0])[i] = tr_buf[i];
 #endif
   // scheduler bookkeeping: the last CTA of the launch to get here re-arms the counters
   if (threadIdx.x == 0) {
