@@ -74,8 +74,8 @@ struct FwdSmem {
   // p_full[NT], o_ready[NT], k_full[S], k_empty[S], v_full[S], v_empty[S], sched_full[kRing]
   static constexpr int kRing = 8;
   static constexpr int kNumBars = 2 * QBUF + 5 * NT + 4 * STAGES + kRing;
-  static constexpr int kSched = kBar + 8 * kNumBars;        // ring of unit indices
-  static constexpr int kTmemSlot = kSched + 4 * kRing;
+  static constexpr int kSched = (kBar + 8 * kNumBars + 15) / 16 * 16;   // ring of unit descriptors (16 ints each)
+  static constexpr int kTmemSlot = kSched + 64 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
 #ifdef NLFA_TRACE
@@ -214,9 +214,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   // Every role reads the index of its uc-th unit from the ring the producer fills;
   // a negative index means there is no more work.
-  auto next_unit = [&](int uc, bool& ok) -> int {
+  // The producer works the descriptor out once (several integer divisions) and publishes all
+  // of it: {u, b, h, hk, tile0, lo, extra_sinks, n_iters, n_valid, valid mask, tr[0], tr[1]}.
+  static_assert(NT <= 2, "the published unit descriptor holds two tile ranges");
+  auto next_unit = [&](int uc, bool& ok, Unit<NT>& w) -> int {
     ok = mbar_wait(bar(SCHED_FULL + (uc % kRing)), (uc / kRing) & 1, wctx, 11);
-    return ok ? sched_ring[uc % kRing] : -1;
+    if (!ok) return -1;
+    const int4* e = reinterpret_cast<const int4*>(const_cast<const int*>(sched_ring) + 16 * (uc % kRing));
+    const int4 a = e[0], b = e[1], c = e[2], d = e[3];
+    w.b = a.y; w.h = a.z; w.hk = a.w;
+    w.tile0 = b.x; w.lo = b.y; w.extra_sinks = b.z; w.n_iters = b.w;
+    w.n_valid = c.x;
+    w.valid[0] = (c.y & 1) != 0;
+    w.tr[0].lo = c.z; w.tr[0].hi = c.w; w.tr[0].sink_blocks = d.x;
+    if (NT > 1) {
+      w.valid[NT - 1] = (c.y & 2) != 0;
+      w.tr[NT - 1].lo = d.y; w.tr[NT - 1].hi = d.z; w.tr[NT - 1].sink_blocks = d.w;
+    }
+    return a.x;
   };
 
   // Register reallocation (NT = 2: 384 threads launch with 168 registers each): the
@@ -239,10 +254,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       auto fetch_unit = [&](int uc) -> int {
         int u = static_cast<int>(atomicAdd(&p.sched[0], 1u));
         if (u >= p.total_units) u = -1;
-        sched_ring[uc % kRing] = u;
+        Unit<NT> w{};
+        if (u >= 0) w = make_unit<NT>(u, p, BH);
+        volatile int* e = sched_ring + 16 * (uc % kRing);
+        e[0] = u; e[1] = w.b; e[2] = w.h; e[3] = w.hk;
+        e[4] = w.tile0; e[5] = w.lo; e[6] = w.extra_sinks; e[7] = w.n_iters;
+        e[8] = w.n_valid; e[9] = (w.valid[0] ? 1 : 0) | (w.valid[NT - 1] ? 2 : 0);
+        e[10] = w.tr[0].lo; e[11] = w.tr[0].hi; e[12] = w.tr[0].sink_blocks;
+        e[13] = w.tr[NT - 1].lo; e[14] = w.tr[NT - 1].hi; e[15] = w.tr[NT - 1].sink_blocks;
         mbar_arrive(bar(SCHED_FULL + (uc % kRing)));
         if (u < 0) return u;
-        const Unit<NT> w = make_unit<NT>(u, p, BH);
         const int qb = uc % QBUF;
         const uint32_t qph = (uc / QBUF) & 1;
         if (!(ok = mbar_wait(bar(Q_EMPTY + qb), qph ^ 1, wctx, 10))) return u;
@@ -257,7 +278,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       };
       int u = fetch_unit(0);
       for (int uc = 0; ok && u >= 0; ++uc) {
-        const Unit<NT> w = make_unit<NT>(u, p, BH);
+        Unit<NT> w;
+        next_unit(uc, ok, w);                    // published by this thread: never waits
+        if (!ok) break;
         // the next unit's Q is requested once this unit's first K/V blocks are on their way
         // (with a single Q buffer: only when this unit has released it)
         int u_next = -2;
@@ -341,25 +364,54 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         umma_commit(leader, bar(S_FULL + t));
         ++s_issued[t];
       };
-      for (int uc = 0; ok; ++uc) {
-        const int u = __shfl_sync(0xffffffffu, next_unit(uc, ok), 0);
+      // A warp-uniform copy of the uc-th unit's published descriptor.
+      auto get_unit = [&](int uc, Unit<NT>& w) -> int {
+        const int u = __shfl_sync(0xffffffffu, next_unit(uc, ok, w), 0);
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok || u < 0) break;
-        const Unit<NT> w = make_unit<NT>(u, p, BH);
-        const int qb = uc % QBUF;
-        if (leader) NLFA_TRACE_EVENT(2, 1);
-        if (!(ok = wait_all(bar(Q_FULL + qb), (uc / QBUF) & 1, 3))) break;
-        if (leader) NLFA_TRACE_EVENT(2, 2);
-        {
-          const int s0 = git % STAGES;
-          if (!(ok = wait_all(bar(K_FULL + s0), (git / STAGES) & 1, 4))) break;
-          const int j0 = w.block_at(0);
-          for (int t = 0; ok && t < NT; ++t)
-            if (w.sees(t, j0)) start_s(qb, t, s0);
-          if (!ok) break;
-          umma_commit(leader, bar(K_EMPTY + s0));
-          if (leader) NLFA_TRACE_EVENT(2, 3);
+        w.lo = __shfl_sync(0xffffffffu, w.lo, 0);
+        w.extra_sinks = __shfl_sync(0xffffffffu, w.extra_sinks, 0);
+        w.n_iters = __shfl_sync(0xffffffffu, w.n_iters, 0);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          w.valid[t] = __shfl_sync(0xffffffffu, w.valid[t] ? 1 : 0, 0) != 0;
+          w.tr[t].lo = __shfl_sync(0xffffffffu, w.tr[t].lo, 0);
+          w.tr[t].hi = __shfl_sync(0xffffffffu, w.tr[t].hi, 0);
+          w.tr[t].sink_blocks = __shfl_sync(0xffffffffu, w.tr[t].sink_blocks, 0);
         }
+        return u;
+      };
+      // A unit's first S products, in three steps so that they can be slotted into the end of
+      // the previous unit: wait for its Q tiles and first K block; one tile's product; release.
+      // `g0` is the global index of the unit's first key block.
+      auto pro_wait = [&](int uc, int g0) {
+        if (leader) NLFA_TRACE_EVENT(2, 1);
+        ok = wait_all(bar(Q_FULL + uc % QBUF), (uc / QBUF) & 1, 3);
+        if (ok) ok = wait_all(bar(K_FULL + g0 % STAGES), (g0 / STAGES) & 1, 4);
+        if (leader) NLFA_TRACE_EVENT(2, 2);
+      };
+      auto pro_s = [&](const Unit<NT>& w, int uc, int g0, int t) {
+        if (ok && w.sees(t, w.block_at(0))) start_s(uc % QBUF, t, g0 % STAGES);
+      };
+      auto pro_done = [&](int g0) {
+        if (ok) umma_commit(leader, bar(K_EMPTY + g0 % STAGES));
+        if (leader) NLFA_TRACE_EVENT(2, 3);
+      };
+      // With two Q buffers and P in its own columns, the next unit's first S products are
+      // issued during this unit's last key block.  Otherwise the first tile of a causal pair,
+      // which sees one block fewer than the second, would idle for a whole block at the end of
+      // every unit, waiting for the issuer to get through the second tile's last block.
+      constexpr bool kEarlyPro = kSepP && NT == 2 && QBUF > 1;
+      Unit<NT> w;
+      int u = get_unit(0, w);
+      if (ok && u >= 0) {
+        pro_wait(0, git);
+        for (int t = 0; t < NT; ++t) pro_s(w, 0, git, t);
+        pro_done(git);
+      }
+      for (int uc = 0; ok && u >= 0; ++uc) {
+        const int qb = uc % QBUF;
+        Unit<NT> wn;
+        int un = -2;                                  // next unit: not looked at yet
         bool o_started[NT];
         for (int t = 0; t < NT; ++t) o_started[t] = false;
         auto do_pv = [&](int t, int stage) {
@@ -391,6 +443,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (have_next && !(ok = wait_all(bar(K_FULL + s1), ph1, 6))) break;
             if (have_next && w.sees(1, j1)) start_s(qb, 1, s1);
             if (!ok) break;
+            if (kEarlyPro && !have_next) {
+              un = get_unit(uc + 1, wn);
+              if (ok && un >= 0) {
+                pro_wait(uc + 1, git + 1);
+                pro_s(wn, uc + 1, git + 1, 0);
+              }
+              if (!ok) break;
+            }
             if (it > 0) {
               if (w.sees(0, w.block_at(it - 1))) do_pv(0, sp);
               if (!ok) break;
@@ -399,6 +459,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (have_next && w.sees(0, j1)) start_s(qb, 0, s1);
             if (!ok) break;
             if (have_next) umma_commit(leader, bar(K_EMPTY + s1));
+            if (kEarlyPro && !have_next && un >= 0) {
+              pro_s(wn, uc + 1, git + 1, 1);
+              pro_done(git + 1);
+              if (!ok) break;
+            }
             if (!(ok = wait_all(bar(V_FULL + s), ph, 5))) break;
             if (w.sees(1, j)) do_pv(1, s);
           }
@@ -436,6 +501,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         if (!ok) break;
         umma_commit(leader, bar(Q_EMPTY + qb));
+        if (un == -2) {
+          un = get_unit(uc + 1, wn);
+          if (ok && un >= 0) {
+            pro_wait(uc + 1, git);
+            for (int t = 0; t < NT; ++t) pro_s(wn, uc + 1, git, t);
+            pro_done(git);
+          }
+        }
+        u = un;
+        w = wn;
       }
     }
   }
@@ -488,10 +563,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ++turn;
     };
     for (int uc = 0; ok; ++uc) {
-      const int u = next_unit(uc, ok);
+      Unit<NT> w;
+      const int u = next_unit(uc, ok, w);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok || u < 0) break;
-      const Unit<NT> w = make_unit<NT>(u, p, BH);
       if (!w.valid[t]) {
         if (row == 0) {
           release_pending();
