@@ -554,7 +554,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // [va, va + vw] (plus the sink prefix for the dQ orientation).
         auto do_chunk = [&](auto ch_c, auto masked_c) {
           constexpr int ch = decltype(ch_c)::value;
-          constexpr bool kMasked = decltype(masked_c)::value;
+          constexpr int kMasked = decltype(masked_c)::value;   // 0 none, 1 window/sinks, 2 plain causal
 #pragma unroll
           for (int c8 = 0; c8 < 8; ++c8) {
             const int c4 = 8 * ch + c8;
@@ -576,7 +576,21 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             unpack_f2(xa, p0, p1);
             unpack_f2(xb, p2, p3);
             p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
-            if (kMasked) {
+            if (kMasked == 2) {
+              // plain causal: one compare per element against a per-thread limit
+              const int lim = pos - other0;      // dQ: last visible column; dK/dV: first visible
+              if (MODE == MODE_DQ) {
+                if (c + 0 > lim) p0 = 0.f;
+                if (c + 1 > lim) p1 = 0.f;
+                if (c + 2 > lim) p2 = 0.f;
+                if (c + 3 > lim) p3 = 0.f;
+              } else {
+                if (c + 0 < lim) p0 = 0.f;
+                if (c + 1 < lim) p1 = 0.f;
+                if (c + 2 < lim) p2 = 0.f;
+                if (c + 3 < lim) p3 = 0.f;
+              }
+            } else if (kMasked == 1) {
               const unsigned o = static_cast<unsigned>(other0 + c - va);   // wraps below va
               const int ox = other0 + c;
               if (!(o + 0u <= vw || ox + 0 < vsink)) p0 = 0.f;
@@ -613,15 +627,16 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const bool out = (x1 < va || x0 > hi) && x0 >= vsink;
           const bool all_in = __all_sync(0xffffffffu, in);
           const bool all_out = __all_sync(0xffffffffu, out);
-          if (all_in) do_chunk(ch_c, std::false_type{});
+          if (all_in) do_chunk(ch_c, std::integral_constant<int, 0>{});
           else if (all_out) zero_chunk(ch_c);
-          else do_chunk(ch_c, std::true_type{});
+          else if (p.window == 0) do_chunk(ch_c, std::integral_constant<int, 2>{});
+          else do_chunk(ch_c, std::integral_constant<int, 1>{});
         };
         if (full) {
           // interior blocks: one straight-line pass over all 64 columns (branches between the
           // chunks would drain the exponential unit's pipeline at every chunk)
-          do_chunk(std::integral_constant<int, 0>{}, std::false_type{});
-          do_chunk(std::integral_constant<int, 1>{}, std::false_type{});
+          do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 0>{});
+          do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{});
         } else {
           chunk(std::integral_constant<int, 0>{});
           chunk(std::integral_constant<int, 1>{});

@@ -625,7 +625,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // its own are too few to cover the unit's latency (measured: 1760 clocks per row with
         // per-chunk branches against 1130 without).
         const int k0 = j * kTile;
-        if (!block_fully_visible(tile, j, p.window, p.sinks)) {
+        if (!block_fully_visible(tile, j, p.window, p.sinks) && p.window == 0) {
+          // plain causal: the row sees the columns up to its own position -- one compare per
+          // element against a per-thread limit
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int last = qpos - (k0 + 32 * c);                       // last visible column of the chunk
+            if (__all_sync(0xffffffffu, last >= 31)) continue;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i > last) sv[c][i] = __float_as_uint(-INFINITY);
+          }
+        } else if (!block_fully_visible(tile, j, p.window, p.sinks)) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int x0 = k0 + 32 * c, x1 = x0 + 31;
