@@ -160,6 +160,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr uint32_t kPCol = kSep ? 256 + kOutCols : 0;        // P  (dK/dV only)
   constexpr uint32_t kDsCol = kSep ? 256 + kOutCols + 64 : 128;
   constexpr int kRing = L::kRing;
+  constexpr int kRegsLaunch = 168, kRegsCompute = 200, kRegsOther = 104;   // per thread
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -229,7 +230,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   };
 
   if (warp >= 8) {
-  setmaxnreg_dec<104>();
+  setmaxnreg_dec<kRegsOther>();
+  // setmaxnreg.inc blocks until the registers it asks for have been released, so the four
+  // warps that shrink must free at least what the eight that grow take.
+  static_assert((kRegsLaunch - kRegsOther) * 4 >= (kRegsCompute - kRegsLaunch) * 8,
+                "register reallocation does not balance");
   if (dead || warp >= 10) {
     // nothing to do (spare warps only complete the third warpgroup)
   } else if (warp == 8) {
@@ -452,7 +457,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   } else {
     // ================================= compute ===============================
-    setmaxnreg_inc<200>();
+    setmaxnreg_inc<kRegsCompute>();
     if (!dead) {
     const int half = warp >> 2;                      // which 64 columns of the row
     const uint32_t lane_base = 32u * (warp & 3);

@@ -150,6 +150,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr bool kSepP = NT * (128 + D + 64) <= 512;      // P has columns of its own
   constexpr uint32_t kPBase = NT * (128 + D);
   constexpr int kRing = L::kRing;
+  constexpr int kRegsLaunch = 168, kRegsCompute = 216, kRegsOther = 72;   // per thread
 #ifndef NLFA_PINGPONG
 #define NLFA_PINGPONG 0
 #endif
@@ -238,7 +239,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   // warpgroup of the producer, the MMA issuer and two spare warps drops to 72, the softmax
   // warpgroups take 216 each.
   if (warp >= 4 * NT) {
-  if (NT == 2) setmaxnreg_dec<72>();
+  if (NT == 2) setmaxnreg_dec<kRegsOther>();
+  // setmaxnreg.inc blocks until the registers it asks for have been released, so the four
+  // warps that shrink must free at least what the eight that grow take.
+  static_assert((kRegsLaunch - kRegsOther) * 4 >= (kRegsCompute - kRegsLaunch) * 8,
+                "register reallocation does not balance");
   if (dead || warp >= 4 * NT + 2) {
     // nothing to do (spare warps only complete the warpgroup)
   } else if (warp == 4 * NT) {
@@ -516,7 +521,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   } else {
     // ================================= softmax ===============================
-    if (NT == 2) setmaxnreg_inc<216>();
+    if (NT == 2) setmaxnreg_inc<kRegsCompute>();
     if (!dead) {
     const int t = warp >> 2;                       // query tile of this warpgroup
     const int row = threadIdx.x - 128 * t;         // row inside the tile == TMEM lane
