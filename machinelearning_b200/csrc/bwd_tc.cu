@@ -85,7 +85,7 @@ struct BwdSmem {
   // barriers: x_full[XBUF], x_empty[XBUF], t_full, t_consumed, pd_full, out_ready,
   //           sched_full[kRing], y_full[S], y_empty[S]
   static constexpr int kRing = 8;
-  static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES;
+  static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES + 2;
   static constexpr int kSched = (kBar + 8 * kNumBars + 15) / 16 * 16;   // ring of unit descriptors (8 ints each)
   static constexpr int kTmemSlot = kSched + 32 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
@@ -145,7 +145,7 @@ __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p
 }
 
 template <typename T, int D, int MODE, int STAGES, int XBUF>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(512, 1)
 bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_out0,
@@ -160,7 +160,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr uint32_t kPCol = kSep ? 256 + kOutCols : 0;        // P  (dK/dV only)
   constexpr uint32_t kDsCol = kSep ? 256 + kOutCols + 64 : 128;
   constexpr int kRing = L::kRing;
-  constexpr int kRegsLaunch = 168, kRegsCompute = 200, kRegsOther = 104;   // per thread
+  constexpr int kRegsLaunch = 128, kRegsCompute = 200, kRegsOther = 56;    // per thread
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -176,7 +176,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   auto bar = [&](int i) -> uint32_t { return base + L::kBar + 8u * i; };
   constexpr int X_FULL = 0, X_EMPTY = XBUF, T_FULL = 2 * XBUF, T_CONSUMED = T_FULL + 1,
                 PD_FULL = T_FULL + 2, OUT_READY = T_FULL + 3, SCHED_FULL = T_FULL + 4,
-                Y_FULL = SCHED_FULL + kRing, Y_EMPTY = Y_FULL + STAGES;
+                Y_FULL = SCHED_FULL + kRing, Y_EMPTY = Y_FULL + STAGES,
+                UNIT_DONE = Y_EMPTY + STAGES, OUT_DRAINED = UNIT_DONE + 1;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
   volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
@@ -192,6 +193,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     mbar_init(bar(T_CONSUMED), 256);
     mbar_init(bar(PD_FULL), 256);
     mbar_init(bar(OUT_READY), 1);
+    mbar_init(bar(UNIT_DONE), 1);
+    mbar_init(bar(OUT_DRAINED), 128);
     for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(Y_FULL + s), 1);
@@ -209,9 +212,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tmem = *tmem_slot;
   const bool dead = *abort_flag != 0;
 
-  // The launch gives every thread 168 registers (384 threads).  Inside its role's branch
-  // each warp of the third warpgroup (producer, MMA issuer, two spare warps) drops to 104 and
-  // the two compute warpgroups take 200 each.
+  // Sixteen warps: 0-7 compute, 8 scheduler + TMA producer, 9 MMA issuer, 10-11 idle, 12-15
+  // epilogue (one warp per TMEM lane quarter).  The launch gives every thread 128 registers;
+  // inside its role's branch each warp of the upper half drops to 56 and the compute warps
+  // take 200 each.
 
   // Every role reads the unit index of its uc-th unit from the ring the producer
   // fills; a negative index means there is no more work.
@@ -231,12 +235,76 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   if (warp >= 8) {
   setmaxnreg_dec<kRegsOther>();
-  // setmaxnreg.inc blocks until the registers it asks for have been released, so the four
+  // setmaxnreg.inc blocks until the registers it asks for have been released, so the eight
   // warps that shrink must free at least what the eight that grow take.
-  static_assert((kRegsLaunch - kRegsOther) * 4 >= (kRegsCompute - kRegsLaunch) * 8,
+  static_assert((kRegsLaunch - kRegsOther) * 8 >= (kRegsCompute - kRegsLaunch) * 8,
                 "register reallocation does not balance");
-  if (dead || warp >= 10) {
-    // nothing to do (spare warps only complete the third warpgroup)
+  if (dead || warp == 10 || warp == 11) {
+    // nothing to do (spare warps only complete the warpgroup)
+  } else if (warp >= 12) {
+    // ================================ epilogue ===============================
+    // One thread per row of the unit's output tiles.  When the unit's last output product has
+    // completed, the fp32 accumulators are pulled out of TMEM (which frees them for the next
+    // unit at once), converted and staged in the unit's stationary tiles -- dead by then, and
+    // in the swizzled layout the loads use: dQ over the Q tile, dK over K, dV over V -- and
+    // written with TMA stores.  The compute warps meanwhile work on the next unit.
+    const uint32_t lane_base = 32u * (warp & 3);
+    const int row = 32 * (warp & 3) + lane;
+    const uint32_t sw = static_cast<uint32_t>(row & 7);
+    bool ok = true;
+    for (int uc = 0; ok; ++uc) {
+      BwdUnit<MODE> w;
+      const int u = next_unit(uc, ok, w);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok || u < 0) break;
+      ok = mbar_wait_idle(bar(UNIT_DONE), uc & 1, wctx, 41);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int xb = uc % XBUF;
+      const uint32_t stage0 = base + L::kX + xb * 2 * L::kTileBytes;       // X0 region
+#pragma unroll 1
+      for (int c = 0; c < kOutCols; c += 32) {
+        // dK/dV: columns [0, D) are dV (over the V tile), [D, 2D) are dK (over the K tile, scaled)
+        const bool second = MODE == MODE_DKV && c >= D;
+        const uint32_t tile_base = (MODE == MODE_DKV && !second) ? stage0 + L::kTileBytes : stage0;
+        const float mul = (MODE == MODE_DQ || second) ? p.scale : 1.f;
+        const int col0 = second ? c - D : c;
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tmem, lane_base, kOutCol + c), r);
+        tc_wait_ld();
+        if (c + 32 >= kOutCols) {
+          tc_fence_before();
+          mbar_arrive(bar(OUT_DRAINED));          // the accumulators may be overwritten
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = col0 + 8 * i;                         // first of 8 columns = one 16 B chunk
+          const uint32_t addr = tile_base + static_cast<uint32_t>(col >> 6) * kBoxBytes +
+                                static_cast<uint32_t>(row) * 128u +
+                                ((static_cast<uint32_t>((col & 63) >> 3) ^ sw) << 4);
+          st_shared_v4(addr,
+                       Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * mul, __uint_as_float(r[8 * i + 1]) * mul),
+                       Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * mul, __uint_as_float(r[8 * i + 3]) * mul),
+                       Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * mul, __uint_as_float(r[8 * i + 5]) * mul),
+                       Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * mul, __uint_as_float(r[8 * i + 7]) * mul));
+        }
+      }
+      fence_proxy_async_smem();
+      named_barrier(1, 128);
+      if (warp == 12 && lane == 0) {
+        const int oh = MODE == MODE_DQ ? w.h : w.hk;
+        for (int x = 0; x < kBoxes; ++x) {
+          tma_store_4d(&tm_out0, stage0 + x * kBoxBytes, 64 * x, oh, w.tile * kTile, w.b);
+          if (MODE == MODE_DKV)
+            tma_store_4d(&tm_out1, stage0 + L::kTileBytes + x * kBoxBytes, 64 * x, oh,
+                         w.tile * kTile, w.b);
+        }
+        tma_store_commit();
+        tma_store_wait_read();
+        mbar_arrive(bar(X_EMPTY + xb));          // second arrival: the buffer may be reloaded
+      }
+    }
   } else if (warp == 8) {
     // ========================= scheduler + TMA producer ======================
     const CUtensorMap* mx0 = MODE == MODE_DQ ? &tm_q : &tm_k;
@@ -409,6 +477,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
       int g = 0;                        // global iteration of `cur`
+      int cur_uc = 0;                   // index of the unit `cur` belongs to
       while (ok && cur_u >= 0) {
         // ---- locate the next global iteration
         int nxt_u = cur_u, nxt_it = cur_it + 1, nxt_n = cur_n, nxt_xb = cur_xb;
@@ -432,25 +501,35 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             if (leader) NLFA_BTRACE(2, 20);
           }
         };
-        // With a single stationary buffer the next unit's tiles can only be loaded once this
-        // unit's buffer has been released, i.e. after the output products below are issued.
-        // At a unit's last iteration the output products go first, so that the epilogue (which
-        // has to wait for them) can start as early as possible.
-        const bool early = kSep && have_next && !crossed;
+        // The next iteration's T products go first, also across a unit boundary, so that the
+        // compute warps never wait for them.  With a single stationary buffer the next unit's
+        // tiles can only be loaded once this unit's buffer has been released, i.e. after the
+        // output products below are issued, so there the boundary is not crossed early.
+        const bool early = kSep && have_next && (!crossed || XBUF > 1);
         if (early) issue_next_t();
         if (!ok) break;
         if (leader) NLFA_BTRACE(2, 10);
         if (!(ok = wait_all(bar(PD_FULL), g & 1, 34))) break;
         if (leader) NLFA_BTRACE(2, 11);
         tc_fence_after();
+        // a unit's first output product overwrites the accumulators: the epilogue warps must
+        // have pulled the previous unit's out of TMEM
+        if (cur_it == 0 && cur_uc > 0) {
+          if (!(ok = wait_all(bar(OUT_DRAINED), (cur_uc - 1) & 1, 42))) break;
+          tc_fence_after();
+        }
         issue_out(g, cur_it > 0 ? 1u : 0u);
-        if (cur_it + 1 == cur_n) umma_commit(leader, bar(X_EMPTY + cur_xb));
+        if (cur_it + 1 == cur_n) {
+          umma_commit(leader, bar(X_EMPTY + cur_xb));
+          umma_commit(leader, bar(UNIT_DONE));
+        }
         if (!early && have_next) issue_next_t();
         if (!ok) break;
         cur_u = nxt_u;
         cur_it = nxt_it;
         cur_n = nxt_n;
         cur_xb = nxt_xb;
+        if (crossed) cur_uc = uc;
         ++g;
       }
     }
@@ -470,17 +549,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
     bool ok = true;
     int g = 0;                    // global iteration
-    // With two stationary buffers the thread that issued a unit's TMA stores does not wait for
-    // them on the spot (that would hold up every warp at the next hand-off); it releases the
-    // buffer a little later, when the stores have long finished reading shared memory.
-    int pending_xb = -1;
-    auto release_pending = [&]() {
-      if (pending_xb >= 0) {
-        tma_store_wait_read();
-        mbar_arrive(bar(X_EMPTY + pending_xb));
-        pending_xb = -1;
-      }
-    };
     float pre_lse = 0.f, pre_delta = 0.f;     // dQ: row statistics of the next unit
     int out_waited = 0;           // OUT_READY phases this thread has observed
     auto wait_out = [&](int needed) {
@@ -513,7 +581,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       uint64_t negl2_row = pack_f2(-INFINITY, -INFINITY), negd_row = 0ull;
       if (MODE == MODE_DQ && pos < p.T) {
-        if (uc > 0) {                       // fetched during the previous unit's epilogue
+        if (uc > 0) {                       // fetched during the previous unit's last iteration
           negl2_row = pack_f2(-pre_lse * kLog2e, -pre_lse * kLog2e);
           negd_row = pack_f2(-pre_delta, -pre_delta);
         } else {
@@ -530,6 +598,20 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const int s = g % STAGES;
         const int idx = w.streamed_index(inner);
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 1);
+        if (MODE == MODE_DQ && it + 1 == w.n_iters) {
+          // The next unit's row statistics are requested now (its descriptor is published well
+          // ahead), so that their memory latency passes during this unit's last iteration.
+          BwdUnit<MODE> wn;
+          const int un = next_unit(uc + 1, ok, wn);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const int pos_n = wn.tile * kTile + row;
+          if (un >= 0 && pos_n < p.T) {
+            const long long nidx = (static_cast<long long>(wn.b) * p.H + wn.h) * p.T + pos_n;
+            pre_lse = p.lse[nidx];
+            pre_delta = p.delta[nidx];
+          }
+        }
         ok = mbar_wait(bar(T_FULL), g & 1, wctx, 35);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -655,91 +737,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(PD_FULL));
-        if (XBUF > 1 && it == 0 && threadIdx.x == 0) release_pending();
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 5);
       }
       if (!ok) break;
 
-      if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 6);
-      if (MODE == MODE_DQ) {
-        // The next unit's row statistics are requested now (its descriptor is published well
-        // ahead), so that their memory latency passes during this unit's epilogue.
-        BwdUnit<MODE> wn;
-        const int un = next_unit(uc + 1, ok, wn);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const int pos_n = wn.tile * kTile + row;
-        if (un >= 0 && pos_n < p.T) {
-          const long long idx = (static_cast<long long>(wn.b) * p.H + wn.h) * p.T + pos_n;
-          pre_lse = p.lse[idx];
-          pre_delta = p.delta[idx];
-        }
-      }
-      wait_out(g);                 // this unit's last output product
-      if (!ok) break;
-      tc_fence_after();
-      // The unit's stationary tiles are dead now (every product that read them has
-      // completed), so their shared memory stages the output tiles, in the same swizzled
-      // layout the loads use, for coalesced TMA stores: dQ over the Q tile, dK over K, dV over V.
-      {
-        const int xb = uc % XBUF;
-        const uint32_t stage0 = base + L::kX + xb * 2 * L::kTileBytes;       // X0 region
-        const uint32_t sw = static_cast<uint32_t>(row & 7);
-        auto stage_cols = [&](uint32_t tile_base, uint32_t tmem_col, int col0, int ncols, float mul) {
-          // converts fp32 columns [col0, col0 + ncols) of this thread's row and writes them
-          for (int c = 0; c < ncols; c += 32) {
-            uint32_t r[32];
-            tmem_ld32(tmem_addr(tmem, lane_base, tmem_col + c), r);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int col = col0 + c + 8 * i;                   // first of 8 columns = one 16 B chunk
-              const uint32_t box = static_cast<uint32_t>(col >> 6);
-              const uint32_t chunk = static_cast<uint32_t>((col & 63) >> 3);
-              const uint32_t addr = tile_base + box * kBoxBytes + static_cast<uint32_t>(row) * 128u +
-                                    ((chunk ^ sw) << 4);
-              st_shared_v4(addr,
-                           Pack2<T>::pack(__uint_as_float(r[8 * i + 0]) * mul, __uint_as_float(r[8 * i + 1]) * mul),
-                           Pack2<T>::pack(__uint_as_float(r[8 * i + 2]) * mul, __uint_as_float(r[8 * i + 3]) * mul),
-                           Pack2<T>::pack(__uint_as_float(r[8 * i + 4]) * mul, __uint_as_float(r[8 * i + 5]) * mul),
-                           Pack2<T>::pack(__uint_as_float(r[8 * i + 6]) * mul, __uint_as_float(r[8 * i + 7]) * mul));
-            }
-          }
-        };
-        if (MODE == MODE_DQ) {
-          // each half converts D/2 columns of its dQ row
-          stage_cols(stage0, kOutCol + half * (D / 2), half * (D / 2), D / 2, p.scale);
-        } else if (half == 0) {
-          stage_cols(stage0 + L::kTileBytes, kOutCol, 0, D, 1.f);           // dV over the V tile
-        } else {
-          stage_cols(stage0, kOutCol + D, 0, D, p.scale);                   // dK over the K tile
-        }
-        fence_proxy_async_smem();
-        tc_fence_before();
-        named_barrier(1, 256);
-        if (threadIdx.x == 0) {
-          const int oh = MODE == MODE_DQ ? w.h : w.hk;
-          for (int x = 0; x < kBoxes; ++x) {
-            tma_store_4d(&tm_out0, stage0 + x * kBoxBytes, 64 * x, oh, w.tile * kTile, w.b);
-            if (MODE == MODE_DKV)
-              tma_store_4d(&tm_out1, stage0 + L::kTileBytes + x * kBoxBytes, 64 * x, oh,
-                           w.tile * kTile, w.b);
-          }
-          tma_store_commit();
-          if (XBUF > 1) {
-            pending_xb = xb;                     // released after the next unit's first iteration
-          } else {
-            tma_store_wait_read();
-            mbar_arrive(bar(X_EMPTY + xb));      // second arrival: the buffer may be reloaded
-          }
-        }
-      }
-      if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 7);
-      // the next unit's first output product overwrites these columns; it is issued
-      // only after this thread's next PD arrival, which follows in program order
-      tc_fence_before();
     }
-    if (threadIdx.x == 0) release_pending();
     }
   }
 
@@ -830,7 +832,7 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
   bp.sched = sched_slot();
   if (bp.sched == nullptr) return NLFA_ERR_CUDA;
   const int grid = bp.total_units < sm_count_bwd() ? bp.total_units : sm_count_bwd();
-  kern<<<grid, 384, L::kDynamic, stream>>>(mq, mk, mv, mdo, mo0, mo1, bp);
+  kern<<<grid, 512, L::kDynamic, stream>>>(mq, mk, mv, mdo, mo0, mo1, bp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 

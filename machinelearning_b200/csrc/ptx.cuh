@@ -105,6 +105,27 @@ static __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t par
   }
 }
 
+// The same bounded wait for roles that expect to wait long (a whole work unit): the warp
+// sleeps between polls, so that its polling does not take issue slots from the warps that
+// share its scheduler.
+static __device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+                                                      unsigned where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t spins = 1;; ++spins) {
+    __nanosleep(200);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 0x3fu) == 0u) {
+      if (*ctx.abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *ctx.abort_flag = 1;
+        atomicCAS(ctx.status, STATUS_OK, STATUS_WAIT_TIMEOUT | (where & 0xffu));
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           unsigned where) {
   if (mbar_try_wait(bar, parity)) return true;
