@@ -724,6 +724,11 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           // chunks would drain the exponential unit's pipeline at every chunk)
           do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 0>{});
           do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{});
+        } else if (p.window == 0) {
+          // plain causal boundary block: the same straight-line pass with one compare per
+          // element; skipping the fully masked chunks would bring the branches back
+          do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 2>{});
+          do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 2>{});
         } else {
           chunk(std::integral_constant<int, 0>{});
           chunk(std::integral_constant<int, 1>{});
