@@ -14,7 +14,8 @@ Prints one JSON line:
              slowest rank
   e2e        the same metric through ``flash_cuda.flash_attn`` + autograd with
              pinned host buffers: host->device copies of q, k, v, dO and
-             device->host copies of O, dQ, dK, dV inside the timed region
+             device->host copies of O, dQ, dK, dV inside the timed region, in
+             batch slices on three streams (``host_pipeline.HostPipeline``)
   roofline   the dominant kernel timed alone against the measured dense bf16 peak
   cpu_baseline  the reference's CPU attention (torch SDPA + autograd, restated in
              oracle/sdpa_port.py) on this box's host cores, bounded sample
@@ -292,7 +293,7 @@ def dram_traffic(kernel, workload):
 
 def run_gpu_arm(args, shape, rank, world, local_rank):
     import torch.distributed as dist
-    from machinelearning_b200 import flash_cuda, sharding
+    from machinelearning_b200 import flash_cuda, host_pipeline, sharding
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -336,13 +337,11 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
     host_out = [torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)]
     scale = 1.0 / math.sqrt(D)
 
+    # batch slices: copy-in, flash_attn + autograd and copy-out of neighbouring slices overlap
+    pipe = host_pipeline.HostPipeline(tuple(hq.shape), tuple(hk.shape), hq.dtype, dev, n_slices=16)
+
     def e2e_step():
-        dq_, dk_, dv_, ddo = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
-        dq_.requires_grad_(), dk_.requires_grad_(), dv_.requires_grad_()
-        y = flash_cuda.flash_attn(dq_, dk_, dv_, scale, use_mma=True, window=window, sinks=sinks)
-        grads = torch.autograd.grad(y, (dq_, dk_, dv_), ddo)
-        for dst, src in zip(host_out, (y.detach(), *grads)):
-            dst.copy_(src, non_blocking=True)
+        pipe.run(hq, hk, hv, hdo, *host_out, scale=scale, window=window, sinks=sinks)
 
     for _ in range(3):
         e2e_step()
@@ -398,7 +397,8 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
                          if 8 * q.numel() * 2 > 126e6 else "working set smaller than L2",
                    "flops_per_step_per_gpu": ff + fb},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "pipeline": "16 batch slices; copy-in, kernels and copy-out on three streams"},
         "gpu_launches": Step.launches_per_step * args.steps,
         "kernel_ms": kt,
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
