@@ -73,7 +73,7 @@ struct FwdSmem {
   // barriers (8 bytes each): q_full[QBUF], q_empty[QBUF], s_full[NT], s_consumed[NT],
   // p_full[NT], o_ready[NT], k_full[S], k_empty[S], v_full[S], v_empty[S], sched_full[kRing]
   static constexpr int kRing = 8;
-  static constexpr int kNumBars = 2 * QBUF + 5 * NT + 4 * STAGES + kRing;
+  static constexpr int kNumBars = 2 * QBUF + 4 * NT + 4 * STAGES + kRing;
   static constexpr int kSched = (kBar + 8 * kNumBars + 15) / 16 * 16;   // ring of unit descriptors (16 ints each)
   static constexpr int kTmemSlot = kSched + 64 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
@@ -151,10 +151,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr uint32_t kPBase = NT * (128 + D);
   constexpr int kRing = L::kRing;
   constexpr int kRegsLaunch = 168, kRegsCompute = 216, kRegsOther = 72;   // per thread
-#ifndef NLFA_PINGPONG
-#define NLFA_PINGPONG 0
-#endif
-  constexpr bool kPingPong = NT == 2 && NLFA_PINGPONG;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -172,7 +168,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr int Q_FULL = 0, Q_EMPTY = QBUF, S_FULL = 2 * QBUF, S_CONSUMED = S_FULL + NT,
                 P_FULL = S_CONSUMED + NT, O_READY = P_FULL + NT, K_FULL = O_READY + NT,
                 K_EMPTY = K_FULL + STAGES, V_FULL = K_EMPTY + STAGES, V_EMPTY = V_FULL + STAGES,
-                SCHED_FULL = V_EMPTY + STAGES, XU_TOKEN = SCHED_FULL + kRing;
+                SCHED_FULL = V_EMPTY + STAGES;
   volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
@@ -194,7 +190,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(bar(O_READY + t), 1);
     }
     for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
-    for (int t = 0; t < NT; ++t) mbar_init(bar(XU_TOKEN + t), 4);     // one arrival per warp
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(K_FULL + s), 1);
       mbar_init(bar(K_EMPTY + s), 1);
@@ -318,11 +313,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     // lane that issues.  All values that feed a descriptor are made provably warp-uniform.
     {
       const uint32_t leader = elect_one() ? 1u : 0u;
-#ifdef NLFA_NO_MMA
-      const uint32_t mma_leader = 0u;      // timing experiment: hand-offs without the products
-#else
-      const uint32_t mma_leader = leader;
-#endif
       const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
       auto wait_all = [&](uint32_t b, uint32_t parity, unsigned where) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(b, parity, wctx, where));
@@ -336,7 +326,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          umma_ss(mma_leader, tmem + 128 * t, make_smem_desc(qa + off, 16, 1024),
+          umma_ss(leader, tmem + 128 * t, make_smem_desc(qa + off, 16, 1024),
                  make_smem_desc(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
       };
@@ -346,7 +336,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk) {
           // 16 keys per step: 8 packed TMEM columns of P, 16 rows (2048 bytes) of V
-          umma_ts(mma_leader, tmem + 128 * NT + D * t, tmem + pa + 8 * kk,
+          umma_ts(leader, tmem + 128 * NT + D * t, tmem + pa + 8 * kk,
                  make_smem_desc(va + kk * 2048, kBoxBytes, 1024), idesc_pv,
                  (accumulate || kk > 0) ? 1u : 0u);
         }
@@ -543,30 +533,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     };
     bool ok = true;
-    // The two softmax warpgroups share the exponential unit, and a block's exponentials are
-    // most of its work.  Left alone the warpgroups fall into step -- both in their exponentials,
-    // then both out of them -- and the unit idles half the time.  A token makes them take
-    // strict turns instead: a warpgroup computes its exponentials only while it holds the token
-    // and hands it over as soon as they are done, so one loads, reduces and stores while the
-    // other exponentiates.  Turns follow the MMA issuer's order (kLead first), one turn per
-    // (unit, key block) whether or not the tile sees the block.
-    constexpr int kLead = kSepP ? 1 : 0;
-    int turn = 0;
-    auto token_acquire = [&]() {
-      if (!kPingPong) return;
-      if (t == kLead) {
-        if (turn > 0) ok = mbar_wait(bar(XU_TOKEN + t), (turn - 1) & 1, wctx, 14);
-      } else {
-        ok = mbar_wait(bar(XU_TOKEN + t), turn & 1, wctx, 14);
-      }
-      ok = __all_sync(0xffffffffu, ok);
-    };
-    auto token_release = [&]() {
-      if (!kPingPong) return;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(XU_TOKEN + (t ^ 1)));
-      ++turn;
-    };
     for (int uc = 0; ok; ++uc) {
       Unit<NT> w;
       const int u = next_unit(uc, ok, w);
@@ -576,10 +542,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (row == 0) {
           release_pending();
           mbar_arrive(bar(Q_EMPTY + (uc % QBUF)));                // nothing to store for this tile
-        }
-        for (int it = 0; ok && it < w.n_iters; ++it) {
-          token_acquire();
-          token_release();
         }
         continue;
       }
@@ -601,12 +563,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const unsigned vw = static_cast<unsigned>(qpos - va);
       for (int it = 0; it < w.n_iters; ++it) {
         const int j = w.block_at(it);
-        if (!tile_sees_block(w.tr[t], j)) {
-          token_acquire();
-          token_release();
-          if (!ok) break;
-          continue;
-        }
+        if (!tile_sees_block(w.tr[t], j)) continue;
         if (row == 0) NLFA_TRACE_EVENT(t, 1);
         ok = mbar_wait(bar(S_FULL + t), s_count & 1, wctx, 8);
         ok = __all_sync(0xffffffffu, ok);
@@ -677,25 +634,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           rescale = true;
           l *= alpha;
         }
-        token_acquire();
-        if (!ok) break;
         if (row == 0) NLFA_TRACE_EVENT(t, 31);
 
         // all exponentials of the row first (P stays in registers) ...
         const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        uint64_t negm2 = pack_f2(-m_use, -m_use);
+        const uint64_t negm2 = pack_f2(-m_use, -m_use);
         uint64_t acc0 = 0ull, acc1 = 0ull;              // packed (0.f, 0.f)
         uint32_t pk[4][16];
-#ifndef NLFA_EXP_GROUP
-#define NLFA_EXP_GROUP 2
-#endif
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          // Scheduling fence between groups of chunks: the next group's inputs are made to
-          // depend on the last word of the previous one.  Without it the compiler interleaves
-          // all 128 elements and runs out of registers; with a fence after every chunk (or a
-          // branch) the exponential unit drains four times per row.
-          if (c > 0 && c % NLFA_EXP_GROUP == 0) asm volatile("" : "+l"(negm2) : "r"(pk[c - 1][15]));
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             float e0, e1, e2, e3;
@@ -715,7 +662,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           unpack_f2(fadd2(acc0, acc1), lo, hi);
           l += lo + hi;
         }
-        token_release();
         if (row == 0) NLFA_TRACE_EVENT(t, 32);
         // ... and only then the hand-off that needs the previous block's PV product to be
         // complete (O may be rescaled, P's columns may be overwritten); by now it long is.

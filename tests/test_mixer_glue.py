@@ -1,0 +1,102 @@
+"""Routing of the mixer's attention core to the kernels (host logic; the GPU case
+at the bottom checks the windowed route against the oracle)."""
+import logging
+import sys
+import types
+
+import numpy as np
+import pytest
+import torch
+
+from machinelearning_b200 import flash_cuda, mixer_glue
+
+
+class FakeMixer:
+    def __init__(self, **kw):
+        self.flash_cuda = True
+        self.causal = True
+        self.block_attn = 0
+        self.swa_window = 0
+        self.swa_sinks = 0
+        self._flash_declined = False
+        self.__dict__.update(kw)
+
+
+def _cpu_qkv():
+    q = torch.zeros(1, 8, 2, 64)
+    return q, q.clone(), q.clone()
+
+
+def test_install_registers_module_and_attribute():
+    pkg = types.ModuleType("fakelab")
+    sys.modules["fakelab"] = pkg
+    try:
+        mixer_glue.install("fakelab")
+        assert sys.modules["fakelab.flash_cuda"] is flash_cuda
+        assert pkg.flash_cuda is flash_cuda
+        import importlib
+        assert importlib.import_module("fakelab.flash_cuda") is flash_cuda
+    finally:
+        sys.modules.pop("fakelab", None)
+        sys.modules.pop("fakelab.flash_cuda", None)
+
+
+def test_install_refuses_after_mixers_bound_elsewhere():
+    sys.modules["fakelab2"] = types.ModuleType("fakelab2")
+    sys.modules["fakelab2.mixers"] = types.ModuleType("fakelab2.mixers")
+    sys.modules["fakelab2.flash_cuda"] = types.ModuleType("fakelab2.flash_cuda")
+    try:
+        with pytest.raises(RuntimeError):
+            mixer_glue.install("fakelab2")
+    finally:
+        for n in ("fakelab2", "fakelab2.mixers", "fakelab2.flash_cuda"):
+            sys.modules.pop(n, None)
+
+
+@pytest.mark.parametrize("kw,needle", [
+    (dict(flash_cuda=False), "off"),
+    (dict(causal=False), "non-causal"),
+    (dict(block_attn=16), "block-causal"),
+    (dict(swa_window=8, swa_sinks=8), "sinks"),
+])
+def test_decline_reasons_before_any_load(kw, needle):
+    q, k, v = _cpu_qkv()
+    why = mixer_glue.decline_reason(FakeMixer(**kw), q, k, v)
+    assert why is not None and needle in why
+
+
+def test_cpu_tensors_decline_and_warn_once(caplog):
+    q, k, v = _cpu_qkv()
+    m = FakeMixer(swa_window=4, swa_sinks=1)
+    with caplog.at_level(logging.WARNING, logger="machinelearning_b200.mixer_glue"):
+        assert mixer_glue.attention_core(m, q, k, v, 0.125) is None
+        assert mixer_glue.attention_core(m, q, k, v, 0.125) is None
+    warnings = [r for r in caplog.records if "cannot run" in r.getMessage()]
+    assert len(warnings) == 1 and "unsupported inputs" in warnings[0].getMessage()
+    assert m._flash_declined
+
+
+def test_flag_off_is_silent(caplog):
+    q, k, v = _cpu_qkv()
+    with caplog.at_level(logging.WARNING, logger="machinelearning_b200.mixer_glue"):
+        assert mixer_glue.attention_core(FakeMixer(flash_cuda=False), q, k, v, 0.125) is None
+    assert not caplog.records
+
+
+@pytest.mark.gpu
+def test_windowed_mixer_routes_through_the_kernel():
+    from oracle import attention_f64
+    if not flash_cuda.is_available():
+        pytest.fail(f"flash_cuda unavailable on a GPU box: {flash_cuda.unavailable_reason()}")
+    g = torch.Generator().manual_seed(7)
+    B, T, H, Hkv, D = 2, 200, 4, 2, 64
+    q = torch.randn(B, T, H, D, generator=g).bfloat16()
+    k = torch.randn(B, T, Hkv, D, generator=g).bfloat16()
+    v = torch.randn(B, T, Hkv, D, generator=g).bfloat16()
+    m = FakeMixer(swa_window=64, swa_sinks=4)
+    y = mixer_glue.attention_core(m, q.cuda(), k.cuda(), v.cuda(), 0.125)
+    assert y is not None and not m._flash_declined
+    ref, _ = attention_f64.attention_fwd(q.double().numpy(), k.double().numpy(), v.double().numpy(),
+                                        0.125, window=64, sinks=4)
+    err = np.abs(y.float().cpu().numpy() - ref).max() / np.abs(ref).max()
+    assert err <= 2e-2, err        # relative, bf16 tolerance of the path
