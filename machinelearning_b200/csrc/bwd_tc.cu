@@ -27,6 +27,7 @@
 // columns; dV then dK: 2 D columns).  The 16-bit P / dS operands of the output
 // products live in their own columns when there is room (everything except
 // dK/dV at D = 128, where they overwrite the columns of T0/T1 just read).
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -789,7 +790,7 @@ int sm_count_bwd() {
 // Device address of a fresh pair of scheduler counters on the current device.
 unsigned* sched_slot() {
   static unsigned* base[64];
-  static unsigned next_slot = 0;
+  static std::atomic<unsigned> next_slot{0};   // launches may come from several host threads
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   if (base[dev] == nullptr) {
@@ -797,7 +798,7 @@ unsigned* sched_slot() {
     if (cudaGetSymbolAddress(&ptr, g_bwd_sched) != cudaSuccess) return nullptr;
     base[dev] = static_cast<unsigned*>(ptr);
   }
-  const unsigned slot = (next_slot++) % kSchedSlots;
+  const unsigned slot = next_slot.fetch_add(1u, std::memory_order_relaxed) % kSchedSlots;
   return base[dev] + 2 * slot;
 }
 

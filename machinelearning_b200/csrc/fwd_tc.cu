@@ -21,6 +21,8 @@
 // Computes what nanolab/csrc/flash_attn_cuda.cu:583-797 computes (softmax in
 // base 2, L = m ln2 + log l at :279), with the sliding-window mask of
 // nanolab/mixers.py:125-132 and skipping of key blocks no row can see.
+#include <atomic>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -778,7 +780,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 // Device address of a fresh pair of scheduler counters on the current device.
 unsigned* fwd_sched_slot() {
   static unsigned* base[64];
-  static unsigned next_slot = 0;
+  static std::atomic<unsigned> next_slot{0};   // launches may come from several host threads
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   if (base[dev] == nullptr) {
@@ -786,7 +788,7 @@ unsigned* fwd_sched_slot() {
     if (cudaGetSymbolAddress(&ptr, g_fwd_sched) != cudaSuccess) return nullptr;
     base[dev] = static_cast<unsigned*>(ptr);
   }
-  const unsigned slot = (next_slot++) % kFwdSchedSlots;
+  const unsigned slot = next_slot.fetch_add(1u, std::memory_order_relaxed) % kFwdSchedSlots;
   return base[dev] + 2 * slot;
 }
 
