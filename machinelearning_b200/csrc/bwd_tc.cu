@@ -642,7 +642,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // [va, va + vw] (plus the sink prefix for the dQ orientation).
         auto do_chunk = [&](auto ch_c, auto masked_c) {
           constexpr int ch = decltype(ch_c)::value;
-          constexpr int kMasked = decltype(masked_c)::value;   // 0 none, 1 window/sinks, 2 plain causal
+          constexpr int kMasked = decltype(masked_c)::value;   // 0 none, 1 general, 2 causal edge, 3 window edge
 #pragma unroll
           for (int c8 = 0; c8 < 8; ++c8) {
             const int c4 = 8 * ch + c8;
@@ -677,6 +677,21 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 if (c + 1 < lim) p1 = 0.f;
                 if (c + 2 < lim) p2 = 0.f;
                 if (c + 3 < lim) p3 = 0.f;
+              }
+            } else if (kMasked == 3) {
+              // only the window's lower edge cuts the block
+              if (MODE == MODE_DQ) {
+                const int lim = va - other0;                               // first visible column
+                if (c + 0 < lim) p0 = 0.f;
+                if (c + 1 < lim) p1 = 0.f;
+                if (c + 2 < lim) p2 = 0.f;
+                if (c + 3 < lim) p3 = 0.f;
+              } else {
+                const int lim = pos + (p.window - p.sinks) - 1 - other0;   // last query that sees this key
+                if (c + 0 > lim) p0 = 0.f;
+                if (c + 1 > lim) p1 = 0.f;
+                if (c + 2 > lim) p2 = 0.f;
+                if (c + 3 > lim) p3 = 0.f;
               }
             } else if (kMasked == 1) {
               const unsigned o = static_cast<unsigned>(other0 + c - va);   // wraps below va
@@ -717,7 +732,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const bool all_out = __all_sync(0xffffffffu, out);
           if (all_in) do_chunk(ch_c, std::integral_constant<int, 0>{});
           else if (all_out) zero_chunk(ch_c);
-          else if (p.window == 0) do_chunk(ch_c, std::integral_constant<int, 2>{});
           else do_chunk(ch_c, std::integral_constant<int, 1>{});
         };
         if (full) {
@@ -725,11 +739,14 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           // chunks would drain the exponential unit's pipeline at every chunk)
           do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 0>{});
           do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{});
-        } else if (p.window == 0) {
-          // plain causal boundary block: the same straight-line pass with one compare per
-          // element; skipping the fully masked chunks would bring the branches back
+        } else if (block_edges(qtile, kblock, p.window, p.sinks) == EDGE_CAUSAL) {
+          // only the causal edge cuts the block: the same straight-line pass with one compare
+          // per element; skipping the fully masked chunks would bring the branches back
           do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 2>{});
           do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 2>{});
+        } else if (block_edges(qtile, kblock, p.window, p.sinks) == EDGE_WINDOW) {
+          do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 3>{});
+          do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 3>{});
         } else {
           chunk(std::integral_constant<int, 0>{});
           chunk(std::integral_constant<int, 1>{});

@@ -60,6 +60,21 @@ __host__ __device__ inline bool block_fully_visible(int tile, int j, int window,
   return true;
 }
 
+// Which edges of the mask cut through query tile `tile` x key block `j` (for blocks that are
+// not fully visible): only the causal edge k <= q (plain causal, or windows whose lower edge
+// stays below the block), only the window's lower edge k > q - (window - sinks) (blocks below
+// the diagonal that hold no sink keys), or both / sinks involved.  One-edge blocks need a
+// single compare per element against a per-thread limit.
+enum { EDGE_CAUSAL = 0, EDGE_WINDOW = 1, EDGE_BOTH = 2 };
+__host__ __device__ inline int block_edges(int tile, int j, int window, int sinks) {
+  if (window == 0) return EDGE_CAUSAL;
+  const int span = window - sinks;
+  const int last_row = tile * kTile + kTile - 1;
+  if (j * kTile > last_row - span) return EDGE_CAUSAL;           // lower edge below the block
+  if (j < tile && j * kTile >= sinks) return EDGE_WINDOW;        // causal edge above, no sink keys
+  return EDGE_BOTH;
+}
+
 __host__ __device__ inline bool key_visible(int q, int k, int window, int sinks) {
   if (k > q) return false;
   if (window == 0) return true;

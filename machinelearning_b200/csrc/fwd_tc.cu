@@ -589,9 +589,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // its own are too few to cover the unit's latency (measured: 1760 clocks per row with
         // per-chunk branches against 1130 without).
         const int k0 = j * kTile;
-        if (!block_fully_visible(tile, j, p.window, p.sinks) && p.window == 0) {
-          // plain causal: the row sees the columns up to its own position -- one compare per
-          // element against a per-thread limit
+        const int edges = block_fully_visible(tile, j, p.window, p.sinks)
+                              ? -1 : block_edges(tile, j, p.window, p.sinks);
+        if (edges == EDGE_CAUSAL) {
+          // only the causal edge cuts the block: the row sees the columns up to its own
+          // position -- one compare per element against a per-thread limit
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int last = qpos - (k0 + 32 * c);                       // last visible column of the chunk
@@ -600,7 +602,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             for (int i = 0; i < 32; ++i)
               if (i > last) sv[c][i] = __float_as_uint(-INFINITY);
           }
-        } else if (!block_fully_visible(tile, j, p.window, p.sinks)) {
+        } else if (edges == EDGE_WINDOW) {
+          // only the window's lower edge cuts the block: the row sees the columns from va on
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int first_vis = va - (k0 + 32 * c);                    // first visible column of the chunk
+            if (__all_sync(0xffffffffu, first_vis <= 0)) continue;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (i < first_vis) sv[c][i] = __float_as_uint(-INFINITY);
+          }
+        } else if (edges == EDGE_BOTH) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int x0 = k0 + 32 * c, x1 = x0 + 31;
