@@ -39,7 +39,7 @@ extern "C" {
  * (None -> AUTO, False -> SIMT, True -> TENSOR) */
 #define NLFA_PATH_AUTO 0
 #define NLFA_PATH_SIMT 1   /* fp32 FMA kernels: every dtype, every head dim */
-#define NLFA_PATH_TENSOR 2 /* TMA + tcgen05 + TMEM kernels: f16/bf16, D in {64,128} */
+#define NLFA_PATH_TENSOR 2 /* TMA + tcgen05 + TMEM kernels: f16/bf16 (D = 32 on 64-wide tiles) */
 
 /* status codes: 0 is success, everything else is a refusal or a failure */
 #define NLFA_OK 0

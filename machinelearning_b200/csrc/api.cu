@@ -128,7 +128,7 @@ const char* nlfa_strerror(int status) {
     case NLFA_ERR_BAD_HEAD_DIM: return "unsupported head dim (32, 64, 128)";
     case NLFA_ERR_BAD_WINDOW: return "bad window/sinks (need window >= 0 and 0 <= sinks < window)";
     case NLFA_ERR_MISALIGNED: return "base pointer is not 16-byte aligned";
-    case NLFA_ERR_UNSUPPORTED_PATH: return "tensor-core path needs float16/bfloat16 and head dim 64 or 128";
+    case NLFA_ERR_UNSUPPORTED_PATH: return "tensor-core path needs float16/bfloat16";
     case NLFA_ERR_NOT_SM100: return "device is not compute capability 10.x";
     case NLFA_ERR_CUDA: return "CUDA runtime or driver call failed";
     case NLFA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
@@ -151,7 +151,7 @@ int nlfa_resolve_path(int dtype, int head_dim, int path) {
   if (dtype != NLFA_DTYPE_F32 && dtype != NLFA_DTYPE_F16 && dtype != NLFA_DTYPE_BF16)
     return -NLFA_ERR_BAD_DTYPE;
   if (head_dim != 32 && head_dim != 64 && head_dim != 128) return -NLFA_ERR_BAD_HEAD_DIM;
-  const bool tensor_ok = dtype != NLFA_DTYPE_F32 && (head_dim == 64 || head_dim == 128);
+  const bool tensor_ok = dtype != NLFA_DTYPE_F32;      // head dim 32 runs the 64-wide kernels, zero-padded by TMA
   if (path == NLFA_PATH_SIMT) return NLFA_PATH_SIMT;
   if (path == NLFA_PATH_TENSOR) return tensor_ok ? NLFA_PATH_TENSOR : -NLFA_ERR_UNSUPPORTED_PATH;
   if (path == NLFA_PATH_AUTO) return tensor_ok ? NLFA_PATH_TENSOR : NLFA_PATH_SIMT;

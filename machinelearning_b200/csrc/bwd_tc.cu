@@ -879,7 +879,10 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
                   const void* o, const float* lse, void* dq, void* dk, void* dv, float* delta,
                   int passes, unsigned* status, cudaStream_t stream) {
   if (p.dtype != NLFA_DTYPE_F16 && p.dtype != NLFA_DTYPE_BF16) return NLFA_ERR_UNSUPPORTED_PATH;
-  if (p.D != 64 && p.D != 128) return NLFA_ERR_UNSUPPORTED_PATH;
+  if (p.D != 32 && p.D != 64 && p.D != 128) return NLFA_ERR_UNSUPPORTED_PATH;
+  // Head dim 32 runs the 64-wide kernels: the tensor maps describe the real 32 columns, the
+  // TMA boxes are 64 wide, so loads fill columns 32-63 with zeros (which add nothing to any
+  // product) and stores drop them.
   int st = NLFA_OK;
   if (passes & NLFA_PASS_DELTA) st = launch_delta(p, dout, o, delta, stream);
   if (st != NLFA_OK) return st;
@@ -890,7 +893,7 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   if (st == NLFA_OK) st = make_tile_map(&mdo, dout, p.dtype, p.B, p.T, p.H, p.D, kTile);
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
-  if (p.D == 64) {
+  if (p.D <= 64) {
     return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
                 : launch_both<__half, 64, 4, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
   }

@@ -850,7 +850,10 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
 int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v, void* o,
                   float* lse, unsigned* status, cudaStream_t stream) {
   if (p.dtype != NLFA_DTYPE_F16 && p.dtype != NLFA_DTYPE_BF16) return NLFA_ERR_UNSUPPORTED_PATH;
-  if (p.D != 64 && p.D != 128) return NLFA_ERR_UNSUPPORTED_PATH;
+  if (p.D != 32 && p.D != 64 && p.D != 128) return NLFA_ERR_UNSUPPORTED_PATH;
+  // Head dim 32 runs the 64-wide kernels: the tensor maps describe the real 32 columns, the
+  // TMA boxes are 64 wide, so loads fill columns 32-63 with zeros (which add nothing to any
+  // product) and stores drop them.
   if (!(p.scale > 0.f)) return NLFA_ERR_UNSUPPORTED_PATH;     // row max is taken before scaling
   CUtensorMap mq, mk, mv, mo;
   int st = make_tile_map(&mq, q, p.dtype, p.B, p.T, p.H, p.D, kTile);
@@ -859,7 +862,7 @@ int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v,
   if (st == NLFA_OK) st = make_tile_map(&mo, o, p.dtype, p.B, p.T, p.H, p.D, kTile);
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
-  if (p.D == 64) {
+  if (p.D <= 64) {
     return bf16 ? launch_t<__nv_bfloat16, 64, 2, 3, 2>(p, mq, mk, mv, mo, o, lse, status, stream)
                 : launch_t<__half, 64, 2, 3, 2>(p, mq, mk, mv, mo, o, lse, status, stream);
   }

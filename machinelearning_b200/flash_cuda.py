@@ -35,10 +35,12 @@ log = logging.getLogger("machinelearning_b200.flash_cuda")
 SUPPORTED_HEAD_DIMS = (32, 64, 128)
 SUPPORTED_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
 MMA_DTYPES = (torch.float16, torch.bfloat16)      # tcgen05 kind::f16 operands
-# Head dims with a tensor-core kernel, forward and backward alike.  The
-# reference stops its tensor-core backward at 64 (flash_cuda.py:48-51).
-MMA_HEAD_DIMS = (64, 128)
-MMA_BWD_HEAD_DIMS = (64, 128)
+# Head dims with a tensor-core kernel, forward and backward alike (32 runs the
+# 64-wide kernels on tiles that TMA pads with zeros).  The reference stops its
+# tensor-core backward at 64 (flash_cuda.py:48-51).
+MMA_HEAD_DIMS = (32, 64, 128)
+MMA_BWD_HEAD_DIMS = (32, 64, 128)
+_PROBE_HEAD_DIMS = (64, 128)                      # kernel instantiations the load-time probe runs
 
 _DTYPE_CODE = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16,
                torch.bfloat16: _lib.DTYPE_BF16}
@@ -62,7 +64,7 @@ def _probe_mma(lib) -> tuple[bool, str]:
         errs = (ctypes.c_float * 2)()
         stream = torch.cuda.current_stream().cuda_stream
         for code, name in ((_lib.DTYPE_BF16, "bf16"), (_lib.DTYPE_F16, "f16")):
-            for d in MMA_HEAD_DIMS:
+            for d in _PROBE_HEAD_DIMS:
                 st = lib.nlfa_selftest(code, d, ws.data_ptr(), ws.numel(), errs, stream)
                 if st != _lib.OK:
                     return False, (f"self-test failed for {name} D={d}: {_lib.strerror(st)} "

@@ -52,7 +52,8 @@ def test_path_resolution_mirrors_use_mma(lib):
     assert lib.nlfa_resolve_path(L.DTYPE_BF16, 64, L.PATH_AUTO) == L.PATH_TENSOR
     assert lib.nlfa_resolve_path(L.DTYPE_F16, 128, L.PATH_AUTO) == L.PATH_TENSOR
     assert lib.nlfa_resolve_path(L.DTYPE_F32, 64, L.PATH_AUTO) == L.PATH_SIMT
-    assert lib.nlfa_resolve_path(L.DTYPE_BF16, 32, L.PATH_AUTO) == L.PATH_SIMT
+    assert lib.nlfa_resolve_path(L.DTYPE_BF16, 32, L.PATH_AUTO) == L.PATH_TENSOR   # zero-padded 64-wide tiles
+    assert lib.nlfa_resolve_path(L.DTYPE_F32, 32, L.PATH_AUTO) == L.PATH_SIMT
     assert lib.nlfa_resolve_path(L.DTYPE_BF16, 64, L.PATH_SIMT) == L.PATH_SIMT
     assert lib.nlfa_resolve_path(L.DTYPE_F32, 64, L.PATH_TENSOR) == -7     # use_mma=True on fp32
     assert lib.nlfa_resolve_path(L.DTYPE_BF16, 48, L.PATH_AUTO) == -4

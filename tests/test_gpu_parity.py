@@ -77,8 +77,7 @@ def test_simt_fp32_matches_reference_golden(fc, path):
         assert mabs(got, g[name]) <= 2 * ABS_F32, name
 
 
-@pytest.mark.parametrize("path", [p for p in golden_paths() if "_d64" in p.stem or "_d128" in p.stem
-                                  or "w256" in p.stem], ids=lambda p: p.stem)
+@pytest.mark.parametrize("path", golden_paths(), ids=lambda p: p.stem)
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_tensor_core_matches_reference_golden(fc, path, dtype):
     g = load_golden(path)
@@ -104,6 +103,8 @@ CASES = [
     (2, 100, 4, 2, 64, 0, 0),        # the reference's device-test shape (tests.py:364) at D=64
     (2, 100, 4, 2, 128, 0, 0),
     (1, 33, 2, 1, 64, 0, 0),         # shorter than one tile
+    (2, 300, 4, 2, 32, 0, 0),        # head dim 32 on the 64-wide tensor-core kernels
+    (1, 520, 2, 2, 32, 64, 4),
     (1, 128, 1, 1, 64, 0, 0),        # exactly one tile
     (1, 129, 2, 2, 128, 0, 0),       # one row into the second tile
     (1, 640, 3, 1, 64, 0, 0),        # odd tile count, GQA group 3
