@@ -863,8 +863,8 @@ int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v,
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D <= 64) {
-    return bf16 ? launch_t<__nv_bfloat16, 64, 2, 4, 2>(p, mq, mk, mv, mo, o, lse, status, stream)
-                : launch_t<__half, 64, 2, 4, 2>(p, mq, mk, mv, mo, o, lse, status, stream);
+    return bf16 ? launch_t<__nv_bfloat16, 64, 2, 3, 2>(p, mq, mk, mv, mo, o, lse, status, stream)
+                : launch_t<__half, 64, 2, 3, 2>(p, mq, mk, mv, mo, o, lse, status, stream);
   }
   return bf16 ? launch_t<__nv_bfloat16, 128, 2, 2, 1>(p, mq, mk, mv, mo, o, lse, status, stream)
               : launch_t<__half, 128, 2, 2, 1>(p, mq, mk, mv, mo, o, lse, status, stream);
