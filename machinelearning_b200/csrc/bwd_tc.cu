@@ -23,10 +23,11 @@
 // while the exponentials are computed; the stationary tiles are double buffered
 // so the next unit's loads and first products overlap the current unit's tail.
 //
-// TMEM: T0 at column 0, T1 at 128 (fp32); outputs accumulate at 256 (dQ: D
-// columns; dV then dK: 2 D columns).  The 16-bit P / dS operands of the output
-// products live in their own columns when there is room (everything except
-// dK/dV at D = 128, where they overwrite the columns of T0/T1 just read).
+// TMEM: with streamed tiles of YR rows, T0 at column 0 and T1 at YR (fp32); outputs
+// accumulate at 2 YR (dQ: D columns; dV then dK: 2 D columns).  The 16-bit P / dS
+// operands of the output products live in columns of their own behind the outputs.
+// YR is 128 at D = 64 and 64 at D = 128, where shared memory would hold only two
+// stages of 128-row tiles (one load in flight) and TMEM no separate P / dS columns.
 #include <atomic>
 #include <type_traits>
 
@@ -64,7 +65,8 @@ enum { MODE_DQ = 0, MODE_DKV = 1 };
 struct BwdParams {
   int T, H, Hkv;
   int window, sinks;
-  int n_tiles;
+  int n_tiles;           // 128-row tiles
+  int n_ytiles;          // streamed tiles (YR rows each)
   int BH;                // B * H (dQ) or B * Hkv (dK/dV)
   int total_units;       // n_tiles * BH
   float scale, scale_log2;
@@ -76,12 +78,13 @@ struct BwdParams {
   unsigned* sched;       // this launch's two counters
 };
 
-template <int D, int STAGES, int XBUF>
+template <int D, int STAGES, int XBUF, int YR>
 struct BwdSmem {
-  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kTileBytes = kTile * D * 2;              // stationary tile: 128 rows
+  static constexpr int kYTileBytes = YR * D * 2;                // streamed tile: YR rows
   static constexpr int kX = 0;                                  // [XBUF] x (X0, X1)
   static constexpr int kY = kX + XBUF * 2 * kTileBytes;         // per stage: Y0, Y1
-  static constexpr int kVec = kY + STAGES * 2 * kTileBytes;     // per stage: -lse2[128], -delta[128]
+  static constexpr int kVec = kY + STAGES * 2 * kYTileBytes;    // per stage: -lse2[YR], -delta[YR]
   static constexpr int kBar = kVec + STAGES * 1024;
   // barriers: x_full[XBUF], x_empty[XBUF], t_full, t_consumed, pd_full, out_ready,
   //           sched_full[kRing], y_full[S], y_empty[S]
@@ -110,7 +113,9 @@ struct BwdUnit {
   }
 };
 
-template <int MODE>
+// `YR` is the height of a streamed tile (128, or 64 where shared memory is short); the streamed
+// indices s_lo, extra, n_inner count tiles of that height.
+template <int MODE, int YR>
 __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p) {
   BwdUnit<MODE> w;
   const int rank = u / p.BH;
@@ -121,21 +126,26 @@ __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p
     w.b = bh / p.H;
     w.h = bh - w.b * p.H;
     w.hk = w.h / group;
-    const TileRange r = tile_range(w.tile, p.window, p.sinks);
-    w.s_lo = r.lo;
-    w.extra = r.sink_blocks < r.lo ? r.sink_blocks : r.lo;
-    w.n_inner = w.extra + (r.hi - r.lo + 1);
+    // keys [lo_pos, last row of the tile], plus the sink prefix
+    const int q_last = w.tile * kTile + kTile - 1;
+    const int lo_pos = p.window > 0 ? w.tile * kTile - (p.window - p.sinks) + 1 : 0;
+    int hi = q_last / YR;
+    hi = hi < p.n_ytiles - 1 ? hi : p.n_ytiles - 1;
+    w.s_lo = lo_pos > 0 ? lo_pos / YR : 0;
+    const int sink_tiles = p.window > 0 ? (p.sinks + YR - 1) / YR : 0;
+    w.extra = sink_tiles < w.s_lo ? sink_tiles : w.s_lo;
+    w.n_inner = w.extra + (hi - w.s_lo + 1);
     w.n_iters = w.n_inner;
   } else {
     w.tile = rank;                              // early key blocks are seen by the most queries
     w.b = bh / p.Hkv;
     w.hk = bh - w.b * p.Hkv;
     w.h = w.hk * group;
-    w.s_lo = w.tile;
-    int s_hi = p.n_tiles - 1;
+    w.s_lo = w.tile * (kTile / YR);             // first query tile that reaches the block
+    int s_hi = p.n_ytiles - 1;
     if (p.window > 0 && w.tile >= (p.sinks + kTile - 1) / kTile) {
       const int last_q = w.tile * kTile + kTile - 1 + (p.window - p.sinks) - 1;
-      const int hi = last_q / kTile;
+      const int hi = last_q / YR;
       s_hi = hi < s_hi ? hi : s_hi;
     }
     w.extra = 0;
@@ -145,21 +155,27 @@ __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p
   return w;
 }
 
-template <typename T, int D, int MODE, int STAGES, int XBUF>
+// tm_x0 / tm_x1: the stationary tensors (dQ: Q, dO; dK/dV: K, V), boxes of 128 rows;
+// tm_y0 / tm_y1: the streamed tensors (dQ: K, V; dK/dV: Q, dO), boxes of YR rows.
+template <typename T, int D, int MODE, int STAGES, int XBUF, int YR>
 __global__ void __launch_bounds__(512, 1)
-bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_x1,
+              const __grid_constant__ CUtensorMap tm_y0, const __grid_constant__ CUtensorMap tm_y1,
               const __grid_constant__ CUtensorMap tm_out0,
               const __grid_constant__ CUtensorMap tm_out1, const BwdParams p) {
-  using L = BwdSmem<D, STAGES, XBUF>;
+  using L = BwdSmem<D, STAGES, XBUF, YR>;
+  static_assert(YR == 64 || YR == 128, "streamed tiles are 64 or 128 rows");
   constexpr int kBoxes = D / 64;
-  constexpr int kBoxBytes = kTile * 128;
+  constexpr int kBoxBytes = kTile * 128;          // one 64-column box of a stationary tile
+  constexpr int kYBoxBytes = YR * 128;            // ... of a streamed tile
+  constexpr int kCh = YR / 64;                    // 32-column chunks per compute thread
   constexpr bool kBf16 = Pack2<T>::kIsBf16;
-  constexpr uint32_t kOutCol = 256;
+  constexpr uint32_t kT1Col = YR;                 // T0 at column 0, T1 behind it
+  constexpr uint32_t kOutCol = 2 * YR;
   constexpr int kOutCols = MODE == MODE_DQ ? D : 2 * D;
-  constexpr bool kSep = (256 + kOutCols + 128) <= 512;        // room for separate P / dS columns
-  constexpr uint32_t kPCol = kSep ? 256 + kOutCols : 0;        // P  (dK/dV only)
-  constexpr uint32_t kDsCol = kSep ? 256 + kOutCols + 64 : 128;
+  constexpr bool kSep = (2 * YR + kOutCols + YR) <= 512;       // room for separate P / dS columns
+  constexpr uint32_t kPCol = kSep ? 2 * YR + kOutCols : 0;     // P  (dK/dV only)
+  constexpr uint32_t kDsCol = kSep ? 2 * YR + kOutCols + YR / 2 : YR;
   constexpr int kRing = L::kRing;
   constexpr int kRegsLaunch = 128, kRegsCompute = 200, kRegsOther = 56;    // per thread
 
@@ -308,10 +324,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
   } else if (warp == 8) {
     // ========================= scheduler + TMA producer ======================
-    const CUtensorMap* mx0 = MODE == MODE_DQ ? &tm_q : &tm_k;
-    const CUtensorMap* mx1 = MODE == MODE_DQ ? &tm_do : &tm_v;
-    const CUtensorMap* my0 = MODE == MODE_DQ ? &tm_k : &tm_q;
-    const CUtensorMap* my1 = MODE == MODE_DQ ? &tm_v : &tm_do;
+    const CUtensorMap* mx0 = &tm_x0;
+    const CUtensorMap* mx1 = &tm_x1;
+    const CUtensorMap* my0 = &tm_y0;
+    const CUtensorMap* my1 = &tm_y1;
     if (lane == 0) {
       tma_prefetch_desc(mx0);
       tma_prefetch_desc(mx1);
@@ -328,7 +344,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         u = static_cast<int>(atomicAdd(&p.sched[0], 1u));
         if (u >= p.total_units) u = -1;
         BwdUnit<MODE> w{};
-        if (u >= 0) w = make_bwd_unit<MODE>(u, p);
+        if (u >= 0) w = make_bwd_unit<MODE, YR>(u, p);
         volatile int* e = sched_ring + 8 * (uc % kRing);
         e[0] = u; e[1] = w.tile; e[2] = w.b; e[3] = w.h;
         e[4] = w.hk; e[5] = w.s_lo; e[6] = w.n_inner; e[7] = MODE == MODE_DQ ? w.extra : w.n_iters;
@@ -375,12 +391,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // The tile loads go out first; the per-row vectors (plain loads, a full memory latency)
         // follow while they are in flight, and the arrival that completes the stage comes last.
         if (lane == 0) {
-          mbar_expect_tx(bar(Y_FULL + s), 2 * L::kTileBytes);
-          const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes;
+          mbar_expect_tx(bar(Y_FULL + s), 2 * L::kYTileBytes);
+          const uint32_t y0 = base + L::kY + s * 2 * L::kYTileBytes;
           for (int x = 0; x < kBoxes; ++x) {
-            tma_load_4d(y0 + x * kBoxBytes, my0, bar(Y_FULL + s), 64 * x, yh, idx * kTile, w.b);
-            tma_load_4d(y0 + L::kTileBytes + x * kBoxBytes, my1, bar(Y_FULL + s), 64 * x, yh,
-                        idx * kTile, w.b);
+            tma_load_4d(y0 + x * kYBoxBytes, my0, bar(Y_FULL + s), 64 * x, yh, idx * YR, w.b);
+            tma_load_4d(y0 + L::kYTileBytes + x * kYBoxBytes, my1, bar(Y_FULL + s), 64 * x, yh,
+                        idx * YR, w.b);
           }
         }
         if (MODE == MODE_DKV) {
@@ -388,12 +404,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           float* vec = reinterpret_cast<float*>(gen + L::kVec + s * 1024);
           const long long row0 = (static_cast<long long>(w.b) * p.H + yh) * p.T;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int c = lane * 4 + i;
-            const int qpos = idx * kTile + c;
+          for (int i = 0; i < YR / 32; ++i) {
+            const int c = lane * (YR / 32) + i;
+            const int qpos = idx * YR + c;
             const bool in = qpos < p.T;
             vec[c] = in ? -p.lse[row0 + qpos] * kLog2e : -INFINITY;
-            vec[128 + c] = in ? -p.delta[row0 + qpos] : 0.f;
+            vec[YR + c] = in ? -p.delta[row0 + qpos] : 0.f;
           }
           __syncwarp();
         }
@@ -419,44 +435,48 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         return u;
       };
-      constexpr uint32_t idesc_t = make_idesc(kBf16, 128, 128, false, false);
+      constexpr uint32_t idesc_t = make_idesc(kBf16, 128, YR, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, 128, D, false, true);
 
       // T0 = X0 Y0^T, T1 = X1 Y1^T for global iteration `g` of unit buffer `xb`
       auto issue_t = [&](int xb, int g) {
         const int s = g % STAGES;
         const uint32_t x0 = base + L::kX + xb * 2 * L::kTileBytes, x1 = x0 + L::kTileBytes;
-        const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes, y1 = y0 + L::kTileBytes;
+        const uint32_t y0 = base + L::kY + s * 2 * L::kYTileBytes, y1 = y0 + L::kYTileBytes;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          umma_ss(leader, tmem + 0, make_smem_desc(x0 + off, 16, 1024), make_smem_desc(y0 + off, 16, 1024),
+          const uint32_t xoff = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+          const uint32_t yoff = (kk >> 2) * kYBoxBytes + (kk & 3) * 32;
+          umma_ss(leader, tmem + 0, make_smem_desc(x0 + xoff, 16, 1024), make_smem_desc(y0 + yoff, 16, 1024),
                  idesc_t, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-          umma_ss(leader, tmem + 128, make_smem_desc(x1 + off, 16, 1024), make_smem_desc(y1 + off, 16, 1024),
+          const uint32_t xoff = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+          const uint32_t yoff = (kk >> 2) * kYBoxBytes + (kk & 3) * 32;
+          umma_ss(leader, tmem + kT1Col, make_smem_desc(x1 + xoff, 16, 1024), make_smem_desc(y1 + yoff, 16, 1024),
                  idesc_t, kk > 0 ? 1u : 0u);
         }
         umma_commit(leader, bar(T_FULL));
       };
       auto issue_out = [&](int g, uint32_t acc) {
         const int s = g % STAGES;
-        const uint32_t y0 = base + L::kY + s * 2 * L::kTileBytes, y1 = y0 + L::kTileBytes;
+        const uint32_t y0 = base + L::kY + s * 2 * L::kYTileBytes, y1 = y0 + L::kYTileBytes;
         // 16-bit operand of k-step kk: 8 TMEM columns per step.  The dV and dK steps alternate,
         // so consecutive instructions never update the same accumulator.
+        constexpr int kStepsPerHalf = YR / 32;
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk) {
-          const uint32_t acol = kSep ? 8 * kk : 64 * (kk >> 2) + 8 * (kk & 3);
+        for (int kk = 0; kk < YR / 16; ++kk) {
+          const uint32_t acol = kSep ? 8 * kk
+                                     : (YR / 2) * (kk / kStepsPerHalf) + 8 * (kk % kStepsPerHalf);
           if (MODE == MODE_DQ) {
             umma_ts(leader, tmem + kOutCol, tmem + kDsCol + acol,
-                   make_smem_desc(y0 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
+                   make_smem_desc(y0 + kk * 2048, kYBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           } else {
             umma_ts(leader, tmem + kOutCol, tmem + kPCol + acol,
-                   make_smem_desc(y1 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
+                   make_smem_desc(y1 + kk * 2048, kYBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
             umma_ts(leader, tmem + kOutCol + D, tmem + kDsCol + acol,
-                   make_smem_desc(y0 + kk * 2048, kBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
+                   make_smem_desc(y0 + kk * 2048, kYBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
           }
         }
         umma_commit(leader, bar(OUT_READY));
@@ -539,13 +559,19 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     // ================================= compute ===============================
     setmaxnreg_inc<kRegsCompute>();
     if (!dead) {
-    const int half = warp >> 2;                      // which 64 columns of the row
+    const int half = warp >> 2;                      // which YR / 2 columns of the row
     const uint32_t lane_base = 32u * (warp & 3);
     const int row = 32 * (warp & 3) + lane;          // row of the stationary tile == TMEM lane
-    const uint32_t t0 = tmem_addr(tmem, lane_base, 64 * half);
-    const uint32_t t1 = tmem_addr(tmem, lane_base, 128 + 64 * half);
-    const uint32_t p_dst = tmem_addr(tmem, lane_base, kSep ? kPCol + 32 * half : 64 * half);
-    const uint32_t ds_dst = tmem_addr(tmem, lane_base, kSep ? kDsCol + 32 * half : 128 + 64 * half);
+    const uint32_t t0 = tmem_addr(tmem, lane_base, (YR / 2) * half);
+    const uint32_t t1 = tmem_addr(tmem, lane_base, kT1Col + (YR / 2) * half);
+    const uint32_t p_dst = tmem_addr(tmem, lane_base, kSep ? kPCol + (YR / 4) * half : (YR / 2) * half);
+    const uint32_t ds_dst = tmem_addr(tmem, lane_base, kSep ? kDsCol + (YR / 4) * half
+                                                             : kT1Col + (YR / 2) * half);
+    // calls f(chunk 0) and, with two chunks per thread, f(chunk 1)
+    auto each_chunk = [&](auto&& f) {
+      f(std::integral_constant<int, 0>{});
+      if constexpr (kCh > 1) f(std::integral_constant<int, 1>{});
+    };
     const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
 
     bool ok = true;
@@ -619,24 +645,28 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_after();
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 2);
 
-        uint32_t sv[2][32], dv[2][32];
-        tmem_ld32(t0, sv[0]);
-        tmem_ld32(t0 + 32, sv[1]);
-        tmem_ld32(t1, dv[0]);
-        tmem_ld32(t1 + 32, dv[1]);
+        uint32_t sv[kCh][32], dv[kCh][32];
+#pragma unroll
+        for (int ch = 0; ch < kCh; ++ch) tmem_ld32(t0 + 32 * ch, sv[ch]);
+#pragma unroll
+        for (int ch = 0; ch < kCh; ++ch) tmem_ld32(t1 + 32 * ch, dv[ch]);
         tc_wait_ld();
         tc_fence_before();
         mbar_arrive(bar(T_CONSUMED));
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 3);
 
-        const int qtile = MODE == MODE_DQ ? w.tile : idx;
-        const int kblock = MODE == MODE_DQ ? idx : w.tile;
-        const bool full = block_fully_visible(qtile, kblock, p.window, p.sinks);
+        // positions of the (stationary tile) x (streamed tile) rectangle
+        const int q_lo = MODE == MODE_DQ ? w.tile * kTile : idx * YR;
+        const int q_hi = q_lo + (MODE == MODE_DQ ? kTile : YR) - 1;
+        const int k_lo = MODE == MODE_DQ ? idx * YR : w.tile * kTile;
+        const int k_hi = k_lo + (MODE == MODE_DQ ? YR : kTile) - 1;
+        const bool full = rect_fully_visible(q_lo, q_hi, k_lo, k_hi, p.window, p.sinks);
+        const int edges = rect_edges(q_lo, q_hi, k_lo, k_hi, p.window, p.sinks);
         const ulonglong2* vec2 =
-            reinterpret_cast<const ulonglong2*>(gen + L::kVec + s * 1024) + 16 * half;
-        const int other0 = idx * kTile + 64 * half;      // position of this thread's first column
+            reinterpret_cast<const ulonglong2*>(gen + L::kVec + s * 1024) + (YR / 8) * half;
+        const int other0 = idx * YR + (YR / 2) * half;   // position of this thread's first column
 
-        uint32_t pp[32], dd[32];
+        uint32_t pp[16 * kCh], dd[16 * kCh];
         // One 32-column chunk (8 groups of 4 columns).  kMasked: apply the per-element
         // visibility test; the test is one unsigned compare against the row's visible interval
         // [va, va + vw] (plus the sink prefix for the dQ orientation).
@@ -652,7 +682,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               nd_a = nd_b = negd_row;
             } else {
               const ulonglong2 nl = vec2[c4];              // -lse2 of columns 4 c4 .. 4 c4 + 3
-              const ulonglong2 nd = vec2[32 + c4];         // -delta
+              const ulonglong2 nd = vec2[YR / 4 + c4];     // -delta
               nl_a = nl.x; nl_b = nl.y; nd_a = nd.x; nd_b = nd.y;
             }
             const int c = 4 * c4;
@@ -735,28 +765,29 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           else do_chunk(ch_c, std::integral_constant<int, 1>{});
         };
         if (full) {
-          // interior blocks: one straight-line pass over all 64 columns (branches between the
+          // interior blocks: one straight-line pass over all columns (branches between the
           // chunks would drain the exponential unit's pipeline at every chunk)
-          do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 0>{});
-          do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{});
-        } else if (block_edges(qtile, kblock, p.window, p.sinks) == EDGE_CAUSAL) {
+          each_chunk([&](auto ch_c) { do_chunk(ch_c, std::integral_constant<int, 0>{}); });
+        } else if (edges == EDGE_CAUSAL) {
           // only the causal edge cuts the block: the same straight-line pass with one compare
           // per element; skipping the fully masked chunks would bring the branches back
-          do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 2>{});
-          do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 2>{});
-        } else if (block_edges(qtile, kblock, p.window, p.sinks) == EDGE_WINDOW) {
-          do_chunk(std::integral_constant<int, 0>{}, std::integral_constant<int, 3>{});
-          do_chunk(std::integral_constant<int, 1>{}, std::integral_constant<int, 3>{});
+          each_chunk([&](auto ch_c) { do_chunk(ch_c, std::integral_constant<int, 2>{}); });
+        } else if (edges == EDGE_WINDOW) {
+          each_chunk([&](auto ch_c) { do_chunk(ch_c, std::integral_constant<int, 3>{}); });
         } else {
-          chunk(std::integral_constant<int, 0>{});
-          chunk(std::integral_constant<int, 1>{});
+          each_chunk([&](auto ch_c) { chunk(ch_c); });
         }
         if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 4);
         // the previous iteration's output products must be done reading P / dS
         wait_out(g);
         if (!ok) break;
-        if (MODE == MODE_DKV) tmem_st32(p_dst, pp);
-        tmem_st32(ds_dst, dd);
+        if constexpr (kCh == 2) {
+          if (MODE == MODE_DKV) tmem_st32(p_dst, pp);
+          tmem_st32(ds_dst, dd);
+        } else {
+          if (MODE == MODE_DKV) tmem_st16(p_dst, pp);
+          tmem_st16(ds_dst, dd);
+        }
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(PD_FULL));
@@ -819,20 +850,29 @@ unsigned* sched_slot() {
   return base[dev] + 2 * slot;
 }
 
-template <typename T, int D, int MODE, int STAGES, int XBUF>
-int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
-                const CUtensorMap& mv, const CUtensorMap& mdo, const float* lse,
-                const float* delta, void* out0, void* out1, unsigned* status,
+template <typename T, int D, int MODE, int STAGES, int XBUF, int YR>
+int launch_mode(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
+                const float* lse, const float* delta, void* out0, void* out1, unsigned* status,
                 cudaStream_t stream) {
-  // output tiles leave through TMA stores: dQ is [B,T,H,D], dK and dV are [B,T,Hkv,D]
-  CUtensorMap mo0, mo1;
-  const int out_heads = MODE == MODE_DQ ? p.H : p.Hkv;
-  int mst = make_tile_map(&mo0, out0, p.dtype, p.B, p.T, out_heads, p.D, kTile);
+  // stationary tensors in boxes of 128 rows, streamed tensors in boxes of YR rows; output tiles
+  // leave through TMA stores: dQ is [B,T,H,D], dK and dV are [B,T,Hkv,D]
+  const void* x0 = MODE == MODE_DQ ? q : k;
+  const void* x1 = MODE == MODE_DQ ? dout : v;
+  const void* y0 = MODE == MODE_DQ ? k : q;
+  const void* y1 = MODE == MODE_DQ ? v : dout;
+  const int x_heads = MODE == MODE_DQ ? p.H : p.Hkv;
+  const int y_heads = MODE == MODE_DQ ? p.Hkv : p.H;
+  CUtensorMap mx0, mx1, my0, my1, mo0, mo1;
+  int mst = make_tile_map(&mx0, x0, p.dtype, p.B, p.T, x_heads, p.D, kTile);
+  if (mst == NLFA_OK) mst = make_tile_map(&mx1, x1, p.dtype, p.B, p.T, x_heads, p.D, kTile);
+  if (mst == NLFA_OK) mst = make_tile_map(&my0, y0, p.dtype, p.B, p.T, y_heads, p.D, YR);
+  if (mst == NLFA_OK) mst = make_tile_map(&my1, y1, p.dtype, p.B, p.T, y_heads, p.D, YR);
+  if (mst == NLFA_OK) mst = make_tile_map(&mo0, out0, p.dtype, p.B, p.T, x_heads, p.D, kTile);
   if (mst == NLFA_OK)
-    mst = make_tile_map(&mo1, MODE == MODE_DQ ? out0 : out1, p.dtype, p.B, p.T, out_heads, p.D, kTile);
+    mst = make_tile_map(&mo1, MODE == MODE_DQ ? out0 : out1, p.dtype, p.B, p.T, x_heads, p.D, kTile);
   if (mst != NLFA_OK) return mst;
-  using L = BwdSmem<D, STAGES, XBUF>;
-  auto kern = bwd_tc_kernel<T, D, MODE, STAGES, XBUF>;
+  using L = BwdSmem<D, STAGES, XBUF, YR>;
+  auto kern = bwd_tc_kernel<T, D, MODE, STAGES, XBUF, YR>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
       cudaSuccess)
     return NLFA_ERR_CUDA;
@@ -843,6 +883,7 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
   bp.window = p.window;
   bp.sinks = p.sinks;
   bp.n_tiles = (p.T + kTile - 1) / kTile;
+  bp.n_ytiles = (p.T + YR - 1) / YR;
   bp.BH = p.B * (MODE == MODE_DQ ? p.H : p.Hkv);
   bp.total_units = bp.n_tiles * bp.BH;
   bp.scale = p.scale;
@@ -855,21 +896,20 @@ int launch_mode(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
   bp.sched = sched_slot();
   if (bp.sched == nullptr) return NLFA_ERR_CUDA;
   const int grid = bp.total_units < sm_count_bwd() ? bp.total_units : sm_count_bwd();
-  kern<<<grid, 512, L::kDynamic, stream>>>(mq, mk, mv, mdo, mo0, mo1, bp);
+  kern<<<grid, 512, L::kDynamic, stream>>>(mx0, mx1, my0, my1, mo0, mo1, bp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
-template <typename T, int D, int STAGES, int XBUF>
-int launch_both(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk,
-                const CUtensorMap& mv, const CUtensorMap& mdo, const float* lse,
-                const float* delta, void* dq, void* dk, void* dv, int passes, unsigned* status,
-                cudaStream_t stream) {
+template <typename T, int D, int STAGES, int XBUF, int YR>
+int launch_both(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
+                const float* lse, const float* delta, void* dq, void* dk, void* dv, int passes,
+                unsigned* status, cudaStream_t stream) {
   int st = NLFA_OK;
   if (passes & NLFA_PASS_DKV)
-    st = launch_mode<T, D, MODE_DKV, STAGES, XBUF>(p, mq, mk, mv, mdo, lse, delta, dk, dv, status, stream);
+    st = launch_mode<T, D, MODE_DKV, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dk, dv, status, stream);
   if (st != NLFA_OK) return st;
   if (passes & NLFA_PASS_DQ)
-    st = launch_mode<T, D, MODE_DQ, STAGES, XBUF>(p, mq, mk, mv, mdo, lse, delta, dq, nullptr, status, stream);
+    st = launch_mode<T, D, MODE_DQ, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dq, nullptr, status, stream);
   return st;
 }
 
@@ -886,19 +926,17 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   int st = NLFA_OK;
   if (passes & NLFA_PASS_DELTA) st = launch_delta(p, dout, o, delta, stream);
   if (st != NLFA_OK) return st;
-  CUtensorMap mq, mk, mv, mdo;
-  st = make_tile_map(&mq, q, p.dtype, p.B, p.T, p.H, p.D, kTile);
-  if (st == NLFA_OK) st = make_tile_map(&mk, k, p.dtype, p.B, p.T, p.Hkv, p.D, kTile);
-  if (st == NLFA_OK) st = make_tile_map(&mv, v, p.dtype, p.B, p.T, p.Hkv, p.D, kTile);
-  if (st == NLFA_OK) st = make_tile_map(&mdo, dout, p.dtype, p.B, p.T, p.H, p.D, kTile);
-  if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D <= 64) {
-    return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
-                : launch_both<__half, 64, 4, 2>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
+    // 128-row streamed tiles, four stages, two stationary buffers
+    return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream)
+                : launch_both<__half, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream);
   }
-  return bf16 ? launch_both<__nv_bfloat16, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream)
-              : launch_both<__half, 128, 2, 1>(p, mq, mk, mv, mdo, lse, delta, dq, dk, dv, passes, status, stream);
+  // D = 128: shared memory holds one stationary pair (64 KB) and 128 KB of streamed tiles.
+  // As 64-row tiles that is four stages in flight instead of two, and the narrower T tiles
+  // leave TMEM columns for separate P / dS operands, i.e. for the one-iteration lookahead.
+  return bf16 ? launch_both<__nv_bfloat16, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream)
+              : launch_both<__half, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream);
 }
 
 #ifdef NLFA_TRACE

@@ -75,6 +75,22 @@ __host__ __device__ inline int block_edges(int tile, int j, int window, int sink
   return EDGE_BOTH;
 }
 
+// The same two questions for a rectangle of query positions [q_lo, q_hi] x key positions
+// [k_lo, k_hi] (tiles of unequal height).
+__host__ __device__ inline bool rect_fully_visible(int q_lo, int q_hi, int k_lo, int k_hi,
+                                                   int window, int sinks) {
+  if (k_hi > q_lo) return false;                                           // causal edge cuts in
+  if (window > 0 && k_lo <= q_hi - (window - sinks)) return false;         // lower window edge cuts in
+  return true;
+}
+__host__ __device__ inline int rect_edges(int q_lo, int q_hi, int k_lo, int k_hi, int window,
+                                          int sinks) {
+  if (window == 0) return EDGE_CAUSAL;
+  if (k_lo > q_hi - (window - sinks)) return EDGE_CAUSAL;                  // lower edge below the rectangle
+  if (k_hi <= q_lo && k_lo >= sinks) return EDGE_WINDOW;                   // causal edge above, no sink keys
+  return EDGE_BOTH;
+}
+
 __host__ __device__ inline bool key_visible(int q, int k, int window, int sinks) {
   if (k > q) return false;
   if (window == 0) return true;
