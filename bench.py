@@ -12,10 +12,10 @@ Prints one JSON line:
   value      whole-job TFLOP/s, algorithmic FLOPs (2 forward + 5 backward GEMMs
              over the unmasked pairs), inputs resident in HBM, CUDA-event time,
              slowest rank
-  e2e        the same metric through ``flash_cuda.flash_attn`` + autograd with
-             pinned host buffers: host->device copies of q, k, v, dO and
-             device->host copies of O, dQ, dK, dV inside the timed region, in
-             batch slices on three streams (``host_pipeline.HostPipeline``)
+  e2e        the same metric for pinned host buffers through
+             ``host_pipeline.HostPipeline`` (``flash_cuda.fwd`` + ``flash_cuda.bwd``
+             per batch slice, three streams): host->device copies of q, k, v, dO
+             and device->host copies of O, dQ, dK, dV inside the timed region
   roofline   the dominant kernel timed alone against the measured dense bf16 peak
   cpu_baseline  the reference's CPU attention (torch SDPA + autograd, restated in
              oracle/sdpa_port.py) on this box's host cores, bounded sample
@@ -338,7 +338,7 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
     scale = 1.0 / math.sqrt(D)
 
     # batch slices: copy-in, flash_attn + autograd and copy-out of neighbouring slices overlap
-    pipe = host_pipeline.HostPipeline(tuple(hq.shape), tuple(hk.shape), hq.dtype, dev, n_slices=16)
+    pipe = host_pipeline.HostPipeline(tuple(hq.shape), tuple(hk.shape), hq.dtype, dev, n_slices=8)
 
     def e2e_step():
         pipe.run(hq, hk, hv, hdo, *host_out, scale=scale, window=window, sinks=sinks)
@@ -398,7 +398,7 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
                    "flops_per_step_per_gpu": ff + fb},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "pipeline": "16 batch slices; copy-in, kernels and copy-out on three streams"},
+                "pipeline": "8 batch slices; copy-in, kernels and copy-out on three streams"},
         "gpu_launches": Step.launches_per_step * args.steps,
         "kernel_ms": kt,
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,

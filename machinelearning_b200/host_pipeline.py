@@ -4,8 +4,9 @@ The attention path is independent per batch element (``sharding.py``), so a
 host-resident batch does not have to be copied in whole before the first kernel
 starts: it is cut into batch slices, and three CUDA streams carry, at the same
 time, the host-to-device copy of slice ``i + 1``, the kernels of slice ``i``
-(``flash_cuda.flash_attn`` and its autograd backward, i.e. the same public call a
-caller with device tensors makes) and the device-to-host copy of slice ``i - 1``.
+(``flash_cuda.fwd`` and ``flash_cuda.bwd``, the native entries behind
+``flash_attn`` and its autograd backward) and the device-to-host copy of slice
+``i - 1``.
 PCIe is full duplex, so a step costs about the larger of the two copy times
 instead of the sum of both copies and the kernels.
 
@@ -27,9 +28,11 @@ class HostPipeline:
 
     ``run`` reads pinned host tensors ``q [B,T,H,D]``, ``k, v [B,T,Hkv,D]``,
     ``dout [B,T,H,D]`` and fills pinned host tensors ``o, dq [B,T,H,D]`` and
-    ``dk, dv [B,T,Hkv,D]``.  Everything is asynchronous with respect to the host;
-    the caller's current stream is made to wait for the last copy, so ordinary
-    stream semantics (events, ``synchronize``) apply to the results.
+    ``dk, dv [B,T,Hkv,D]``.  The inputs must be complete in host memory when ``run``
+    is called (they are read by a stream of the pipeline's own, not the caller's).
+    Everything is asynchronous with respect to the host; the caller's current
+    stream is made to wait for the last copy out, so ordinary stream semantics
+    (events, ``synchronize``) apply to the results.
     """
 
     def __init__(self, q_shape, kv_shape, dtype, device, n_slices: int = 8):
@@ -57,8 +60,14 @@ class HostPipeline:
                 raise ValueError("HostPipeline.run takes pinned host tensors")
         if scale is None:
             scale = 1.0 / math.sqrt(q.shape[-1])
+        if not flash_cuda.supports(self.dq_in, self.dk_in, self.dv_in) or not flash_cuda.is_available():
+            raise RuntimeError(f"flash_cuda cannot run these inputs ({flash_cuda.unavailable_reason()})")
+        flash_cuda.check_window(window, sinks)
+        use_mma = flash_cuda._tensor_path_fits(q.dtype, q.shape[-1]) and flash_cuda.mma_available()
         cur = torch.cuda.current_stream(self.device)
-        self.s_in.wait_stream(cur)
+        # The inputs are host memory, complete when this is called, so the copy-in stream does
+        # not wait for the caller's stream: the next call's copies in then overlap this call's
+        # copies out.  (Reuse of the device staging is ordered by the per-slice events.)
         self.s_out.wait_stream(cur)
         keep = []      # outputs of the compute stream, alive until the copy stream is done with them
         for i, (b0, b1) in enumerate(self.bounds):
@@ -73,15 +82,15 @@ class HostPipeline:
                 self.ev_in[i].record(self.s_in)
             with torch.cuda.stream(self.s_cmp):
                 self.s_cmp.wait_event(self.ev_in[i])
-                qs = self.dq_in[sl].detach().requires_grad_()
-                ks = self.dk_in[sl].detach().requires_grad_()
-                vs = self.dv_in[sl].detach().requires_grad_()
-                y = flash_cuda.flash_attn(qs, ks, vs, scale, use_mma=True, window=window, sinks=sinks)
-                grads = torch.autograd.grad(y, (qs, ks, vs), self.ddo_in[sl])
+                qs, ks, vs = self.dq_in[sl], self.dk_in[sl], self.dv_in[sl]
+                # the two native entries behind flash_attn and its autograd backward, called
+                # directly: no graph is needed when both directions run back to back
+                y, lse = flash_cuda.fwd(qs, ks, vs, scale, use_mma, window, sinks)
+                grads = flash_cuda.bwd(self.ddo_in[sl], qs, ks, vs, y, lse, scale, use_mma, window, sinks)
                 self.ev_cmp[i].record(self.s_cmp)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_cmp[i])
-                for dst, src in zip((o, dq, dk, dv), (y.detach(), *grads)):
+                for dst, src in zip((o, dq, dk, dv), (y, *grads)):
                     dst[sl].copy_(src, non_blocking=True)
                 keep.append((y, grads))
         self.used = True
