@@ -161,6 +161,18 @@ int nlfa_selftest(int dtype, int head_dim, void* workspace, size_t workspace_byt
 int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,
                         float* s_out, float* o_out, void* stream);
 
+/* Host-only check of the mask geometry the tensor-core kernels rely on: for a
+ * sequence of T positions with the given window / sinks it compares, against the
+ * element-wise predicate of nanolab/mixers.py:125-132 evaluated for every
+ * (query, key) pair, (1) the range of key blocks a 128-row query tile is given,
+ * (2) the "every pair visible" claim for each (128-row tile) x (stream_rows-row
+ * tile) rectangle, in both orientations, and (3) the claim that only the causal
+ * edge or only the window's lower edge cuts a rectangle.  stream_rows is 64 or
+ * 128.  Returns 0 when all agree, otherwise 1 + the index of the first failing
+ * check (negative: bad arguments).  Needs no device.  No counterpart in the
+ * reference. */
+int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows);
+
 /* Reads (and clears) the device status word that bounded waits inside the
  * kernels write when they give up.  Synchronises the device.  Returns NLFA_OK
  * or NLFA_ERR_DEVICE_TIMEOUT; *raw receives the raw word when raw != NULL. */

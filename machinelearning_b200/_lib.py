@@ -40,6 +40,7 @@ SIGNATURES = {
     "nlfa_selftest": (_c_int, [_c_int, _c_int, _c_void_p, _c_size_t,
                                ctypes.POINTER(_c_float), _c_void_p]),
     "nlfa_selftest_tiles": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6),
+    "nlfa_check_mask_geometry": (_c_int, [_c_int] * 4),
     "nlfa_device_status": (_c_int, [ctypes.POINTER(ctypes.c_uint)]),
 }
 

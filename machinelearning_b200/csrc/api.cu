@@ -240,6 +240,62 @@ int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, c
                                static_cast<cudaStream_t>(stream));
 }
 
+int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows) {
+  if (T <= 0 || window < 0 || sinks < 0 || (window > 0 && sinks >= window) ||
+      (window == 0 && sinks != 0) || (stream_rows != 64 && stream_rows != 128))
+    return -NLFA_ERR_BAD_WINDOW;
+  const int n128 = (T + kTile - 1) / kTile;
+  const int nys = (T + stream_rows - 1) / stream_rows;
+  int check = 0;
+  // (1) key blocks given to a query tile cover every block with a visible pair
+  for (int t = 0; t < n128; ++t) {
+    const TileRange r = tile_range(t, window, sinks);
+    for (int j = 0; j < n128; ++j, ++check) {
+      bool any = false;
+      for (int q = t * kTile; q < (t + 1) * kTile && !any; ++q)
+        for (int k = j * kTile; k < (j + 1) * kTile && !any; ++k) any = key_visible(q, k, window, sinks);
+      const bool given = (j >= r.lo && j <= r.hi) || j < r.sink_blocks;
+      if (any && !given) return 1 + check;
+    }
+  }
+  // (2), (3): rectangles of a 128-row tile and a stream_rows-row tile, both orientations
+  for (int orient = 0; orient < 2; ++orient)
+    for (int t = 0; t < n128; ++t)
+      for (int y = 0; y < nys; ++y) {
+        const int q_lo = orient == 0 ? t * kTile : y * stream_rows;
+        const int q_hi = q_lo + (orient == 0 ? kTile : stream_rows) - 1;
+        const int k_lo = orient == 0 ? y * stream_rows : t * kTile;
+        const int k_hi = k_lo + (orient == 0 ? stream_rows : kTile) - 1;
+        bool all = true, causal_only = true, window_only = true;
+        for (int q = q_lo; q <= q_hi; ++q)
+          for (int k = k_lo; k <= k_hi; ++k) {
+            const bool vis = key_visible(q, k, window, sinks);
+            all = all && vis;
+            causal_only = causal_only && (vis == (k <= q));
+            window_only = window_only && (vis == (k > q - (window - sinks)));
+          }
+        // (a rectangle made fully visible by sink keys alone may be reported as cut: that only costs a mask)
+        if (rect_fully_visible(q_lo, q_hi, k_lo, k_hi, window, sinks) && !all) return 1 + check;
+        ++check;
+        const int e = rect_edges(q_lo, q_hi, k_lo, k_hi, window, sinks);
+        if (e == EDGE_CAUSAL && !causal_only) return 1 + check;
+        ++check;
+        if (e == EDGE_WINDOW && !window_only) return 1 + check;
+        ++check;
+        if (stream_rows == kTile) {
+          const int qt = orient == 0 ? t : y, kb = orient == 0 ? y : t;
+          if (block_fully_visible(qt, kb, window, sinks) && !all) return 1 + check;
+          ++check;
+          if (!all) {
+            const int be = block_edges(qt, kb, window, sinks);
+            if ((be == EDGE_CAUSAL && !causal_only) || (be == EDGE_WINDOW && !window_only)) return 1 + check;
+          }
+          ++check;
+        }
+      }
+  return 0;
+}
+
 size_t nlfa_selftest_workspace_bytes(void) {
   // q, k, v tiles (16-bit, D <= 128) then S [128,128] and O [128,128] float32
   return 3 * 128 * 128 * 2 + 2 * 128 * 128 * 4;

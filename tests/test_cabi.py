@@ -83,3 +83,21 @@ def test_argument_checks_answer_without_a_gpu(lib):
     errs = (ctypes.c_float * 2)()
     assert lib.nlfa_selftest(L.DTYPE_BF16, 64, one, 16, errs, None) == 11
     assert lib.nlfa_selftest(L.DTYPE_F32, 64, one, 1 << 20, errs, None) == 7
+
+
+@pytest.mark.parametrize("T,window,sinks", [
+    (1024, 0, 0), (300, 0, 0), (129, 0, 0),
+    (1024, 256, 0), (1024, 64, 4), (900, 300, 130), (700, 256, 0), (2048, 512, 4),
+    (300, 400, 4), (511, 64, 0), (640, 129, 128), (384, 128, 0), (385, 1, 0),
+])
+@pytest.mark.parametrize("stream_rows", [64, 128])
+def test_mask_geometry_matches_the_elementwise_predicate(lib, T, window, sinks, stream_rows):
+    """Block ranges, fully-visible tests and one-edge classifications against every (q, k) pair."""
+    assert lib.nlfa_check_mask_geometry(T, window, sinks, stream_rows) == 0
+
+
+def test_mask_geometry_rejects_bad_arguments(lib):
+    assert lib.nlfa_check_mask_geometry(0, 0, 0, 128) < 0
+    assert lib.nlfa_check_mask_geometry(256, 8, 8, 128) < 0
+    assert lib.nlfa_check_mask_geometry(256, 0, 4, 128) < 0
+    assert lib.nlfa_check_mask_geometry(256, 0, 0, 96) < 0
