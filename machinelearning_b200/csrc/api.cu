@@ -108,6 +108,15 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, i
   CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    // The encoder is a driver entry point and wants a context current on the calling thread.  A
+    // host thread that has made no runtime call yet (an autograd worker, say) has none: a
+    // runtime call binds the device's primary context, then the encoding is tried once more.
+    (void)cudaFree(nullptr);
+    r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   return r == CUDA_SUCCESS ? NLFA_OK : NLFA_ERR_CUDA;
 }
 

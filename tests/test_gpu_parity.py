@@ -264,3 +264,29 @@ def test_autocast_bridge_and_errors(fc):
     # empty batch is a no-op
     e = torch.empty(0, 16, 2, 64, device="cuda")
     assert fc.flash_attn(e, e, e, scale).shape == e.shape
+
+
+def test_backward_from_a_fresh_host_thread(fc):
+    """The first CUDA work of a host thread may be the backward (autograd runs it on a worker
+    thread): the tensor-map encoder then needs the library to bind a context first."""
+    import threading
+    torch.manual_seed(3)
+    q, k, v, do = (torch.randn(2, 100, 4, 64, device="cuda").bfloat16() for _ in range(4))
+    scale = 0.125
+    o, lse = fc.fwd(q, k, v, scale, True)
+    box = {}
+
+    def work():
+        try:
+            box["grads"] = fc.bwd(do, q, k, v, o, lse, scale, True)
+        except Exception as e:                                    # noqa: BLE001
+            box["error"] = e
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "error" not in box, box.get("error")
+    ref = fc.bwd(do, q, k, v, o, lse, scale, True)
+    torch.cuda.synchronize()
+    for got, want in zip(box["grads"], ref):
+        assert torch.equal(got, want)
