@@ -266,27 +266,37 @@ def test_autocast_bridge_and_errors(fc):
     assert fc.flash_attn(e, e, e, scale).shape == e.shape
 
 
-def test_backward_from_a_fresh_host_thread(fc):
-    """The first CUDA work of a host thread may be the backward (autograd runs it on a worker
-    thread): the tensor-map encoder then needs the library to bind a context first."""
+def test_calls_from_a_fresh_host_thread(fc):
+    """The first CUDA work of a host thread may be one of these calls (autograd runs the
+    backward on a worker thread): the tensor-map encoder is a driver entry point and needs the
+    library to bind a context to the thread first."""
     import threading
     torch.manual_seed(3)
     q, k, v, do = (torch.randn(2, 100, 4, 64, device="cuda").bfloat16() for _ in range(4))
     scale = 0.125
     o, lse = fc.fwd(q, k, v, scale, True)
+    ref = fc.bwd(do, q, k, v, o, lse, scale, True)
+    torch.cuda.synchronize()
     box = {}
 
-    def work():
+    def forward_first():
+        try:
+            box["fwd"] = fc.fwd(q, k, v, scale, True)
+        except Exception as e:                                    # noqa: BLE001
+            box["error"] = e
+
+    def dkv_pass_first():
         try:
             box["grads"] = fc.bwd(do, q, k, v, o, lse, scale, True)
         except Exception as e:                                    # noqa: BLE001
             box["error"] = e
 
-    t = threading.Thread(target=work)
-    t.start()
-    t.join()
-    assert "error" not in box, box.get("error")
-    ref = fc.bwd(do, q, k, v, o, lse, scale, True)
+    for target in (forward_first, dkv_pass_first):
+        t = threading.Thread(target=target)
+        t.start()
+        t.join()
+        assert "error" not in box, box.get("error")
     torch.cuda.synchronize()
+    assert torch.equal(box["fwd"][0], o) and torch.equal(box["fwd"][1], lse)
     for got, want in zip(box["grads"], ref):
         assert torch.equal(got, want)
