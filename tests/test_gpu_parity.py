@@ -300,3 +300,32 @@ def test_calls_from_a_fresh_host_thread(fc):
     assert torch.equal(box["fwd"][0], o) and torch.equal(box["fwd"][1], lse)
     for got, want in zip(box["grads"], ref):
         assert torch.equal(got, want)
+
+
+def test_cuda_graph_capture_and_replay(fc):
+    """Forward + backward captured in a CUDA graph replay bit-identically (the in-kernel
+    schedulers re-arm their counters at the end of every launch)."""
+    torch.manual_seed(5)
+    q, k, v, do = (torch.randn(2, 300, 4, 64, device="cuda").bfloat16() for _ in range(4))
+    scale = 0.125
+    o_ref, lse_ref = fc.fwd(q, k, v, scale, True)
+    g_ref = fc.bwd(do, q, k, v, o_ref, lse_ref, scale, True)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):                       # warm-up on the capture stream
+        fc.bwd(do, q, k, v, *fc.fwd(q, k, v, scale, True), scale, True)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o, lse = fc.fwd(q, k, v, scale, True)
+        grads = fc.bwd(do, q, k, v, o, lse, scale, True)
+    for _ in range(3):
+        for t in (o, lse, *grads):
+            t.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert device_status_ok()
+        assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+        for got, want in zip(grads, g_ref):
+            assert torch.equal(got, want)
