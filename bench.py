@@ -21,6 +21,11 @@ Prints one JSON line:
              oracle/sdpa_port.py) on this box's host cores, bounded sample
 
 ``--impl reference`` times only that CPU path, on the same config and metric.
+
+``--workload c4`` is the other half of the metric: tokens/s of the whole nanolab
+GPT training step (12 layers, d_model 768, 12x64 heads, context 1024, global
+batch 64 sequences split over the ranks, gradient all-reduce over NCCL) with the
+attention core in the library, next to the same step with the flag off (SDPA).
 """
 from __future__ import annotations
 
@@ -51,7 +56,12 @@ WORKLOAD_TEXT = {
     "c3": "sliding-window bf16 attention fwd+bwd, B=16 H=16 T=4096 D=64 window=256 (per GPU)",
     "c5": "long-context causal bf16 attention fwd+bwd, B=1 of 8, H=16 T=16384 D=128 (per GPU)",
 }
+WHOLE_MODEL = "c4"
+WHOLE_MODEL_TEXT = ("nanolab GPT training step, flash_cuda on: 12 layers d_model=768 12x64 heads RoPE RMSNorm "
+                    "QK-norm SwiGLU(2048) vocab=50304 context=1024, global batch 64 sequences, bf16 autocast, "
+                    "AdamW (stands in for nanolab's Muon+AdamW)")
 METRIC = "attention fwd+bwd TFLOP/s (bf16 causal)"
+METRIC_TOKENS = "nanolab tokens/sec (whole-model training step)"
 FALLBACK_PEAK_TFLOPS = 1590.0
 
 
@@ -415,23 +425,176 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------------------------------------
+# Whole-model arm: tokens/s of the GPT training step that calls the path
+# ----------------------------------------------------------------------------
+
+GLOBAL_BATCH = 64
+
+
+def whole_model_cpu_tokens_per_s(n_seq, reps, warmup=1):
+    """The same training step on the host cores (flag off: the mixer's SDPA branch), n_seq sequences."""
+    from machinelearning_b200 import whole_model as wm
+    torch.set_num_threads(os.cpu_count() or 1)
+    torch.manual_seed(0)
+    model = wm.GPT(wm.ModelShape(flash_cuda=False))
+    step = wm.DataParallelStep(model)
+    x, y = wm.synthetic_tokens(model.shape.vocab_size, n_seq, model.shape.block_size, seed=0)
+    times = []
+    for i in range(warmup + reps):
+        t0 = time.perf_counter()
+        step.step(x, y)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    return n_seq * model.shape.block_size / sec, sec
+
+
+def run_whole_model_reference_arm(args, rank):
+    if rank != 0:
+        return
+    n_seq = 2
+    reps = max(1, min(args.steps, 5))              # a step of the sample is seconds of host time
+    tok_s, sec = whole_model_cpu_tokens_per_s(n_seq, reps=reps, warmup=1)
+    sample = (f"{n_seq} of {GLOBAL_BATCH} sequences per step on the host cores, attention through torch SDPA "
+              f"(the mixer's own branch), bf16 autocast, median of {reps} timed steps of {sec:.2f} s after 1 warm-up")
+    line = {
+        "impl": "reference", "metric": METRIC_TOKENS, "value": tok_s, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3 * GLOBAL_BATCH / n_seq, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WHOLE_MODEL_TEXT.replace("flash_cuda on", "flash_cuda off, CPU"),
+                   "global_batch": GLOBAL_BATCH, "cpu_sample": sample},
+        "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_whole_model_arm(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from machinelearning_b200 import flash_cuda, sharding, whole_model as wm
+
+    if GLOBAL_BATCH % world:
+        raise SystemExit(f"global batch {GLOBAL_BATCH} does not split over {world} ranks")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if not flash_cuda.is_available():
+        raise SystemExit("attention library unavailable: " + str(flash_cuda.unavailable_reason()))
+    per_rank = GLOBAL_BATCH // world
+    lo = rank * per_rank
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def build(flag):
+        torch.manual_seed(0)                       # same weights on every rank
+        model = wm.GPT(wm.ModelShape(flash_cuda=flag)).to(dev)
+        return model, wm.DataParallelStep(model)
+
+    # counts the library's launches: 1 forward + 3 backward kernels per flash_attn call
+    calls = {"n": 0}
+    real_fwd = flash_cuda.fwd
+
+    def counted_fwd(*a, **k):
+        calls["n"] += 1
+        return real_fwd(*a, **k)
+    flash_cuda.fwd = counted_fwd
+
+    x_host, y_host = wm.synthetic_tokens(50304, GLOBAL_BATCH, 1024, seed=0)
+    x_pin, y_pin = x_host[lo:lo + per_rank].pin_memory(), y_host[lo:lo + per_rank].pin_memory()
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def measure(flag, steps, warmup, sample_clocks):
+        model, step = build(flag)
+        x, y = x_pin.to(dev), y_pin.to(dev)
+        for _ in range(warmup):
+            step.step(x, y)
+        barrier()
+        sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
+        if sampler:
+            sampler.__enter__()
+        calls["n"] = 0
+        resident = time_region(lambda: step.step(x, y), steps)
+        n_calls = calls["n"]
+        if sampler:
+            sampler.__exit__(None, None, None)
+        barrier()
+
+        def host_step():                          # token ids from pinned host memory, loss back to the host
+            xs, ys = x_pin.to(dev, non_blocking=True), y_pin.to(dev, non_blocking=True)
+            loss_host.copy_(step.step(xs, ys), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        host_step()
+        barrier()
+        e2e = time_region(host_step, max(3, min(steps, 10)))
+        barrier()
+        loss = float(loss_host)
+        flops_tok = model.flops_per_token()
+        del model, step
+        torch.cuda.empty_cache()
+        return (sharding.max_over_ranks(resident, dev), sharding.max_over_ranks(e2e, dev), n_calls, loss,
+                flops_tok, sampler.summary() if sampler else None)
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    ms, e2e_ms, n_calls, loss, flops_tok, clocks = measure(True, steps, warmup, True)
+    sdpa_ms, sdpa_e2e_ms, _, sdpa_loss, _, _ = measure(False, max(3, steps // 2), 3, False)
+    if rank != 0:
+        return
+    tokens = GLOBAL_BATCH * 1024
+    peak, peak_src = measured_peak()
+    tok_s = tokens / (ms * 1e-3)
+    line = {
+        "metric": METRIC_TOKENS, "value": tok_s, "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WHOLE_MODEL_TEXT, "global_batch": GLOBAL_BATCH, "per_gpu_batch": per_rank,
+                   "parallelism": f"data-parallel x{world}, flat-bucket NCCL all-reduce of the gradients",
+                   "l2": "activations and weights far larger than the 126 MB L2",
+                   "params": 123699612, "flops_per_token": flops_tok},
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 2 * x_pin.numel() * x_pin.element_size(), "d2h_bytes_per_step": 4},
+        "gpu_launches": 4 * n_calls,
+        "attention_calls_per_step": n_calls // steps,
+        "model_flops_utilisation": flops_tok * tok_s / world / 1e12 / peak,
+        "peak_source": peak_src,
+        "loss": loss,
+        "flag_off_sdpa": {"tokens_per_s": tokens / (sdpa_ms * 1e-3), "ms_per_step": sdpa_ms, "loss": sdpa_loss},
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_tok_s, sec = whole_model_cpu_tokens_per_s(2, reps=2)
+        line["cpu_baseline"] = {"value": cpu_tok_s, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                                "kind": "port",
+                                "sample": f"2 of {GLOBAL_BATCH} sequences per step on the host cores, flag off "
+                                          f"(SDPA), median of 2 steps of {sec:.2f} s"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + [WHOLE_MODEL])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    shape = WORKLOADS[args.workload]
+    shape = WORKLOADS.get(args.workload)
 
     if args.impl == "reference":
-        run_reference_arm(args, shape, rank, world)
+        if args.workload == WHOLE_MODEL:
+            run_whole_model_reference_arm(args, rank)
+        else:
+            run_reference_arm(args, shape, rank, world)
         return 0
 
     import torch.distributed as dist
@@ -445,7 +608,10 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_gpu_arm(args, shape, rank, world, local_rank)
+        if args.workload == WHOLE_MODEL:
+            run_whole_model_arm(args, rank, world, local_rank)
+        else:
+            run_gpu_arm(args, shape, rank, world, local_rank)
     finally:
         if world > 1:
             dist.destroy_process_group()

@@ -1,0 +1,307 @@
+"""The caller of the attention path: nanolab's GPT training step, restated.
+
+nanolab's own ``model.py`` / ``train.py`` use ``flash_cuda`` unchanged, but they
+are not part of this package, so the whole-model configuration (12 layers,
+d_model 768, 12 heads of 64, RoPE, RMSNorm, SwiGLU, vocabulary 50304, context
+1024, global batch 64 sequences) needs a caller that lives here.  This module is
+that caller and nothing more: the same layer arithmetic and the same parameter
+names as ``nanolab/model.py:178-245`` (``Block``, ``GPT``) and
+``nanolab/mixers.py:206-345`` (``Attention``), so a nanolab ``state_dict`` loads
+into it, and ``tests/golden/whole_model_tiny.npz`` (written by
+``tests/golden/make_whole_model_golden.py`` from nanolab itself) pins its loss and
+gradients to nanolab's.
+
+The attention core goes through ``mixer_glue.attention_core`` -- the routing of
+``Attention._flash_cuda_attn`` (``nanolab/mixers.py:347-370``) -- and falls back
+to SDPA exactly where nanolab's mixer does (CPU tensors, flag off).
+
+``DataParallelStep`` is the data-parallel training step of the whole-model
+configuration: one process per GPU, each on ``global_batch / world`` sequences,
+gradients averaged with one ``all_reduce`` per flat bucket (the convention of
+the reference's only data-parallel script: average every gradient that exists),
+then a fused AdamW step.  nanolab's phase-1 preset trains with Muon + AdamW;
+the optimiser is not on the attention path and AdamW stands in for it here.
+"""
+from __future__ import annotations
+
+import dataclasses
+import math
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import mixer_glue
+
+
+@dataclasses.dataclass
+class ModelShape:
+    """The fields of nanolab's ``Config`` (``nanolab/config.py:47-255``) this path reads.
+
+    Defaults are the ``phase1`` preset (``config.py:393-399``) with nanolab's
+    architecture defaults: QK-norm, gated attention, value residual, tied
+    embeddings, zero-initialised output projections.
+    """
+    n_layer: int = 12
+    d_model: int = 768
+    n_head: int = 12
+    n_kv_head: int = 0          # 0 -> n_head
+    head_dim: int = 64
+    vocab_size: int = 50304
+    block_size: int = 1024
+    rope_base: float = 10000.0
+    qk_norm: bool = True
+    gated_attention: bool = True
+    value_residual: bool = True
+    tie_embeddings: bool = True
+    zero_init_proj: bool = True
+    flash_cuda: bool = False    # ``--flash_cuda true`` (config.py:233-239)
+    swa_window: int = 0         # > 0: every layer is the SWA mixer (config.py:127-139)
+    swa_sinks: int = 0
+
+    def __post_init__(self):
+        if self.n_kv_head == 0:
+            self.n_kv_head = self.n_head
+        if self.n_head % self.n_kv_head:
+            raise ValueError("n_head must be a multiple of n_kv_head")
+
+    @property
+    def ffn_hidden(self) -> int:
+        """SwiGLU width: 2/3 of 4·d rounded up to 64 (``config.py:364-368``)."""
+        return (int(2 / 3 * 4 * self.d_model) + 63) // 64 * 64
+
+
+class RMSNorm(nn.Module):
+    """``nanolab/mixers.py:46-56``: weight only, eps 1e-6."""
+
+    def __init__(self, dim: int, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x):
+        return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
+
+
+def rope_tables(T: int, head_dim: int, base: float, device, dtype):
+    """cos / sin ``[T, head_dim]``, both halves the same angles (``mixers.py:59-65``)."""
+    half = torch.arange(0, head_dim, 2, device=device).float() / head_dim
+    ang = torch.outer(torch.arange(T, device=device).float(), base ** -half)
+    ang = torch.cat((ang, ang), dim=-1)
+    return ang.cos().to(dtype), ang.sin().to(dtype)
+
+
+def rotate(x, cos, sin):
+    """Rotary embedding on ``[B,T,H,D]``, half-split convention (``mixers.py:68-75``)."""
+    lo, hi = x.chunk(2, dim=-1)
+    return x * cos[None, :, None, :] + torch.cat((-hi, lo), dim=-1) * sin[None, :, None, :]
+
+
+class Attention(nn.Module):
+    """Projections, QK-norm, RoPE, value residual, attention core, gate, output projection."""
+
+    def __init__(self, s: ModelShape):
+        super().__init__()
+        self.H, self.Hkv, self.D = s.n_head, s.n_kv_head, s.head_dim
+        self.attn_scale = 1.0 / math.sqrt(s.head_dim)
+        self.q_proj = nn.Linear(s.d_model, self.H * self.D, bias=False)
+        self.k_proj = nn.Linear(s.d_model, self.Hkv * self.D, bias=False)
+        self.v_proj = nn.Linear(s.d_model, self.Hkv * self.D, bias=False)
+        self.o_proj = nn.Linear(self.H * self.D, s.d_model, bias=False)
+        if s.qk_norm:
+            self.q_norm, self.k_norm = RMSNorm(self.D), RMSNorm(self.D)
+        else:
+            self.q_norm = self.k_norm = None
+        self.gate = nn.Linear(s.d_model, self.H, bias=True) if s.gated_attention else None
+        self.vr_lambda = nn.Parameter(torch.zeros(1)) if s.value_residual else None
+        # what mixer_glue.decline_reason reads off a mixer
+        self.flash_cuda = bool(s.flash_cuda)
+        self.causal = True
+        self.block_attn = 0
+        self.swa_window, self.swa_sinks = int(s.swa_window), int(s.swa_sinks)
+        self._flash_declined = False
+
+    def _sdpa(self, q, k, v):
+        q, k, v = (t.transpose(1, 2) for t in (q, k, v))
+        if self.Hkv != self.H:
+            k = k.repeat_interleave(self.H // self.Hkv, dim=1)
+            v = v.repeat_interleave(self.H // self.Hkv, dim=1)
+        if self.swa_window:
+            T = q.shape[2]
+            i = torch.arange(T, device=q.device)
+            span = self.swa_window - self.swa_sinks
+            keep = (i[None, :] <= i[:, None]) & ((i[None, :] > i[:, None] - span) | (i[None, :] < self.swa_sinks))
+            y = F.scaled_dot_product_attention(q, k, v, attn_mask=keep, scale=self.attn_scale)
+        else:
+            y = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=self.attn_scale)
+        return y.transpose(1, 2).contiguous()
+
+    def forward(self, x, cos, sin, v0):
+        B, T, _ = x.shape
+        q = self.q_proj(x).view(B, T, self.H, self.D)
+        k = self.k_proj(x).view(B, T, self.Hkv, self.D)
+        v = raw_v = self.v_proj(x).view(B, T, self.Hkv, self.D)
+        if self.q_norm is not None:
+            q, k = self.q_norm(q), self.k_norm(k)
+        q, k = rotate(q, cos, sin), rotate(k, cos, sin)
+        if self.vr_lambda is not None and v0 is not None:
+            lam = torch.sigmoid(self.vr_lambda)
+            v = (1 - lam) * v + lam * v0
+        y = mixer_glue.attention_core(self, q, k, v, self.attn_scale)
+        if y is None:
+            y = self._sdpa(q, k, v)
+        if self.gate is not None:
+            y = y * torch.sigmoid(self.gate(x)).unsqueeze(-1)
+        return self.o_proj(y.reshape(B, T, self.H * self.D)), raw_v
+
+
+class SwiGLU(nn.Module):
+    """``down(silu(gate(x)) * up(x))`` (``nanolab/model.py:29-43``)."""
+
+    def __init__(self, s: ModelShape):
+        super().__init__()
+        self.gate = nn.Linear(s.d_model, s.ffn_hidden, bias=False)
+        self.up = nn.Linear(s.d_model, s.ffn_hidden, bias=False)
+        self.down = nn.Linear(s.ffn_hidden, s.d_model, bias=False)
+
+    def forward(self, x):
+        return self.down(F.silu(self.gate(x)) * self.up(x))
+
+
+class Block(nn.Module):
+    """Pre-norm residual block (``nanolab/model.py:178-193``)."""
+
+    def __init__(self, s: ModelShape):
+        super().__init__()
+        self.norm1, self.mixer = RMSNorm(s.d_model), Attention(s)
+        self.norm2, self.ffn = RMSNorm(s.d_model), SwiGLU(s)
+
+    def forward(self, x, cos, sin, v0):
+        mixed, raw_v = self.mixer(self.norm1(x), cos, sin, v0)
+        x = x + mixed
+        return x + self.ffn(self.norm2(x)), raw_v
+
+
+class GPT(nn.Module):
+    """Embedding, blocks, final norm, tied head, mean cross-entropy (``model.py:205-245``, ``:364-453``)."""
+
+    def __init__(self, s: ModelShape):
+        super().__init__()
+        self.shape = s
+        self.tok_emb = nn.Embedding(s.vocab_size, s.d_model)
+        self.blocks = nn.ModuleList(Block(s) for _ in range(s.n_layer))
+        self.norm_f = RMSNorm(s.d_model)
+        self.lm_head = nn.Linear(s.d_model, s.vocab_size, bias=False)
+        if s.tie_embeddings:
+            self.lm_head.weight = self.tok_emb.weight
+        for m in self.modules():           # weights N(0, 0.02), biases 0 (model.py:245-251)
+            if isinstance(m, (nn.Linear, nn.Embedding)):
+                nn.init.normal_(m.weight, mean=0.0, std=0.02)
+                if getattr(m, "bias", None) is not None:
+                    nn.init.zeros_(m.bias)
+        for b in self.blocks:
+            if b.mixer.gate is not None:   # gate starts at 0.5 (mixers.py:247-249)
+                nn.init.zeros_(b.mixer.gate.weight)
+            if s.zero_init_proj:           # blocks start as the identity (model.py:263-285)
+                nn.init.zeros_(b.mixer.o_proj.weight)
+                nn.init.zeros_(b.ffn.down.weight)
+        self._rope = {}
+
+    def n_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def flops_per_token(self) -> float:
+        """nanolab's estimate, 6·N + 12·L·H·D·T (``model.py:461-490``)."""
+        s = self.shape
+        span = min(s.swa_window, s.block_size) if s.swa_window else s.block_size
+        return 6.0 * self.n_params() + 12.0 * s.n_layer * s.n_head * s.head_dim * span
+
+    def forward(self, idx, targets=None):
+        s = self.shape
+        x = self.tok_emb(idx)
+        key = (idx.shape[1], x.device, x.dtype)
+        if key not in self._rope:
+            self._rope[key] = rope_tables(idx.shape[1], s.head_dim, s.rope_base, x.device, x.dtype)
+        cos, sin = self._rope[key]
+        v0 = None
+        for blk in self.blocks:
+            x, raw_v = blk(x, cos, sin, v0)
+            if v0 is None:
+                v0 = raw_v                 # layer 0's values anchor every later layer
+        x = self.norm_f(x)
+        if targets is None:
+            return self.lm_head(x[:, [-1], :]), None
+        logits = self.lm_head(x)
+        loss = F.cross_entropy(logits.view(-1, logits.size(-1)), targets.reshape(-1), ignore_index=-1)
+        return logits, loss
+
+
+class DataParallelStep:
+    """One optimiser step of the whole-model configuration on this rank's share of the batch.
+
+    ``step(idx, targets)``: autocast forward, backward, gradient average across
+    ranks, global-norm clip (nanolab's default 1.0, ``config.py:163``), fused AdamW.
+    Gradients are averaged in flat fp32 buckets of ``bucket_mb``: every parameter
+    that received a gradient is packed, one ``all_reduce`` runs per bucket, and
+    the result is unpacked -- layer 0's ``vr_lambda`` never gets a gradient (it has
+    no ``v0``), which is why this does not use a wrapper that expects every
+    parameter to take part.  With one rank no collective is issued.
+    """
+
+    def __init__(self, model: GPT, lr: float = 6e-4, weight_decay: float = 0.1, grad_clip: float = 1.0,
+                 dtype=torch.bfloat16, bucket_mb: int = 128, group=None):
+        self.model, self.grad_clip, self.dtype, self.group = model, grad_clip, dtype, group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.bucket_elems = bucket_mb * (1 << 20) // 4
+        params = list(model.parameters())
+        decay = [p for p in params if p.dim() >= 2]
+        rest = [p for p in params if p.dim() < 2]
+        on_gpu = params[0].is_cuda
+        self.opt = torch.optim.AdamW(
+            [dict(params=decay, weight_decay=weight_decay), dict(params=rest, weight_decay=0.0)],
+            lr=lr, betas=(0.9, 0.95), fused=on_gpu)
+        self._flat = None
+        self.collectives = 0
+
+    def average_gradients(self) -> None:
+        if self.world == 1:
+            return
+        grads = [p.grad for p in self.model.parameters() if p.grad is not None]
+        if self._flat is None:
+            n = min(self.bucket_elems, sum(g.numel() for g in grads))
+            self._flat = torch.empty(max(n, max(g.numel() for g in grads)), dtype=torch.float32,
+                                     device=grads[0].device)
+        i = 0
+        while i < len(grads):
+            j, used = i, 0
+            while j < len(grads) and (used == 0 or used + grads[j].numel() <= self._flat.numel()):
+                used += grads[j].numel()
+                j += 1
+            flat = self._flat[:used]
+            views = torch.split(flat, [g.numel() for g in grads[i:j]])
+            torch._foreach_copy_(list(views), [g.reshape(-1) for g in grads[i:j]])
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+            flat.mul_(1.0 / self.world)
+            torch._foreach_copy_([g.view(-1) for g in grads[i:j]], list(views))
+            self.collectives += 1
+            i = j
+
+    def step(self, idx, targets) -> torch.Tensor:
+        dev = idx.device.type
+        with torch.autocast(dev, dtype=self.dtype, enabled=self.dtype != torch.float32):
+            _, loss = self.model(idx, targets)
+        loss.backward()
+        self.average_gradients()
+        torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip)
+        self.opt.step()
+        self.opt.zero_grad(set_to_none=True)
+        return loss.detach()
+
+
+def synthetic_tokens(vocab_size: int, batch: int, block_size: int, seed: int = 0):
+    """Token ids uniform in ``[0, vocab)`` from a CPU generator, inputs = targets
+    (``nanolab/bench_gpu.py:35-38``)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randint(0, vocab_size, (batch, block_size), generator=g)
+    return x, x.clone()
