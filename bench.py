@@ -475,7 +475,7 @@ def run_whole_model_reference_arm(args, rank):
 
 def run_whole_model_arm(args, rank, world, local_rank):
     import torch.distributed as dist
-    from machinelearning_b200 import flash_cuda, sharding, whole_model as wm
+    from machinelearning_b200 import flash_cuda, qk_prologue, sharding, whole_model as wm
 
     if GLOBAL_BATCH % world:
         raise SystemExit(f"global batch {GLOBAL_BATCH} does not split over {world} ranks")
@@ -496,14 +496,20 @@ def run_whole_model_arm(args, rank, world, local_rank):
         model = wm.GPT(wm.ModelShape(flash_cuda=flag)).to(dev)
         return model, wm.DataParallelStep(model)
 
-    # counts the library's launches: 1 forward + 3 backward kernels per flash_attn call
-    calls = {"n": 0}
-    real_fwd = flash_cuda.fwd
+    # counts the library's launches: 1 forward + 3 backward kernels per flash_attn call, 1 forward +
+    # 2 backward kernels (gradient pass, weight-gradient reduction) per qk_prologue call
+    calls = {"n": 0, "prologue": 0}
+    real_fwd, real_prologue = flash_cuda.fwd, qk_prologue.qk_prologue
 
     def counted_fwd(*a, **k):
         calls["n"] += 1
         return real_fwd(*a, **k)
+
+    def counted_prologue(*a, **k):
+        calls["prologue"] += 1
+        return real_prologue(*a, **k)
     flash_cuda.fwd = counted_fwd
+    qk_prologue.qk_prologue = counted_prologue
 
     x_host, y_host = wm.synthetic_tokens(50304, GLOBAL_BATCH, 1024, seed=0)
     x_pin, y_pin = x_host[lo:lo + per_rank].pin_memory(), y_host[lo:lo + per_rank].pin_memory()
@@ -512,15 +518,16 @@ def run_whole_model_arm(args, rank, world, local_rank):
     def measure(flag, steps, warmup, sample_clocks):
         model, step = build(flag)
         x, y = x_pin.to(dev), y_pin.to(dev)
-        for _ in range(warmup):
+        first_loss = step.step(x, y).item()        # same weights and tokens in both arms: comparable
+        for _ in range(warmup - 1):
             step.step(x, y)
         barrier()
         sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
         if sampler:
             sampler.__enter__()
-        calls["n"] = 0
+        calls["n"] = calls["prologue"] = 0
         resident = time_region(lambda: step.step(x, y), steps)
-        n_calls = calls["n"]
+        n_calls = (calls["n"], calls["prologue"])
         if sampler:
             sampler.__exit__(None, None, None)
         barrier()
@@ -533,7 +540,7 @@ def run_whole_model_arm(args, rank, world, local_rank):
         barrier()
         e2e = time_region(host_step, max(3, min(steps, 10)))
         barrier()
-        loss = float(loss_host)
+        loss = first_loss
         flops_tok = model.flops_per_token()
         del model, step
         torch.cuda.empty_cache()
@@ -558,12 +565,14 @@ def run_whole_model_arm(args, rank, world, local_rank):
                    "params": 123699612, "flops_per_token": flops_tok},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 2 * x_pin.numel() * x_pin.element_size(), "d2h_bytes_per_step": 4},
-        "gpu_launches": 4 * n_calls,
-        "attention_calls_per_step": n_calls // steps,
+        "gpu_launches": 4 * n_calls[0] + 3 * n_calls[1],
+        "attention_calls_per_step": n_calls[0] // steps,
+        "prologue_calls_per_step": n_calls[1] // steps,
         "model_flops_utilisation": flops_tok * tok_s / world / 1e12 / peak,
         "peak_source": peak_src,
-        "loss": loss,
-        "flag_off_sdpa": {"tokens_per_s": tokens / (sdpa_ms * 1e-3), "ms_per_step": sdpa_ms, "loss": sdpa_loss},
+        "first_step_loss": loss,
+        "flag_off_sdpa": {"tokens_per_s": tokens / (sdpa_ms * 1e-3), "ms_per_step": sdpa_ms,
+                          "first_step_loss": sdpa_loss},
         "clocks": clocks,
     }
     if world == 1 and not args.no_cpu_baseline:

@@ -138,6 +138,36 @@ int nlfa_bwd_static_scratch(const void* dout, const void* q, const void* k, cons
                             int T, int H, int Hkv, int D, float scale, int window, int sinks,
                             int dtype, int path, void* stream);
 
+/* Load-side prologue of the attention core for q or k, in one pass over the tensor:
+ * per-head RMSNorm (weight [D], eps), rotary embedding (cos / sin tables [T, D]
+ * float32, half-split convention: out = y * cos + (-y_hi, y_lo) * sin) and the cast
+ * to the kernel dtype.  Replaces, in front of every attention call, the separate
+ * tensor passes of nanolab/mixers.py:287-292 (`q_norm` / `k_norm`, RMSNorm at
+ * :46-56, and `apply_rope`, :68-75) and the cast + contiguous of
+ * nanolab/flash_cuda.py:263-266.
+ *   x [B,T,H,D] of x_dtype -> y [B,T,H,D] of y_dtype; rstd [B*T*H] float32 receives
+ *   1/rms of every row (the backward's tape) when weight != NULL.
+ *   weight == NULL skips the norm; cos_table == sin_table == NULL skips the rotation.
+ * For 16-bit x the normalised, weighted row is rounded to x_dtype before the
+ * rotation, as torch's rms_norm does (it returns its input's type). */
+int nlfa_qk_prologue_fwd(const void* x, int x_dtype, const float* weight, const float* cos_table,
+                         const float* sin_table, void* y, int y_dtype, float* rstd, int B, int T,
+                         int H, int D, float eps, void* stream);
+
+/* Bytes of device scratch `nlfa_qk_prologue_bwd` needs for a head dim (per-CTA
+ * partial sums of the weight gradient; needed only when weight != NULL). */
+size_t nlfa_qk_prologue_scratch_bytes(int D);
+
+/* Backward of nlfa_qk_prologue_fwd: gy [B,T,H,D] of gy_dtype (the gradient of y,
+ * i.e. dq or dk of the attention backward) -> gx [B,T,H,D] of x_dtype and
+ * gweight [D] float32 (overwritten).  Stands where autograd's backward of the
+ * same nanolab lines stands.  The weight gradient is reduced in a fixed order
+ * (per-CTA partial sums in `scratch`, then one small kernel): bit-reproducible. */
+int nlfa_qk_prologue_bwd(const void* gy, int gy_dtype, const void* x, int x_dtype,
+                         const float* weight, const float* cos_table, const float* sin_table,
+                         const float* rstd, void* gx, float* gweight, void* scratch,
+                         size_t scratch_bytes, int B, int T, int H, int D, void* stream);
+
 /* Bytes of device workspace `nlfa_selftest` needs. */
 size_t nlfa_selftest_workspace_bytes(void);
 

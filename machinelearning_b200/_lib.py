@@ -36,6 +36,11 @@ SIGNATURES = {
     "nlfa_static_scratch_max_rows": (_c_size_t, []),
     "nlfa_bwd_static_scratch": (_c_int, [_c_void_p] * 9 + [_c_int] * 5 + [_c_float]
                                 + [_c_int] * 4 + [_c_void_p]),
+    "nlfa_qk_prologue_fwd": (_c_int, [_c_void_p, _c_int] + [_c_void_p] * 4 + [_c_int, _c_void_p]
+                             + [_c_int] * 4 + [_c_float, _c_void_p]),
+    "nlfa_qk_prologue_scratch_bytes": (_c_size_t, [_c_int]),
+    "nlfa_qk_prologue_bwd": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_int] + [_c_void_p] * 7 + [_c_size_t]
+                             + [_c_int] * 4 + [_c_void_p]),
     "nlfa_selftest_workspace_bytes": (_c_size_t, []),
     "nlfa_selftest": (_c_int, [_c_int, _c_int, _c_void_p, _c_size_t,
                                ctypes.POINTER(_c_float), _c_void_p]),

@@ -32,7 +32,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import mixer_glue
+from . import flash_cuda, mixer_glue, qk_prologue
 
 
 @dataclasses.dataclass
@@ -59,6 +59,7 @@ class ModelShape:
     flash_cuda: bool = False    # ``--flash_cuda true`` (config.py:233-239)
     swa_window: int = 0         # > 0: every layer is the SWA mixer (config.py:127-139)
     swa_sinks: int = 0
+    fused_prologue: bool = True  # with flash_cuda on: QK-norm + RoPE + cast in one kernel (qk_prologue)
 
     def __post_init__(self):
         if self.n_kv_head == 0:
@@ -121,6 +122,19 @@ class Attention(nn.Module):
         self.block_attn = 0
         self.swa_window, self.swa_sinks = int(s.swa_window), int(s.swa_sinks)
         self._flash_declined = False
+        self.fused_prologue = bool(s.fused_prologue)
+
+    def _prologue(self, q, k, cos, sin):
+        """QK-norm and RoPE (``mixers.py:287-292``): one fused kernel per tensor when this step goes
+        through the kernels anyway, the separate tensor passes otherwise."""
+        qw = None if self.q_norm is None else self.q_norm.weight
+        kw = None if self.k_norm is None else self.k_norm.weight
+        if (self.fused_prologue and self.flash_cuda and qk_prologue.supports(q, qw, cos, sin)
+                and qk_prologue.supports(k, kw, cos, sin) and flash_cuda.is_available()):
+            return qk_prologue.qk_prologue(q, qw, cos, sin), qk_prologue.qk_prologue(k, kw, cos, sin)
+        if self.q_norm is not None:
+            q, k = self.q_norm(q), self.k_norm(k)
+        return rotate(q, cos, sin), rotate(k, cos, sin)
 
     def _sdpa(self, q, k, v):
         q, k, v = (t.transpose(1, 2) for t in (q, k, v))
@@ -142,9 +156,7 @@ class Attention(nn.Module):
         q = self.q_proj(x).view(B, T, self.H, self.D)
         k = self.k_proj(x).view(B, T, self.Hkv, self.D)
         v = raw_v = self.v_proj(x).view(B, T, self.Hkv, self.D)
-        if self.q_norm is not None:
-            q, k = self.q_norm(q), self.k_norm(k)
-        q, k = rotate(q, cos, sin), rotate(k, cos, sin)
+        q, k = self._prologue(q, k, cos, sin)
         if self.vr_lambda is not None and v0 is not None:
             lam = torch.sigmoid(self.vr_lambda)
             v = (1 - lam) * v + lam * v0
