@@ -26,12 +26,20 @@ constexpr int kVec = 8;
 constexpr int kThreads = 256;
 constexpr int kMaxPartials = 148 * 8;   // CTAs of the backward; rows of the weight-gradient scratch
 
+// Raw: the 8 elements as loaded (kept packed so that several rows can be in flight in few registers).
+struct Raw32 { float4 a, b; };
 template <typename T> struct Elem;
 template <> struct Elem<float> {
-  __device__ static void load(const float* p, float (&v)[kVec]) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  using Raw = Raw32;
+  static constexpr int kInFlight = 2;
+  __device__ static Raw zero() { return Raw{make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)}; }
+  __device__ static Raw load_raw(const float* p) {
+    return Raw{*reinterpret_cast<const float4*>(p), *reinterpret_cast<const float4*>(p + 4)};
   }
+  __device__ static void unpack(const Raw& r, float (&v)[kVec]) {
+    v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+  }
+  __device__ static void load(const float* p, float (&v)[kVec]) { unpack(load_raw(p), v); }
   __device__ static void store(float* p, const float (&v)[kVec]) {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -39,8 +47,12 @@ template <> struct Elem<float> {
   __device__ static float round(float x) { return x; }
 };
 template <> struct Elem<__nv_bfloat16> {
-  __device__ static void load(const __nv_bfloat16* p, float (&v)[kVec]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  using Raw = uint4;
+  static constexpr int kInFlight = 4;
+  __device__ static Raw zero() { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ static Raw load_raw(const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[kVec]) { unpack(load_raw(p), v); }
+  __device__ static void unpack(const Raw& raw, float (&v)[kVec]) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
@@ -55,8 +67,12 @@ template <> struct Elem<__nv_bfloat16> {
   __device__ static float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 };
 template <> struct Elem<__half> {
-  __device__ static void load(const __half* p, float (&v)[kVec]) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  using Raw = uint4;
+  static constexpr int kInFlight = 4;
+  __device__ static Raw zero() { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ static Raw load_raw(const __half* p) { return *reinterpret_cast<const uint4*>(p); }
+  __device__ static void load(const __half* p, float (&v)[kVec]) { unpack(load_raw(p), v); }
+  __device__ static void unpack(const Raw& raw, float (&v)[kVec]) {
     const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
@@ -78,61 +94,63 @@ template <int LPR> __device__ inline float row_sum(float v) {
   return v;
 }
 
-constexpr int kUnroll = 2;                 // row groups a warp has in flight per loop iteration
+// Rows are indexed with 32 bits (the host refuses B*T*H >= 2^31): the position of a row, (row / H) % T,
+// would otherwise cost two 64-bit divisions per row group.
 
 // x [rows, D] (rows = B*T*H, position t = (row / H) % T) -> y [rows, D]; rstd [rows] when weight != nullptr.
 template <typename TIn, typename TOut, int D>
 __global__ void __launch_bounds__(kThreads)
 qk_prologue_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ cosT,
                        const float* __restrict__ sinT, TOut* __restrict__ y, float* __restrict__ rstd,
-                       long long rows, int T, int H, float eps) {
+                       unsigned rows, unsigned T, unsigned H, float eps) {
   constexpr int LPR = D / kVec;              // lanes per row
   constexpr int RPW = 32 / LPR;              // rows per warp and group
-  const int lane = threadIdx.x & 31;
-  const int sub = lane % LPR;                // which 8-element slot of the row
-  const long long warp = (long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * (kThreads / 32);
+  constexpr int U = Elem<TIn>::kInFlight;    // row groups a warp has in flight per loop iteration
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned sub = lane % LPR;           // which 8-element slot of the row
+  const unsigned warp = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const unsigned stride = gridDim.x * (kThreads / 32) * (RPW * U);
   const float sign = sub < LPR / 2 ? -1.f : 1.f;       // rot = (-hi, lo)
   float w[kVec];
 #pragma unroll
   for (int i = 0; i < kVec; ++i) w[i] = weight ? weight[sub * kVec + i] : 1.f;
 
-  for (long long r0 = warp * (RPW * kUnroll); r0 < rows; r0 += nwarps * (RPW * kUnroll)) {
-    long long row[kUnroll];
-    float v[kUnroll][kVec];
+  for (unsigned r0 = warp * (RPW * U); r0 < rows; r0 += stride) {
+    typename Elem<TIn>::Raw raw[U];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {      // every load first; the whole warp stays for the shuffles
-      row[u] = r0 + u * RPW + lane / LPR;
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) v[u][i] = 0.f;
-      if (row[u] < rows) Elem<TIn>::load(x + row[u] * D + sub * kVec, v[u]);
+    for (int u = 0; u < U; ++u) {            // every load first; the whole warp stays for the shuffles
+      const unsigned row = r0 + u * RPW + lane / LPR;
+      raw[u] = row < rows ? Elem<TIn>::load_raw(x + (size_t)row * D + sub * kVec) : Elem<TIn>::zero();
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const bool live = row[u] < rows;
+    for (int u = 0; u < U; ++u) {
+      const unsigned row = r0 + u * RPW + lane / LPR;
+      const bool live = row < rows;
+      float v[kVec];
+      Elem<TIn>::unpack(raw[u], v);
       if (weight) {
         float ss = 0.f;
 #pragma unroll
-        for (int i = 0; i < kVec; ++i) ss = fmaf(v[u][i], v[u][i], ss);
+        for (int i = 0; i < kVec; ++i) ss = fmaf(v[i], v[i], ss);
         const float r = rsqrtf(row_sum<LPR>(ss) * (1.f / D) + eps);
-        if (live && sub == 0) rstd[row[u]] = r;
+        if (live && sub == 0) rstd[row] = r;
 #pragma unroll
-        for (int i = 0; i < kVec; ++i) v[u][i] = Elem<TIn>::round(v[u][i] * r * w[i]);
+        for (int i = 0; i < kVec; ++i) v[i] = Elem<TIn>::round(v[i] * r * w[i]);
       }
       if (cosT) {
-        const int t = live ? (int)((row[u] / H) % T) : 0;
+        const unsigned t = live ? (row / H) % T : 0u;
         float c[kVec], s[kVec];
-        Elem<float>::load(cosT + (long long)t * D + sub * kVec, c);
-        Elem<float>::load(sinT + (long long)t * D + sub * kVec, s);
+        Elem<float>::load(cosT + (size_t)t * D + sub * kVec, c);
+        Elem<float>::load(sinT + (size_t)t * D + sub * kVec, s);
 #pragma unroll
         for (int i = 0; i < kVec; ++i) {
-          const float partner = __shfl_xor_sync(0xffffffffu, v[u][i], LPR / 2);
-          c[i] = v[u][i] * c[i] + sign * partner * s[i];
+          const float partner = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
+          c[i] = v[i] * c[i] + sign * partner * s[i];
         }
 #pragma unroll
-        for (int i = 0; i < kVec; ++i) v[u][i] = c[i];
+        for (int i = 0; i < kVec; ++i) v[i] = c[i];
       }
-      if (live) Elem<TOut>::store(y + row[u] * D + sub * kVec, v[u]);
+      if (live) Elem<TOut>::store(y + (size_t)row * D + sub * kVec, v);
     }
   }
 }
@@ -144,62 +162,68 @@ __global__ void __launch_bounds__(kThreads, 3)
 qk_prologue_bwd_kernel(const TG* __restrict__ gy, const TIn* __restrict__ x, const float* __restrict__ weight,
                        const float* __restrict__ cosT, const float* __restrict__ sinT,
                        const float* __restrict__ rstd, TIn* __restrict__ gx, float* __restrict__ partial,
-                       long long rows, int T, int H) {
+                       unsigned rows, unsigned T, unsigned H) {
   constexpr int LPR = D / kVec;
   constexpr int RPW = 32 / LPR;
+  constexpr int U = 2;
   __shared__ float red[kThreads / 32][D];
-  const int lane = threadIdx.x & 31;
-  const int sub = lane % LPR;
-  const long long warp = (long long)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * (kThreads / 32);
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned sub = lane % LPR;
+  const unsigned warp = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const unsigned stride = gridDim.x * (kThreads / 32) * (RPW * U);
   const float sign = sub < LPR / 2 ? 1.f : -1.f;       // transpose of the rotation
   float w[kVec], dw[kVec];
 #pragma unroll
   for (int i = 0; i < kVec; ++i) { w[i] = weight ? weight[sub * kVec + i] : 1.f; dw[i] = 0.f; }
 
-  for (long long r0 = warp * (RPW * kUnroll); r0 < rows; r0 += nwarps * (RPW * kUnroll)) {
-    long long row[kUnroll];
-    float g[kUnroll][kVec], v[kUnroll][kVec], r[kUnroll];
+  for (unsigned r0 = warp * (RPW * U); r0 < rows; r0 += stride) {
+    typename Elem<TG>::Raw graw[U];
+    typename Elem<TIn>::Raw xraw[U];
+    float r[U];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      row[u] = r0 + u * RPW + lane / LPR;
+    for (int u = 0; u < U; ++u) {
+      const unsigned row = r0 + u * RPW + lane / LPR;
+      graw[u] = Elem<TG>::zero();
+      xraw[u] = Elem<TIn>::zero();
       r[u] = 0.f;
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) { g[u][i] = 0.f; v[u][i] = 0.f; }
-      if (row[u] < rows) {
-        Elem<TG>::load(gy + row[u] * D + sub * kVec, g[u]);
-        if (weight) { Elem<TIn>::load(x + row[u] * D + sub * kVec, v[u]); r[u] = rstd[row[u]]; }
+      if (row < rows) {
+        graw[u] = Elem<TG>::load_raw(gy + (size_t)row * D + sub * kVec);
+        if (weight) { xraw[u] = Elem<TIn>::load_raw(x + (size_t)row * D + sub * kVec); r[u] = rstd[row]; }
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const bool live = row[u] < rows;
+    for (int u = 0; u < U; ++u) {
+      const unsigned row = r0 + u * RPW + lane / LPR;
+      const bool live = row < rows;
+      float g[kVec], v[kVec];
+      Elem<TG>::unpack(graw[u], g);
+      Elem<TIn>::unpack(xraw[u], v);
       if (cosT) {
-        const int t = live ? (int)((row[u] / H) % T) : 0;
+        const unsigned t = live ? (row / H) % T : 0u;
         float c[kVec], s[kVec];
-        Elem<float>::load(cosT + (long long)t * D + sub * kVec, c);
-        Elem<float>::load(sinT + (long long)t * D + sub * kVec, s);
+        Elem<float>::load(cosT + (size_t)t * D + sub * kVec, c);
+        Elem<float>::load(sinT + (size_t)t * D + sub * kVec, s);
 #pragma unroll
         for (int i = 0; i < kVec; ++i) {
-          const float partner = __shfl_xor_sync(0xffffffffu, g[u][i] * s[i], LPR / 2);
-          g[u][i] = g[u][i] * c[i] + sign * partner;
+          const float partner = __shfl_xor_sync(0xffffffffu, g[i] * s[i], LPR / 2);
+          g[i] = g[i] * c[i] + sign * partner;
         }
       }
       if (weight) {
         float dot = 0.f;
 #pragma unroll
         for (int i = 0; i < kVec; ++i) {
-          g[u][i] = Elem<TIn>::round(g[u][i]);   // the gradient passes back through rms_norm's output cast
-          v[u][i] *= r[u];                       // normalised row
-          dw[i] = fmaf(g[u][i], v[u][i], dw[i]);
-          g[u][i] *= w[i];
-          dot = fmaf(g[u][i], v[u][i], dot);
+          g[i] = Elem<TIn>::round(g[i]);     // the gradient passes back through rms_norm's output cast
+          v[i] *= r[u];                      // normalised row
+          dw[i] = fmaf(g[i], v[i], dw[i]);
+          g[i] *= w[i];
+          dot = fmaf(g[i], v[i], dot);
         }
         const float c = row_sum<LPR>(dot) * (1.f / D);
 #pragma unroll
-        for (int i = 0; i < kVec; ++i) g[u][i] = r[u] * (g[u][i] - v[u][i] * c);
+        for (int i = 0; i < kVec; ++i) g[i] = r[u] * (g[i] - v[i] * c);
       }
-      if (live) Elem<TIn>::store(gx + row[u] * D + sub * kVec, g[u]);
+      if (live) Elem<TIn>::store(gx + (size_t)row * D + sub * kVec, g);
     }
   }
 
@@ -218,7 +242,7 @@ qk_prologue_bwd_kernel(const TG* __restrict__ gy, const TIn* __restrict__ x, con
       float s = 0.f;
 #pragma unroll
       for (int wi = 0; wi < kThreads / 32; ++wi) s += red[wi][threadIdx.x];
-      partial[(long long)blockIdx.x * D + threadIdx.x] = s;
+      partial[(size_t)blockIdx.x * D + threadIdx.x] = s;
     }
   }
 }
@@ -243,8 +267,8 @@ weight_grad_reduce_kernel(const float* __restrict__ partial, int n, float* __res
   }
 }
 
-int grid_for(long long rows, int D, int cap) {
-  const long long rows_per_cta = (long long)(kThreads / 32) * (32 / (D / kVec)) * kUnroll;
+int grid_for(long long rows, int D, int cap, int in_flight) {
+  const long long rows_per_cta = (long long)(kThreads / 32) * (32 / (D / kVec)) * in_flight;
   long long need = (rows + rows_per_cta - 1) / rows_per_cta;
   if (need < 1) need = 1;
   return (int)(need < cap ? need : cap);
@@ -253,10 +277,10 @@ int grid_for(long long rows, int D, int cap) {
 template <typename TIn, typename TOut>
 int fwd_for_dim(int D, const void* x, const float* w, const float* c, const float* s, void* y, float* rstd,
                 long long rows, int T, int H, float eps, cudaStream_t st) {
-  const int grid = grid_for(rows, D, 148 * 8);
+  const int grid = grid_for(rows, D, 148 * 8, Elem<TIn>::kInFlight);
 #define NLFA_GO(DD)                                                                               \
-  qk_prologue_fwd_kernel<TIn, TOut, DD><<<grid, kThreads, 0, st>>>((const TIn*)x, w, c, s, (TOut*)y, rstd, rows, \
-                                                                   T, H, eps)
+  qk_prologue_fwd_kernel<TIn, TOut, DD><<<grid, kThreads, 0, st>>>((const TIn*)x, w, c, s, (TOut*)y, rstd,       \
+                                                                   (unsigned)rows, (unsigned)T, (unsigned)H, eps)
   if (D == 32) NLFA_GO(32); else if (D == 64) NLFA_GO(64); else NLFA_GO(128);
 #undef NLFA_GO
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
@@ -266,11 +290,12 @@ template <typename TIn, typename TG>
 int bwd_for_dim(int D, const void* gy, const void* x, const float* w, const float* c, const float* s,
                 const float* rstd, void* gx, float* partial, float* gweight, long long rows, int T, int H,
                 cudaStream_t st) {
-  const int grid = grid_for(rows, D, kMaxPartials);
+  const int grid = grid_for(rows, D, kMaxPartials, 2);
 #define NLFA_GO(DD)                                                                                      \
   do {                                                                                                   \
     qk_prologue_bwd_kernel<TIn, TG, DD><<<grid, kThreads, 0, st>>>((const TG*)gy, (const TIn*)x, w, c, s, rstd, \
-                                                                   (TIn*)gx, partial, rows, T, H);       \
+                                                                   (TIn*)gx, partial, (unsigned)rows,    \
+                                                                   (unsigned)T, (unsigned)H);            \
     if (w) weight_grad_reduce_kernel<DD><<<1, 1024, 0, st>>>(partial, grid, gweight);                     \
   } while (0)
   if (D == 32) NLFA_GO(32); else if (D == 64) NLFA_GO(64); else NLFA_GO(128);
@@ -298,6 +323,7 @@ int nlfa_qk_prologue_fwd(const void* x, int x_dtype, const float* weight, const 
   if (D != 32 && D != 64 && D != 128) return NLFA_ERR_BAD_HEAD_DIM;
   if (!dtype_ok(x_dtype) || !dtype_ok(y_dtype)) return NLFA_ERR_BAD_DTYPE;
   const long long rows = (long long)B * T * H;
+  if (rows >= (1ll << 31)) return NLFA_ERR_BAD_SHAPE;
   if (rows == 0) return NLFA_OK;
   if (!x || !y || (weight && !rstd) || ((cos_table == nullptr) != (sin_table == nullptr))) return NLFA_ERR_NULL_POINTER;
   if (!aligned16(x) || !aligned16(y) || !aligned16(cos_table) || !aligned16(sin_table)) return NLFA_ERR_MISALIGNED;
@@ -321,6 +347,7 @@ int nlfa_qk_prologue_bwd(const void* gy, int gy_dtype, const void* x, int x_dtyp
   if (D != 32 && D != 64 && D != 128) return NLFA_ERR_BAD_HEAD_DIM;
   if (!dtype_ok(x_dtype) || !dtype_ok(gy_dtype)) return NLFA_ERR_BAD_DTYPE;
   const long long rows = (long long)B * T * H;
+  if (rows >= (1ll << 31)) return NLFA_ERR_BAD_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   if (rows == 0) {
     if (weight && gweight && cudaMemsetAsync(gweight, 0, D * sizeof(float), st) != cudaSuccess) return NLFA_ERR_CUDA;

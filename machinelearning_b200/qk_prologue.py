@@ -108,3 +108,92 @@ def qk_prologue(x: torch.Tensor, weight=None, cos=None, sin=None, eps: float = E
     if out_dtype not in _DTYPE_CODE:
         raise ValueError(f"qk_prologue: unsupported output dtype {out_dtype}")
     return _QkPrologueFn.apply(x, weight, cos, sin, eps, out_dtype)
+
+
+def _time_ms(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def main() -> int:
+    """Self-check against the torch passes this replaces, then timings of the two kernels.
+
+        python -m machinelearning_b200.qk_prologue [--batch 64 --seq 1024 --heads 12 --head_dim 64 --iters 20]
+
+    Timings call the C entry points on preallocated buffers (CUDA events, no autograd), so
+    they are kernel times; GB/s counts one read of x (and gy), one write of y (or gx) and
+    the float32 rstd tape.
+    """
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--head_dim", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--in_dtype", default="bf16", choices=("bf16", "fp32"))
+    a = ap.parse_args()
+    if not flash_cuda.is_available():
+        print("unavailable:", flash_cuda.unavailable_reason())
+        return 1
+    lib = flash_cuda._load()
+    B, T, H, D = a.batch, a.seq, a.heads, a.head_dim
+    din = torch.bfloat16 if a.in_dtype == "bf16" else torch.float32
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(B, T, H, D, device="cuda", generator=g).to(din)
+    gy = torch.randn(B, T, H, D, device="cuda", generator=g).bfloat16()
+    w = 1 + 0.1 * torch.randn(D, device="cuda", generator=g)
+    half = torch.arange(0, D, 2, device="cuda").float() / D
+    ang = torch.outer(torch.arange(T, device="cuda").float(), 10000.0 ** -half)
+    ang = torch.cat((ang, ang), dim=-1)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+
+    # correctness: the separate torch passes on a slice
+    xs = x[:2].clone().requires_grad_()
+    ws = w.clone().requires_grad_()
+    y = qk_prologue(xs, ws, cos, sin, out_dtype=torch.bfloat16)
+    y.backward(gy[:2])
+    xr = x[:2].clone().requires_grad_()
+    wr = w.clone().requires_grad_()
+    n = torch.nn.functional.rms_norm(xr, (D,), wr, EPS)
+    lo, hi = n.chunk(2, dim=-1)
+    yr = (n * cos[None, :, None, :] + torch.cat((-hi, lo), dim=-1) * sin[None, :, None, :]).to(torch.bfloat16)
+    yr.backward(gy[:2])
+    rel = lambda p, q: ((p.float() - q.float()).abs().max() / q.float().abs().max()).item()
+    print(f"vs torch passes (relative to the largest magnitude): y {rel(y, yr):.2e}  dx {rel(xs.grad, xr.grad):.2e}  "
+          f"dweight {rel(ws.grad, wr.grad):.2e}")
+
+    out = torch.empty(B, T, H, D, device="cuda", dtype=torch.bfloat16)
+    gx = torch.empty_like(x)
+    rstd = torch.empty(B * T * H, device="cuda", dtype=torch.float32)
+    gw = torch.empty(D, device="cuda", dtype=torch.float32)
+    scratch = torch.empty(lib.nlfa_qk_prologue_scratch_bytes(D), device="cuda", dtype=torch.uint8)
+    st = torch.cuda.current_stream().cuda_stream
+    cx, cg = _DTYPE_CODE[din], _lib.DTYPE_BF16
+
+    def fwd():
+        _lib.check("fwd", lib.nlfa_qk_prologue_fwd(x.data_ptr(), cx, w.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                                  out.data_ptr(), cg, rstd.data_ptr(), B, T, H, D, EPS, st))
+
+    def bwd():
+        _lib.check("bwd", lib.nlfa_qk_prologue_bwd(gy.data_ptr(), cg, x.data_ptr(), cx, w.data_ptr(), cos.data_ptr(),
+                                                  sin.data_ptr(), rstd.data_ptr(), gx.data_ptr(), gw.data_ptr(),
+                                                  scratch.data_ptr(), scratch.numel(), B, T, H, D, st))
+    n_el, es = B * T * H * D, x.element_size()
+    tf, tb = _time_ms(fwd, a.iters), _time_ms(bwd, a.iters)
+    fb, bb = n_el * (es + 2) + 4 * B * T * H, n_el * (2 + 2 * es) + 4 * B * T * H
+    print(f"[{B},{T},{H},{D}] {a.in_dtype} -> bf16: forward {tf * 1e3:.1f} us = {fb / tf / 1e6:.0f} GB/s ({fb / 1e6:.1f} MB); "
+          f"backward {tb * 1e3:.1f} us = {bb / tb / 1e6:.0f} GB/s ({bb / 1e6:.1f} MB)")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
