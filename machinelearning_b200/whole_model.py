@@ -317,3 +317,60 @@ def synthetic_tokens(vocab_size: int, batch: int, block_size: int, seed: int = 0
     g = torch.Generator(device="cpu").manual_seed(seed)
     x = torch.randint(0, vocab_size, (batch, block_size), generator=g)
     return x, x.clone()
+
+
+def _flag(text: str) -> bool:
+    """nanolab's CLI spells booleans ``true`` / ``false`` (``nanolab/config.py:487-505``)."""
+    if text.lower() in ("true", "1", "yes"):
+        return True
+    if text.lower() in ("false", "0", "no"):
+        return False
+    raise ValueError(f"expected true or false, got {text!r}")
+
+
+def main(argv=None) -> int:
+    """Synthetic-token micro-benchmark of the training step, after ``nanolab/bench_gpu.py:41-110``.
+
+        python -m machinelearning_b200.whole_model --flash_cuda true [--batch_size 16 --iters 10 --swa_window 0]
+
+    Prints tokens/s, ms per step, the model-FLOPs estimate nanolab uses and the loss, for one GPU.
+    """
+    import argparse
+    import json
+    import time
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--flash_cuda", type=_flag, default=False)
+    ap.add_argument("--fused_prologue", type=_flag, default=True)
+    ap.add_argument("--batch_size", type=int, default=16)
+    ap.add_argument("--swa_window", type=int, default=0)
+    ap.add_argument("--swa_sinks", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("no CUDA device")
+    torch.manual_seed(0)
+    shape = ModelShape(flash_cuda=a.flash_cuda, fused_prologue=a.fused_prologue, swa_window=a.swa_window,
+                       swa_sinks=a.swa_sinks)
+    model = GPT(shape).cuda()
+    step = DataParallelStep(model)
+    x, y = (t.cuda() for t in synthetic_tokens(shape.vocab_size, a.batch_size, shape.block_size))
+    for _ in range(a.warmup):
+        loss = step.step(x, y)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    for _ in range(a.iters):
+        loss = step.step(x, y)
+    torch.cuda.synchronize()
+    sec = (time.time() - t0) / a.iters
+    tokens = a.batch_size * shape.block_size
+    print(json.dumps({"flash_cuda": a.flash_cuda, "fused_prologue": a.fused_prologue and a.flash_cuda,
+                      "tok_s": tokens / sec, "ms_per_step": sec * 1e3, "loss": loss.item(),
+                      "params_m": model.n_params() / 1e6, "flops_per_tok": model.flops_per_token(),
+                      "model_tflops": model.flops_per_token() * tokens / sec / 1e12,
+                      "kernel_declined": any(b.mixer._flash_declined for b in model.blocks)}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
