@@ -475,7 +475,7 @@ def run_whole_model_reference_arm(args, rank):
 
 def run_whole_model_arm(args, rank, world, local_rank):
     import torch.distributed as dist
-    from machinelearning_b200 import flash_cuda, qk_prologue, sharding, whole_model as wm
+    from machinelearning_b200 import flash_cuda, qk_prologue, sharding, value_gate, whole_model as wm
 
     if GLOBAL_BATCH % world:
         raise SystemExit(f"global batch {GLOBAL_BATCH} does not split over {world} ranks")
@@ -497,9 +497,20 @@ def run_whole_model_arm(args, rank, world, local_rank):
         return model, wm.DataParallelStep(model)
 
     # counts the library's launches: 1 forward + 3 backward kernels per flash_attn call, 1 forward +
-    # 2 backward kernels (gradient pass, weight-gradient reduction) per qk_prologue call
-    calls = {"n": 0, "prologue": 0}
+    # 2 backward kernels (gradient pass, fixed-order reduction) per qk_prologue and per value_blend
+    # call, 1 + 1 per head_gate call
+    calls = {"n": 0, "prologue": 0, "blend": 0, "gate": 0}
     real_fwd, real_prologue = flash_cuda.fwd, qk_prologue.qk_prologue
+    real_blend, real_gate = value_gate.value_blend, value_gate.head_gate
+
+    def counted_blend(*a, **k):
+        calls["blend"] += 1
+        return real_blend(*a, **k)
+
+    def counted_gate(*a, **k):
+        calls["gate"] += 1
+        return real_gate(*a, **k)
+    value_gate.value_blend, value_gate.head_gate = counted_blend, counted_gate
 
     def counted_fwd(*a, **k):
         calls["n"] += 1
@@ -525,9 +536,10 @@ def run_whole_model_arm(args, rank, world, local_rank):
         sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
         if sampler:
             sampler.__enter__()
-        calls["n"] = calls["prologue"] = 0
+        for key in calls:
+            calls[key] = 0
         resident = time_region(lambda: step.step(x, y), steps)
-        n_calls = (calls["n"], calls["prologue"])
+        n_calls = dict(calls)
         if sampler:
             sampler.__exit__(None, None, None)
         barrier()
@@ -565,9 +577,9 @@ def run_whole_model_arm(args, rank, world, local_rank):
                    "params": 123699612, "flops_per_token": flops_tok},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 2 * x_pin.numel() * x_pin.element_size(), "d2h_bytes_per_step": 4},
-        "gpu_launches": 4 * n_calls[0] + 3 * n_calls[1],
-        "attention_calls_per_step": n_calls[0] // steps,
-        "prologue_calls_per_step": n_calls[1] // steps,
+        "gpu_launches": 4 * n_calls["n"] + 3 * n_calls["prologue"] + 3 * n_calls["blend"] + 2 * n_calls["gate"],
+        "library_calls_per_step": {"flash_attn": n_calls["n"] // steps, "qk_prologue": n_calls["prologue"] // steps,
+                                   "value_blend": n_calls["blend"] // steps, "head_gate": n_calls["gate"] // steps},
         "model_flops_utilisation": flops_tok * tok_s / world / 1e12 / peak,
         "peak_source": peak_src,
         "first_step_loss": loss,

@@ -168,6 +168,36 @@ int nlfa_qk_prologue_bwd(const void* gy, int gy_dtype, const void* x, int x_dtyp
                          const float* rstd, void* gx, float* gweight, void* scratch,
                          size_t scratch_bytes, int B, int T, int H, int D, void* stream);
 
+/* Value-residual blend in front of the attention core, with the cast to the kernel
+ * dtype: out = (1 - s) * v + s * v0, s = sigmoid(*lambda) (lambda: one float32 on the
+ * device).  Replaces the tensor passes of nanolab/mixers.py:294-297 and the cast of
+ * v in nanolab/flash_cuda.py:263-266.  v, v0 share v_dtype; n = element count, a
+ * multiple of 8 (head dims are). */
+int nlfa_value_blend_fwd(const void* v, const void* v0, int v_dtype, const float* lambda, void* out,
+                         int out_dtype, long long n, void* stream);
+
+/* Bytes of device scratch `nlfa_value_blend_bwd` needs (per-CTA partial sums). */
+size_t nlfa_value_blend_scratch_bytes(void);
+
+/* Backward of nlfa_value_blend_fwd: g (gradient of out, g_dtype) -> dv = (1 - s) g and
+ * dv0 = s g in v_dtype, *dlambda = s (1 - s) sum(g * (v0 - v)) (float32, overwritten;
+ * summed in a fixed order).  Stands where autograd's backward of mixers.py:294-297 stands. */
+int nlfa_value_blend_bwd(const void* g, int g_dtype, const void* v, const void* v0, int v_dtype,
+                         const float* lambda, void* dv, void* dv0, float* dlambda, void* scratch,
+                         size_t scratch_bytes, long long n, void* stream);
+
+/* Per-head sigmoid gate behind the attention core: out = y * sigmoid(gate)[..., None],
+ * y and out [rows, D] of y_dtype, gate [rows] of gate_dtype (rows = B*T*H).  The sigmoid
+ * is rounded to gate_dtype before the multiply, as torch does.  Replaces
+ * nanolab/mixers.py:340-342. */
+int nlfa_head_gate_fwd(const void* y, int y_dtype, const void* gate, int gate_dtype, void* out,
+                       long long rows, int D, void* stream);
+
+/* Backward of nlfa_head_gate_fwd: g (gradient of out) and the forward's y, gate ->
+ * dy = g * sigmoid(gate) [rows, D] and dgate = rowsum(g * y) * s * (1 - s) [rows]. */
+int nlfa_head_gate_bwd(const void* g, const void* y, int y_dtype, const void* gate, int gate_dtype,
+                       void* dy, void* dgate, long long rows, int D, void* stream);
+
 /* Bytes of device workspace `nlfa_selftest` needs. */
 size_t nlfa_selftest_workspace_bytes(void);
 

@@ -41,6 +41,15 @@ SIGNATURES = {
     "nlfa_qk_prologue_scratch_bytes": (_c_size_t, [_c_int]),
     "nlfa_qk_prologue_bwd": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_int] + [_c_void_p] * 7 + [_c_size_t]
                              + [_c_int] * 4 + [_c_void_p]),
+    "nlfa_value_blend_fwd": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int,
+                                      ctypes.c_longlong, _c_void_p]),
+    "nlfa_value_blend_scratch_bytes": (_c_size_t, []),
+    "nlfa_value_blend_bwd": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int] + [_c_void_p] * 5
+                             + [_c_size_t, ctypes.c_longlong, _c_void_p]),
+    "nlfa_head_gate_fwd": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, ctypes.c_longlong, _c_int,
+                                    _c_void_p]),
+    "nlfa_head_gate_bwd": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                    ctypes.c_longlong, _c_int, _c_void_p]),
     "nlfa_selftest_workspace_bytes": (_c_size_t, []),
     "nlfa_selftest": (_c_int, [_c_int, _c_int, _c_void_p, _c_size_t,
                                ctypes.POINTER(_c_float), _c_void_p]),

@@ -1,0 +1,122 @@
+"""The two elementwise steps around the attention core, one kernel each way.
+
+``value_blend(v, v0, vr_lambda)``
+    nanolab's value residual, ``(1 - sigmoid(lambda)) * v + sigmoid(lambda) * v0``
+    (``nanolab/mixers.py:294-297``), written directly in the kernel dtype -- in torch
+    that is two multiplies and an add in float32 plus ``flash_attn``'s cast.
+``head_gate(y, gate_logits)``
+    the per-head sigmoid gate on the attention output, ``y * sigmoid(gate)[..., None]``
+    (``nanolab/mixers.py:340-342``).
+
+Both are ``autograd.Function`` s over the C entry points of ``csrc/epilogue.cu``.  No CPU
+path: ``supports_*`` say whether a call can run; the functions raise otherwise.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, flash_cuda
+
+_DTYPE_CODE = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16,
+               torch.bfloat16: _lib.DTYPE_BF16}
+
+
+def _lib_or_raise():
+    lib = flash_cuda._load()
+    if lib is None:
+        raise RuntimeError(f"flash_cuda is unavailable ({flash_cuda.unavailable_reason()})")
+    return lib
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def supports_blend(v: torch.Tensor, v0: torch.Tensor, lam: torch.Tensor) -> bool:
+    return (v.is_cuda and v0.is_cuda and lam.is_cuda and v.dtype in _DTYPE_CODE and v0.dtype == v.dtype
+            and v.shape == v0.shape and v.numel() % 8 == 0 and lam.numel() == 1)
+
+
+def supports_gate(y: torch.Tensor, gate: torch.Tensor) -> bool:
+    return (y.dim() == 4 and y.is_cuda and gate.is_cuda and y.dtype in _DTYPE_CODE and gate.dtype in _DTYPE_CODE
+            and tuple(gate.shape) == tuple(y.shape[:3]) and y.shape[-1] in flash_cuda.SUPPORTED_HEAD_DIMS)
+
+
+class _ValueBlendFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, v, v0, lam, out_dtype):
+        lib = _lib_or_raise()
+        v, v0 = v.contiguous(), v0.contiguous()
+        lam32 = lam.detach().to(torch.float32).reshape(1).contiguous()
+        out = torch.empty(v.shape, dtype=out_dtype, device=v.device)
+        with torch.cuda.device(v.device):
+            st = lib.nlfa_value_blend_fwd(v.data_ptr(), v0.data_ptr(), _DTYPE_CODE[v.dtype], lam32.data_ptr(),
+                                          out.data_ptr(), _DTYPE_CODE[out_dtype], v.numel(), _stream())
+        _lib.check("nlfa_value_blend_fwd", st)
+        ctx.save_for_backward(v, v0, lam32)
+        ctx.lam_meta = (lam.dtype, lam.shape)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        lib = _lib_or_raise()
+        v, v0, lam32 = ctx.saved_tensors
+        g = g.contiguous()
+        dv, dv0 = torch.empty_like(v), torch.empty_like(v0)
+        dlam = torch.empty(1, dtype=torch.float32, device=v.device)
+        scratch = torch.empty(lib.nlfa_value_blend_scratch_bytes(), dtype=torch.uint8, device=v.device)
+        with torch.cuda.device(v.device):
+            st = lib.nlfa_value_blend_bwd(g.data_ptr(), _DTYPE_CODE[g.dtype], v.data_ptr(), v0.data_ptr(),
+                                          _DTYPE_CODE[v.dtype], lam32.data_ptr(), dv.data_ptr(), dv0.data_ptr(),
+                                          dlam.data_ptr(), scratch.data_ptr(), scratch.numel(), v.numel(), _stream())
+        _lib.check("nlfa_value_blend_bwd", st)
+        dtype, shape = ctx.lam_meta
+        return dv, dv0, dlam.to(dtype).reshape(shape), None
+
+
+class _HeadGateFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, gate):
+        lib = _lib_or_raise()
+        y, gate = y.contiguous(), gate.contiguous()
+        out = torch.empty_like(y)
+        rows, D = y.numel() // y.shape[-1], y.shape[-1]
+        with torch.cuda.device(y.device):
+            st = lib.nlfa_head_gate_fwd(y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(), _DTYPE_CODE[gate.dtype],
+                                        out.data_ptr(), rows, D, _stream())
+        _lib.check("nlfa_head_gate_fwd", st)
+        ctx.save_for_backward(y, gate)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        lib = _lib_or_raise()
+        y, gate = ctx.saved_tensors
+        g = g.contiguous().to(y.dtype)
+        dy, dgate = torch.empty_like(y), torch.empty_like(gate)
+        rows, D = y.numel() // y.shape[-1], y.shape[-1]
+        with torch.cuda.device(y.device):
+            st = lib.nlfa_head_gate_bwd(g.data_ptr(), y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(),
+                                        _DTYPE_CODE[gate.dtype], dy.data_ptr(), dgate.data_ptr(), rows, D, _stream())
+        _lib.check("nlfa_head_gate_bwd", st)
+        return dy, dgate
+
+
+def value_blend(v: torch.Tensor, v0: torch.Tensor, lam: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """``(1 - sigmoid(lam)) * v + sigmoid(lam) * v0`` in ``out_dtype`` (default: the autocast dtype
+    under CUDA autocast -- what ``flash_attn`` would cast to -- else ``v.dtype``)."""
+    if not supports_blend(v, v0, lam):
+        raise ValueError(f"value_blend: unsupported inputs {tuple(v.shape)} {v.dtype} / {v0.dtype} on {v.device}")
+    if out_dtype is None:
+        out_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else v.dtype
+    return _ValueBlendFn.apply(v, v0, lam, out_dtype)
+
+
+def head_gate(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """``y * sigmoid(gate)[..., None]`` for ``y [B,T,H,D]`` and gate logits ``[B,T,H]``."""
+    if not supports_gate(y, gate):
+        raise ValueError(f"head_gate: unsupported inputs {tuple(y.shape)} {y.dtype}, gate {tuple(gate.shape)} "
+                         f"{gate.dtype} on {y.device}")
+    return _HeadGateFn.apply(y, gate)

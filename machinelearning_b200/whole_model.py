@@ -32,7 +32,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import flash_cuda, mixer_glue, qk_prologue
+from . import flash_cuda, mixer_glue, qk_prologue, value_gate
 
 
 @dataclasses.dataclass
@@ -60,6 +60,7 @@ class ModelShape:
     swa_window: int = 0         # > 0: every layer is the SWA mixer (config.py:127-139)
     swa_sinks: int = 0
     fused_prologue: bool = True  # with flash_cuda on: QK-norm + RoPE + cast in one kernel (qk_prologue)
+    fused_epilogue: bool = True  # with flash_cuda on: value blend and head gate in one kernel each (value_gate)
 
     def __post_init__(self):
         if self.n_kv_head == 0:
@@ -123,6 +124,7 @@ class Attention(nn.Module):
         self.swa_window, self.swa_sinks = int(s.swa_window), int(s.swa_sinks)
         self._flash_declined = False
         self.fused_prologue = bool(s.fused_prologue)
+        self.fused_epilogue = bool(s.fused_epilogue)
 
     def _prologue(self, q, k, cos, sin):
         """QK-norm and RoPE (``mixers.py:287-292``): one fused kernel per tensor when this step goes
@@ -157,14 +159,22 @@ class Attention(nn.Module):
         k = self.k_proj(x).view(B, T, self.Hkv, self.D)
         v = raw_v = self.v_proj(x).view(B, T, self.Hkv, self.D)
         q, k = self._prologue(q, k, cos, sin)
+        fused = self.fused_epilogue and self.flash_cuda and x.is_cuda and flash_cuda.is_available()
         if self.vr_lambda is not None and v0 is not None:
-            lam = torch.sigmoid(self.vr_lambda)
-            v = (1 - lam) * v + lam * v0
+            if fused and value_gate.supports_blend(v, v0, self.vr_lambda):
+                v = value_gate.value_blend(v, v0, self.vr_lambda)
+            else:
+                lam = torch.sigmoid(self.vr_lambda)
+                v = (1 - lam) * v + lam * v0
         y = mixer_glue.attention_core(self, q, k, v, self.attn_scale)
         if y is None:
             y = self._sdpa(q, k, v)
         if self.gate is not None:
-            y = y * torch.sigmoid(self.gate(x)).unsqueeze(-1)
+            logits = self.gate(x)
+            if fused and value_gate.supports_gate(y, logits):
+                y = value_gate.head_gate(y, logits)
+            else:
+                y = y * torch.sigmoid(logits).unsqueeze(-1)
         return self.o_proj(y.reshape(B, T, self.H * self.D)), raw_v
 
 

@@ -106,14 +106,14 @@ def test_two_gloo_ranks_equal_one_rank_on_the_whole_batch(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("fused", [False, True], ids=["separate-prologue", "fused-prologue"])
+@pytest.mark.parametrize("fused", [False, True], ids=["torch-passes", "fused-prologue-epilogue"])
 @pytest.mark.parametrize("tag", list(CASES))
 def test_caller_through_the_kernels_matches_nanolab_gpt(tag, fused):
     """fp32 tensors, ``flash_cuda=True``: every layer's core runs in the library (D=32, GQA 4/2), with
-    QK-norm and RoPE as torch passes or as the fused prologue kernel."""
+    QK-norm, RoPE, value blend and head gate as torch passes or as the fused kernels."""
     from machinelearning_b200 import flash_cuda
     assert flash_cuda.is_available(), flash_cuda.unavailable_reason()
-    model, *rest = _load(tag, device="cuda", flash_cuda=True, fused_prologue=fused)
+    model, *rest = _load(tag, device="cuda", flash_cuda=True, fused_prologue=fused, fused_epilogue=fused)
     calls = []
     real = flash_cuda.flash_attn
     try:
@@ -139,19 +139,21 @@ def test_bf16_autocast_step_runs_the_tensor_core_path_and_lowers_the_loss():
 
 
 @pytest.mark.gpu
-def test_fused_and_separate_prologue_agree_under_bf16_autocast():
-    """Same weights, same tokens, bf16 autocast: loss and gradients with the prologue kernel against
-    the torch passes it replaces (2e-2 relative, ``max|a - b| / max|b|``)."""
+def test_fused_and_separate_passes_agree_under_bf16_autocast():
+    """Same weights, same tokens, bf16 autocast: loss and gradients with the prologue, value-blend and
+    gate kernels against the torch passes they replace (2e-2 relative, ``max|a - b| / max|b|``)."""
     shape = dict(n_layer=2, d_model=256, n_head=4, n_kv_head=2, head_dim=64, block_size=256, vocab_size=512,
                  flash_cuda=True, zero_init_proj=False)
     x, y = (t.cuda() for t in wm.synthetic_tokens(512, 4, 256, seed=2))
     out = []
     for fused in (False, True):
         torch.manual_seed(1)
-        model = wm.GPT(wm.ModelShape(**shape, fused_prologue=fused)).cuda()
+        model = wm.GPT(wm.ModelShape(**shape, fused_prologue=fused, fused_epilogue=fused)).cuda()
         with torch.no_grad():
             for b in model.blocks:
                 b.mixer.q_norm.weight.add_(0.2 * torch.randn_like(b.mixer.q_norm.weight))
+                b.mixer.gate.weight.normal_(0.0, 0.05)
+                b.mixer.vr_lambda.fill_(0.3)
         with torch.autocast("cuda", dtype=torch.bfloat16):
             _, loss = model(x, y)
         loss.backward()
