@@ -232,16 +232,9 @@ def _tensor_path_fits(dtype, head_dim) -> bool:
     return dtype in MMA_DTYPES and head_dim in MMA_HEAD_DIMS
 
 
-def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
-               scale: float | None = None, use_mma: bool | None = None, *,
-               window: int = 0, sinks: int = 0) -> torch.Tensor:
-    """Causal GQA flash attention. q [B,T,H,D], k/v [B,T,Hkv,D] -> [B,T,H,D].
-
-    Same contract as the reference (``flash_cuda.py:233-279``): raises
-    ``ValueError`` for unsupported inputs instead of falling back; casts q/k/v to
-    the effective dtype and makes them contiguous as autograd ops.  ``window`` /
-    ``sinks`` select the sliding-window mask; ``window=0`` is plain causal.
-    """
+def prepare(q, k, v, scale, use_mma, window, sinks):
+    """The checks, defaults and casts of ``flash_attn`` (reference: ``flash_cuda.py:251-278``);
+    returns ``(q, k, v, scale, use_mma)`` ready for the kernels."""
     if not supports(q, k, v):
         raise ValueError(
             "flash_cuda.flash_attn: unsupported inputs "
@@ -273,6 +266,23 @@ def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
             raise RuntimeError(
                 f"flash_cuda: use_mma=True but the tensor-core path is "
                 f"unavailable ({mma_unavailable_reason()})")
+    return q, k, v, scale, use_mma
+
+
+def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+               scale: float | None = None, use_mma: bool | None = None, *,
+               window: int = 0, sinks: int = 0) -> torch.Tensor:
+    """Causal GQA flash attention. q [B,T,H,D], k/v [B,T,Hkv,D] -> [B,T,H,D].
+
+    Same contract as the reference (``flash_cuda.py:233-279``): raises
+    ``ValueError`` for unsupported inputs instead of falling back; casts q/k/v to
+    the effective dtype and makes them contiguous as autograd ops.  ``window`` /
+    ``sinks`` select the sliding-window mask; ``window=0`` is plain causal.
+    """
+    q, k, v, scale, use_mma = prepare(q, k, v, scale, use_mma, window, sinks)
+    if torch.compiler.is_compiling():
+        from . import compile_ops              # registered operators: one graph node instead of a graph break
+        return compile_ops.attn_fwd(q, k, v, float(scale), bool(use_mma), int(window), int(sinks))[0]
     return _FlashAttnFn.apply(q, k, v, scale, use_mma, window, sinks)
 
 
