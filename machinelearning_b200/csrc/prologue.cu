@@ -46,12 +46,17 @@ qk_prologue_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ weig
     typename Elem<TIn>::Raw raw[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {            // every load first; the whole warp stays for the shuffles
-      const unsigned row = r0 + u * RPW + lane / LPR;
+      const unsigned row = r0 + (lane / LPR) * U + u;
       raw[u] = row < rows ? Elem<TIn>::load_raw(x + (size_t)row * D + sub * kVec) : Elem<TIn>::zero();
     }
+    // A lane's U rows are consecutive, so most of them share a position (H heads per position): the
+    // table entries are fetched again only when the position changes.  (Fetching them per row made the
+    // L1 the busiest unit: 64 bytes of table for every 16 bytes of x.)
+    float c[kVec], s[kVec];
+    unsigned t_have = 0xffffffffu;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const unsigned row = r0 + u * RPW + lane / LPR;
+      const unsigned row = r0 + (lane / LPR) * U + u;
       const bool live = row < rows;
       float v[kVec];
       Elem<TIn>::unpack(raw[u], v);
@@ -66,16 +71,16 @@ qk_prologue_fwd_kernel(const TIn* __restrict__ x, const float* __restrict__ weig
       }
       if (cosT) {
         const unsigned t = live ? (row / H) % T : 0u;
-        float c[kVec], s[kVec];
-        Elem<float>::load(cosT + (size_t)t * D + sub * kVec, c);
-        Elem<float>::load(sinT + (size_t)t * D + sub * kVec, s);
+        if (t != t_have) {
+          Elem<float>::load(cosT + (size_t)t * D + sub * kVec, c);
+          Elem<float>::load(sinT + (size_t)t * D + sub * kVec, s);
+          t_have = t;
+        }
 #pragma unroll
         for (int i = 0; i < kVec; ++i) {
           const float partner = __shfl_xor_sync(0xffffffffu, v[i], LPR / 2);
-          c[i] = v[i] * c[i] + sign * partner * s[i];
+          v[i] = v[i] * c[i] + sign * partner * s[i];
         }
-#pragma unroll
-        for (int i = 0; i < kVec; ++i) v[i] = c[i];
       }
       if (live) Elem<TOut>::store(y + (size_t)row * D + sub * kVec, v);
     }
@@ -109,7 +114,7 @@ qk_prologue_bwd_kernel(const TG* __restrict__ gy, const TIn* __restrict__ x, con
     float r[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const unsigned row = r0 + u * RPW + lane / LPR;
+      const unsigned row = r0 + (lane / LPR) * U + u;
       graw[u] = Elem<TG>::zero();
       xraw[u] = Elem<TIn>::zero();
       r[u] = 0.f;
@@ -118,18 +123,22 @@ qk_prologue_bwd_kernel(const TG* __restrict__ gy, const TIn* __restrict__ x, con
         if (weight) { xraw[u] = Elem<TIn>::load_raw(x + (size_t)row * D + sub * kVec); r[u] = rstd[row]; }
       }
     }
+    float c[kVec], s[kVec];                  // table entries, kept while the position stays the same
+    unsigned t_have = 0xffffffffu;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const unsigned row = r0 + u * RPW + lane / LPR;
+      const unsigned row = r0 + (lane / LPR) * U + u;
       const bool live = row < rows;
       float g[kVec], v[kVec];
       Elem<TG>::unpack(graw[u], g);
       Elem<TIn>::unpack(xraw[u], v);
       if (cosT) {
         const unsigned t = live ? (row / H) % T : 0u;
-        float c[kVec], s[kVec];
-        Elem<float>::load(cosT + (size_t)t * D + sub * kVec, c);
-        Elem<float>::load(sinT + (size_t)t * D + sub * kVec, s);
+        if (t != t_have) {
+          Elem<float>::load(cosT + (size_t)t * D + sub * kVec, c);
+          Elem<float>::load(sinT + (size_t)t * D + sub * kVec, s);
+          t_have = t;
+        }
 #pragma unroll
         for (int i = 0; i < kVec; ++i) {
           const float partner = __shfl_xor_sync(0xffffffffu, g[i] * s[i], LPR / 2);
