@@ -522,6 +522,7 @@ def run_whole_model_arm(args, rank, world, local_rank):
     flash_cuda.fwd = counted_fwd
     qk_prologue.qk_prologue = counted_prologue
 
+    captured = {}
     x_host, y_host = wm.synthetic_tokens(50304, GLOBAL_BATCH, 1024, seed=0)
     x_pin, y_pin = x_host[lo:lo + per_rank].pin_memory(), y_host[lo:lo + per_rank].pin_memory()
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
@@ -530,6 +531,14 @@ def run_whole_model_arm(args, rank, world, local_rank):
         model, step = build(flag)
         x, y = x_pin.to(dev), y_pin.to(dev)
         first_loss = step.step(x, y).item()        # same weights and tokens in both arms: comparable
+        captured[flag] = False
+        if not args.no_graph:
+            try:                                   # the whole step as one CUDA graph (both arms alike)
+                step.capture(x, y)
+                captured[flag] = True
+            except Exception as e:                 # noqa: BLE001
+                print(f"[bench] step not captured ({type(e).__name__}: {e}); launching eagerly", file=sys.stderr)
+                raise
         for _ in range(warmup - 1):
             step.step(x, y)
         barrier()
@@ -574,7 +583,8 @@ def run_whole_model_arm(args, rank, world, local_rank):
         "config": {"workload": WHOLE_MODEL_TEXT, "global_batch": GLOBAL_BATCH, "per_gpu_batch": per_rank,
                    "parallelism": f"data-parallel x{world}, flat-bucket NCCL all-reduce of the gradients",
                    "l2": "activations and weights far larger than the 126 MB L2",
-                   "params": 123699612, "flops_per_token": flops_tok},
+                   "params": 123699612, "flops_per_token": flops_tok,
+                   "launch": "whole step replayed from one CUDA graph" if captured.get(True) else "eager launches"},
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": 2 * x_pin.numel() * x_pin.element_size(), "d2h_bytes_per_step": 4},
         "gpu_launches": 4 * n_calls["n"] + 3 * n_calls["prologue"] + 3 * n_calls["blend"] + 2 * n_calls["gate"],
@@ -604,6 +614,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + [WHOLE_MODEL])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="c4: launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -269,6 +269,14 @@ class DataParallelStep:
     the result is unpacked -- layer 0's ``vr_lambda`` never gets a gradient (it has
     no ``v0``), which is why this does not use a wrapper that expects every
     parameter to take part.  With one rank no collective is issued.
+
+    ``capture(idx, targets)`` records the whole step -- forward, backward, the NCCL
+    all-reduces, the clip and the optimiser -- into one CUDA graph; ``step`` then copies
+    the batch into the graph's input buffers and replays it.  A step is about two
+    thousand kernel launches; at 8 GPUs (8 sequences per GPU) the host cannot issue them as
+    fast as the GPU finishes them, and one replay removes that bound.  The capture runs
+    three warm-up steps first with the learning rate at zero and clears the optimiser
+    state afterwards, so parameters and state are those of an uncaptured run.
     """
 
     def __init__(self, model: GPT, lr: float = 6e-4, weight_decay: float = 0.1, grad_clip: float = 1.0,
@@ -280,11 +288,14 @@ class DataParallelStep:
         decay = [p for p in params if p.dim() >= 2]
         rest = [p for p in params if p.dim() < 2]
         on_gpu = params[0].is_cuda
+        # on the GPU the learning rate is a device tensor: a captured step reads it at replay time
+        self.lr = torch.tensor(float(lr), device=params[0].device) if on_gpu else float(lr)
         self.opt = torch.optim.AdamW(
             [dict(params=decay, weight_decay=weight_decay), dict(params=rest, weight_decay=0.0)],
-            lr=lr, betas=(0.9, 0.95), fused=on_gpu)
+            lr=self.lr, betas=(0.9, 0.95), fused=on_gpu, capturable=on_gpu)
         self._flat = None
         self.collectives = 0
+        self._graph = None
 
     def average_gradients(self) -> None:
         if self.world == 1:
@@ -309,7 +320,38 @@ class DataParallelStep:
             self.collectives += 1
             i = j
 
+    def capture(self, idx, targets) -> None:
+        """Record one whole step into a CUDA graph (GPU only); later ``step`` calls replay it."""
+        if not idx.is_cuda:
+            raise ValueError("capture needs CUDA tensors")
+        self._idx, self._tgt = idx.clone(), targets.clone()
+        lr = self.lr.clone()
+        self.lr.zero_()                                   # warm-up steps must not move the parameters
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                self._eager_step(self._idx, self._tgt)
+        torch.cuda.current_stream().wait_stream(side)
+        for state in self.opt.state.values():             # in place: the graph keeps these tensors
+            for t in state.values():
+                if torch.is_tensor(t):
+                    t.zero_()
+        self.lr.copy_(lr)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._loss = self._eager_step(self._idx, self._tgt)
+        self._graph = graph
+
     def step(self, idx, targets) -> torch.Tensor:
+        if self._graph is not None:
+            self._idx.copy_(idx, non_blocking=True)
+            self._tgt.copy_(targets, non_blocking=True)
+            self._graph.replay()
+            return self._loss
+        return self._eager_step(idx, targets)
+
+    def _eager_step(self, idx, targets) -> torch.Tensor:
         dev = idx.device.type
         with torch.autocast(dev, dtype=self.dtype, enabled=self.dtype != torch.float32):
             _, loss = self.model(idx, targets)

@@ -163,3 +163,25 @@ def test_fused_and_separate_passes_agree_under_bf16_autocast():
     assert set(g0) == set(g1)
     for n in g0:
         assert (g0[n] - g1[n]).abs().max().item() <= 2e-2 * g0[n].abs().max().item() + 1e-6, n
+
+
+@pytest.mark.gpu
+def test_captured_step_follows_the_eager_trajectory():
+    """The whole step replayed from a CUDA graph against the same steps issued eagerly: same weights, same
+    batches; the losses agree step by step (bf16 autocast; the kernels are bit-reproducible, torch's own
+    reductions may differ in the last place between the two)."""
+    shape = dict(n_layer=2, d_model=256, n_head=4, head_dim=64, block_size=256, vocab_size=512, flash_cuda=True,
+                 zero_init_proj=False)
+    batches = [tuple(t.cuda() for t in wm.synthetic_tokens(512, 4, 256, seed=s)) for s in range(5)]
+    runs = []
+    for captured in (False, True):
+        torch.manual_seed(2)
+        model = wm.GPT(wm.ModelShape(**shape)).cuda()
+        step = wm.DataParallelStep(model, lr=3e-4)
+        if captured:
+            step.capture(*batches[0])
+        runs.append([step.step(x, y).item() for x, y in batches])
+    eager, graph = runs
+    assert all(np.isfinite(eager)) and all(np.isfinite(graph))
+    assert max(abs(a - b) for a, b in zip(eager, graph)) <= 2e-3 * max(eager)
+    assert graph[0] != graph[-1]                      # the replays do train
