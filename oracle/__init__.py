@@ -8,5 +8,6 @@ Parity status: PINNED.  ``attention_f64`` is checked against golden vectors that
 were produced by importing the reference's own float64 brute force
 (``nanolab/csrc/flash_attn_sim.py:193-212`` differentiated by autograd) and its
 sliding-window definitions (``nanolab/mixers.py:96-135``, ``:168-200``); the
-generating script and the vectors live in ``tests/golden``.
+generating script and the vectors live in ``tests/golden``.  ``build_ref`` compiles the
+reference's own CUDA kernel into ``oracle/_ref/`` as a second checker on the GPU.
 """
