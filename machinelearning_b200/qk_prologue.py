@@ -52,22 +52,47 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+def fwd(x, weight, cos, sin, eps: float, out_dtype):
+    """(y, rstd) through the C ABI: contiguous CUDA ``x``; float32 ``weight`` / ``cos`` / ``sin`` or None."""
+    lib = flash_cuda._load()
+    if lib is None:
+        raise RuntimeError(f"flash_cuda is unavailable ({flash_cuda.unavailable_reason()})")
+    B, T, H, D = x.shape
+    y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    rstd = torch.empty(B * T * H if weight is not None else 1, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = lib.nlfa_qk_prologue_fwd(x.data_ptr(), _DTYPE_CODE[x.dtype], _ptr(weight), _ptr(cos), _ptr(sin),
+                                      y.data_ptr(), _DTYPE_CODE[out_dtype], rstd.data_ptr(),
+                                      B, T, H, D, float(eps), torch.cuda.current_stream().cuda_stream)
+    _lib.check("nlfa_qk_prologue_fwd", st)
+    return y, rstd
+
+
+def bwd(gy, x, weight, cos, sin, rstd):
+    """(gx, gweight) through the C ABI; ``gweight`` is float32 ``[D]`` (a 1-element dummy without a weight)."""
+    lib = flash_cuda._load()
+    if lib is None:
+        raise RuntimeError(f"flash_cuda is unavailable ({flash_cuda.unavailable_reason()})")
+    B, T, H, D = x.shape
+    gx = torch.empty_like(x)
+    gw = torch.empty(D if weight is not None else 1, dtype=torch.float32, device=x.device)
+    nbytes = lib.nlfa_qk_prologue_scratch_bytes(D) if weight is not None else 0
+    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        st = lib.nlfa_qk_prologue_bwd(gy.data_ptr(), _DTYPE_CODE[gy.dtype], x.data_ptr(), _DTYPE_CODE[x.dtype],
+                                      _ptr(weight), _ptr(cos), _ptr(sin), rstd.data_ptr(), gx.data_ptr(),
+                                      gw.data_ptr() if weight is not None else None, scratch.data_ptr(),
+                                      scratch.numel(), B, T, H, D, torch.cuda.current_stream().cuda_stream)
+    _lib.check("nlfa_qk_prologue_bwd", st)
+    return gx, gw
+
+
 class _QkPrologueFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, cos, sin, eps, out_dtype):
-        lib = flash_cuda._load()
-        if lib is None:
-            raise RuntimeError(f"flash_cuda is unavailable ({flash_cuda.unavailable_reason()})")
         x = x.contiguous()
-        B, T, H, D = x.shape
         w, c, s = _f32(weight), _f32(cos), _f32(sin)
-        y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        rstd = torch.empty(B * T * H if w is not None else 1, dtype=torch.float32, device=x.device)
-        with torch.cuda.device(x.device):
-            st = lib.nlfa_qk_prologue_fwd(x.data_ptr(), _DTYPE_CODE[x.dtype], _ptr(w), _ptr(c), _ptr(s),
-                                          y.data_ptr(), _DTYPE_CODE[out_dtype], rstd.data_ptr(),
-                                          B, T, H, D, float(eps), torch.cuda.current_stream().cuda_stream)
-        _lib.check("nlfa_qk_prologue_fwd", st)
+        y, rstd = fwd(x, w, c, s, eps, out_dtype)
         ctx.save_for_backward(x, w, c, s, rstd)
         ctx.weight_dtype = None if weight is None else weight.dtype
         return y
@@ -75,22 +100,9 @@ class _QkPrologueFn(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, gy):
-        lib = flash_cuda._load()
         x, w, c, s, rstd = ctx.saved_tensors
-        gy = gy.contiguous()
-        B, T, H, D = x.shape
-        gx = torch.empty_like(x)
-        gw = torch.empty(D, dtype=torch.float32, device=x.device) if w is not None else None
-        nbytes = lib.nlfa_qk_prologue_scratch_bytes(D) if w is not None else 0
-        scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)
-        with torch.cuda.device(x.device):
-            st = lib.nlfa_qk_prologue_bwd(gy.data_ptr(), _DTYPE_CODE[gy.dtype], x.data_ptr(),
-                                          _DTYPE_CODE[x.dtype], _ptr(w), _ptr(c), _ptr(s), rstd.data_ptr(),
-                                          gx.data_ptr(), _ptr(gw), scratch.data_ptr(), scratch.numel(),
-                                          B, T, H, D, torch.cuda.current_stream().cuda_stream)
-        _lib.check("nlfa_qk_prologue_bwd", st)
-        if gw is not None and ctx.weight_dtype != torch.float32:
-            gw = gw.to(ctx.weight_dtype)
+        gx, gw = bwd(gy.contiguous(), x, w, c, s, rstd)
+        gw = None if w is None else gw.to(ctx.weight_dtype)
         return gx, gw, None, None, None, None
 
 
@@ -107,6 +119,9 @@ def qk_prologue(x: torch.Tensor, weight=None, cos=None, sin=None, eps: float = E
         out_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
     if out_dtype not in _DTYPE_CODE:
         raise ValueError(f"qk_prologue: unsupported output dtype {out_dtype}")
+    if torch.compiler.is_compiling():
+        from . import compile_ops              # registered operators: one graph node instead of a graph break
+        return compile_ops.qk_prologue(x, weight, cos, sin, eps, out_dtype)
     return _QkPrologueFn.apply(x, weight, cos, sin, eps, out_dtype)
 
 

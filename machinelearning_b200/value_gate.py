@@ -42,35 +42,68 @@ def supports_gate(y: torch.Tensor, gate: torch.Tensor) -> bool:
             and tuple(gate.shape) == tuple(y.shape[:3]) and y.shape[-1] in flash_cuda.SUPPORTED_HEAD_DIMS)
 
 
+def blend_fwd(v, v0, lam32, out_dtype):
+    """The blend through the C ABI: contiguous ``v`` / ``v0`` of one dtype, ``lam32`` one float32 on the device."""
+    lib = _lib_or_raise()
+    out = torch.empty(v.shape, dtype=out_dtype, device=v.device)
+    with torch.cuda.device(v.device):
+        st = lib.nlfa_value_blend_fwd(v.data_ptr(), v0.data_ptr(), _DTYPE_CODE[v.dtype], lam32.data_ptr(),
+                                      out.data_ptr(), _DTYPE_CODE[out_dtype], v.numel(), _stream())
+    _lib.check("nlfa_value_blend_fwd", st)
+    return out
+
+
+def blend_bwd(g, v, v0, lam32):
+    """(dv, dv0, dlambda float32 [1])."""
+    lib = _lib_or_raise()
+    dv, dv0 = torch.empty_like(v), torch.empty_like(v0)
+    dlam = torch.empty(1, dtype=torch.float32, device=v.device)
+    scratch = torch.empty(lib.nlfa_value_blend_scratch_bytes(), dtype=torch.uint8, device=v.device)
+    with torch.cuda.device(v.device):
+        st = lib.nlfa_value_blend_bwd(g.data_ptr(), _DTYPE_CODE[g.dtype], v.data_ptr(), v0.data_ptr(),
+                                      _DTYPE_CODE[v.dtype], lam32.data_ptr(), dv.data_ptr(), dv0.data_ptr(),
+                                      dlam.data_ptr(), scratch.data_ptr(), scratch.numel(), v.numel(), _stream())
+    _lib.check("nlfa_value_blend_bwd", st)
+    return dv, dv0, dlam
+
+
+def gate_fwd(y, gate):
+    lib = _lib_or_raise()
+    out = torch.empty_like(y)
+    rows, D = y.numel() // y.shape[-1], y.shape[-1]
+    with torch.cuda.device(y.device):
+        st = lib.nlfa_head_gate_fwd(y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(), _DTYPE_CODE[gate.dtype],
+                                    out.data_ptr(), rows, D, _stream())
+    _lib.check("nlfa_head_gate_fwd", st)
+    return out
+
+
+def gate_bwd(g, y, gate):
+    """(dy, dgate)."""
+    lib = _lib_or_raise()
+    dy, dgate = torch.empty_like(y), torch.empty_like(gate)
+    rows, D = y.numel() // y.shape[-1], y.shape[-1]
+    with torch.cuda.device(y.device):
+        st = lib.nlfa_head_gate_bwd(g.data_ptr(), y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(),
+                                    _DTYPE_CODE[gate.dtype], dy.data_ptr(), dgate.data_ptr(), rows, D, _stream())
+    _lib.check("nlfa_head_gate_bwd", st)
+    return dy, dgate
+
+
 class _ValueBlendFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, v, v0, lam, out_dtype):
-        lib = _lib_or_raise()
         v, v0 = v.contiguous(), v0.contiguous()
         lam32 = lam.detach().to(torch.float32).reshape(1).contiguous()
-        out = torch.empty(v.shape, dtype=out_dtype, device=v.device)
-        with torch.cuda.device(v.device):
-            st = lib.nlfa_value_blend_fwd(v.data_ptr(), v0.data_ptr(), _DTYPE_CODE[v.dtype], lam32.data_ptr(),
-                                          out.data_ptr(), _DTYPE_CODE[out_dtype], v.numel(), _stream())
-        _lib.check("nlfa_value_blend_fwd", st)
         ctx.save_for_backward(v, v0, lam32)
         ctx.lam_meta = (lam.dtype, lam.shape)
-        return out
+        return blend_fwd(v, v0, lam32, out_dtype)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, g):
-        lib = _lib_or_raise()
         v, v0, lam32 = ctx.saved_tensors
-        g = g.contiguous()
-        dv, dv0 = torch.empty_like(v), torch.empty_like(v0)
-        dlam = torch.empty(1, dtype=torch.float32, device=v.device)
-        scratch = torch.empty(lib.nlfa_value_blend_scratch_bytes(), dtype=torch.uint8, device=v.device)
-        with torch.cuda.device(v.device):
-            st = lib.nlfa_value_blend_bwd(g.data_ptr(), _DTYPE_CODE[g.dtype], v.data_ptr(), v0.data_ptr(),
-                                          _DTYPE_CODE[v.dtype], lam32.data_ptr(), dv.data_ptr(), dv0.data_ptr(),
-                                          dlam.data_ptr(), scratch.data_ptr(), scratch.numel(), v.numel(), _stream())
-        _lib.check("nlfa_value_blend_bwd", st)
+        dv, dv0, dlam = blend_bwd(g.contiguous(), v, v0, lam32)
         dtype, shape = ctx.lam_meta
         return dv, dv0, dlam.to(dtype).reshape(shape), None
 
@@ -78,30 +111,15 @@ class _ValueBlendFn(torch.autograd.Function):
 class _HeadGateFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, gate):
-        lib = _lib_or_raise()
         y, gate = y.contiguous(), gate.contiguous()
-        out = torch.empty_like(y)
-        rows, D = y.numel() // y.shape[-1], y.shape[-1]
-        with torch.cuda.device(y.device):
-            st = lib.nlfa_head_gate_fwd(y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(), _DTYPE_CODE[gate.dtype],
-                                        out.data_ptr(), rows, D, _stream())
-        _lib.check("nlfa_head_gate_fwd", st)
         ctx.save_for_backward(y, gate)
-        return out
+        return gate_fwd(y, gate)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, g):
-        lib = _lib_or_raise()
         y, gate = ctx.saved_tensors
-        g = g.contiguous().to(y.dtype)
-        dy, dgate = torch.empty_like(y), torch.empty_like(gate)
-        rows, D = y.numel() // y.shape[-1], y.shape[-1]
-        with torch.cuda.device(y.device):
-            st = lib.nlfa_head_gate_bwd(g.data_ptr(), y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(),
-                                        _DTYPE_CODE[gate.dtype], dy.data_ptr(), dgate.data_ptr(), rows, D, _stream())
-        _lib.check("nlfa_head_gate_bwd", st)
-        return dy, dgate
+        return gate_bwd(g.contiguous().to(y.dtype), y, gate)
 
 
 def value_blend(v: torch.Tensor, v0: torch.Tensor, lam: torch.Tensor, out_dtype=None) -> torch.Tensor:
@@ -111,6 +129,9 @@ def value_blend(v: torch.Tensor, v0: torch.Tensor, lam: torch.Tensor, out_dtype=
         raise ValueError(f"value_blend: unsupported inputs {tuple(v.shape)} {v.dtype} / {v0.dtype} on {v.device}")
     if out_dtype is None:
         out_dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else v.dtype
+    if torch.compiler.is_compiling():
+        from . import compile_ops              # registered operators: one graph node instead of a graph break
+        return compile_ops.value_blend(v, v0, lam, out_dtype)
     return _ValueBlendFn.apply(v, v0, lam, out_dtype)
 
 
@@ -119,4 +140,7 @@ def head_gate(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     if not supports_gate(y, gate):
         raise ValueError(f"head_gate: unsupported inputs {tuple(y.shape)} {y.dtype}, gate {tuple(gate.shape)} "
                          f"{gate.dtype} on {y.device}")
+    if torch.compiler.is_compiling():
+        from . import compile_ops
+        return compile_ops.head_gate(y, gate)
     return _HeadGateFn.apply(y, gate)
