@@ -144,3 +144,70 @@ def head_gate(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
         from . import compile_ops
         return compile_ops.head_gate(y, gate)
     return _HeadGateFn.apply(y, gate)
+
+
+def main() -> int:
+    """Self-check against the torch expressions these replace, then kernel timings.
+
+        python -m machinelearning_b200.value_gate [--batch 64 --seq 1024 --heads 12 --head_dim 64 --iters 20]
+
+    Timings call the plain ``*_fwd`` / ``*_bwd`` functions (C entry points, CUDA events, no
+    autograd); GB/s counts every operand once and every result once.
+    """
+    import argparse
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--head_dim", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    if not flash_cuda.is_available():
+        print("unavailable:", flash_cuda.unavailable_reason())
+        return 1
+    B, T, H, D = a.batch, a.seq, a.heads, a.head_dim
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g).bfloat16()
+    v, v0, gv, y, gy = (rnd(B, T, H, D) for _ in range(5))
+    gate = rnd(B, T, H)
+    lam = torch.tensor([0.3], device="cuda")
+
+    vs, v0s, ls = v[:2].clone().requires_grad_(), v0[:2].clone().requires_grad_(), lam.clone().requires_grad_()
+    value_blend(vs, v0s, ls, out_dtype=torch.bfloat16).backward(gv[:2])
+    vr, v0r, lr = v[:2].clone().requires_grad_(), v0[:2].clone().requires_grad_(), lam.clone().requires_grad_()
+    s = torch.sigmoid(lr)
+    ((1 - s) * vr + s * v0r).to(torch.bfloat16).backward(gv[:2])
+    rel = lambda p, q: ((p.float() - q.float()).abs().max() / q.float().abs().max()).item()
+    print(f"value blend vs torch (relative): dv {rel(vs.grad, vr.grad):.2e}  dv0 {rel(v0s.grad, v0r.grad):.2e}  "
+          f"dlambda {rel(ls.grad, lr.grad):.2e}")
+    ys, gs = y[:2].clone().requires_grad_(), gate[:2].clone().requires_grad_()
+    head_gate(ys, gs).backward(gy[:2])
+    yr, gr = y[:2].clone().requires_grad_(), gate[:2].clone().requires_grad_()
+    (yr * torch.sigmoid(gr).unsqueeze(-1)).backward(gy[:2])
+    print(f"head gate vs torch (relative): dy {rel(ys.grad, yr.grad):.2e}  dgate {rel(gs.grad, gr.grad):.2e}")
+
+    def time_ms(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / a.iters
+
+    n, rows = B * T * H * D, B * T * H
+    for name, fn, nbytes in (
+            ("value blend forward", lambda: blend_fwd(v, v0, lam, torch.bfloat16), 6 * n),
+            ("value blend backward", lambda: blend_bwd(gv, v, v0, lam), 10 * n),
+            ("head gate forward", lambda: gate_fwd(y, gate), 4 * n + 2 * rows),
+            ("head gate backward", lambda: gate_bwd(gy, y, gate), 6 * n + 4 * rows)):
+        ms = time_ms(fn)
+        print(f"[{B},{T},{H},{D}] bf16 {name}: {ms * 1e3:.1f} us = {nbytes / ms / 1e6:.0f} GB/s ({nbytes / 1e6:.1f} MB)")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
