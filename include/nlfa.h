@@ -198,6 +198,21 @@ int nlfa_head_gate_fwd(const void* y, int y_dtype, const void* gate, int gate_dt
 int nlfa_head_gate_bwd(const void* g, const void* y, int y_dtype, const void* gate, int gate_dtype,
                        void* dy, void* dgate, long long rows, int D, void* stream);
 
+/* Forward attention of an active block of Tq queries over [cache | block], masked by
+ * absolute positions: the attention core of nanolab's KV-cached block forward
+ * (`Attention.forward_cached`, nanolab/mixers.py:372-467), which nanolab runs as a
+ * torch.cat, a repeat_interleave and a masked SDPA.  Forward only.
+ *   q, o [B,Tq,H,D]; k_cache, v_cache [B,Hkv,L,D] (nanolab's cache layout, the block's own
+ *   keys last); lse [B,H,Tq] float32 natural log, or NULL; qpos [Tq], kpos [L] int32 on the
+ *   device, or NULL for contiguous positions (keys 0..L-1, the block at L-Tq..L-1).
+ * Mask: window > 0 (needs causal): kpos <= qpos and (kpos > qpos - (window - sinks) or
+ * kpos < sinks) (mixers.py:417-432; positions stay correct after cache eviction);
+ * causal: kpos <= qpos (:433-437); neither: every key.  A row that sees no key gives
+ * zeros and lse = -inf. */
+int nlfa_fwd_cached(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
+                    const int* qpos, const int* kpos, int B, int Tq, int H, int Hkv, int L, int D,
+                    float scale, int causal, int window, int sinks, int dtype, void* stream);
+
 /* Bytes of device workspace `nlfa_selftest` needs. */
 size_t nlfa_selftest_workspace_bytes(void);
 

@@ -286,6 +286,55 @@ def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return _FlashAttnFn.apply(q, k, v, scale, use_mma, window, sinks)
 
 
+def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tensor, scale: float | None = None, *,
+                      qpos: torch.Tensor | None = None, kpos: torch.Tensor | None = None, causal: bool = False,
+                      window: int = 0, sinks: int = 0, return_lse: bool = False):
+    """Attention of an active block over [cache | block]: the core of nanolab's ``forward_cached``.
+
+    ``q [B,T,H,D]`` is the active block; ``k_full`` / ``v_full [B,Hkv,L,D]`` are the cache with the
+    block's own keys appended, in nanolab's cache layout (``nanolab/mixers.py:401-405``), narrow KV
+    heads; ``qpos [T]`` / ``kpos [L]`` are absolute positions (``None``: contiguous, the block last).
+    The mask is the one ``forward_cached`` builds (``mixers.py:417-437``): with a window, the
+    sliding-window mask on positions (``causal`` must be set, as nanolab requires); with
+    ``causal``, full to the cache and lower-triangular in the block; otherwise every key.
+    Forward only (nanolab runs this path under ``no_grad``); returns ``[B,T,H,D]`` (and the
+    logsumexp ``[B,H,T]`` with ``return_lse``).  Raises ``ValueError`` for unsupported inputs.
+    """
+    ok = (q.dim() == 4 and k_full.dim() == 4 and v_full.dim() == 4 and q.is_cuda and k_full.is_cuda and v_full.is_cuda
+          and q.dtype == k_full.dtype == v_full.dtype and q.dtype in SUPPORTED_DTYPES
+          and q.shape[-1] in SUPPORTED_HEAD_DIMS and k_full.shape == v_full.shape
+          and k_full.shape[0] == q.shape[0] and k_full.shape[3] == q.shape[3]
+          and k_full.shape[1] > 0 and q.shape[2] % k_full.shape[1] == 0)
+    if not ok:
+        raise ValueError(f"flash_attn_cached: unsupported inputs (q={tuple(q.shape)}/{q.dtype}, "
+                         f"k={tuple(k_full.shape)}/{k_full.dtype}, v={tuple(v_full.shape)}/{v_full.dtype})")
+    check_window(window, sinks)
+    if window and not causal:
+        raise ValueError("cached SWA decode requires causal=True")          # nanolab/mixers.py:410-414
+    B, T, H, D = q.shape
+    Hkv, L = k_full.shape[1], k_full.shape[2]
+    if qpos is None and T > L:
+        raise ValueError("without positions the block must be the last T of the L keys")
+    lib = _load()
+    if lib is None:
+        raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    pos = lambda t, n: None if t is None else t.detach().to(device=q.device, dtype=torch.int32).reshape(n).contiguous()
+    qp, kp = pos(qpos, T), pos(kpos, L)
+    q, k_full, v_full = q.detach().contiguous(), k_full.detach().contiguous(), v_full.detach().contiguous()
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device) if return_lse else None
+    with torch.cuda.device(q.device):
+        st = lib.nlfa_fwd_cached(q.data_ptr(), k_full.data_ptr(), v_full.data_ptr(), o.data_ptr(),
+                                 None if lse is None else lse.data_ptr(),
+                                 None if qp is None else qp.data_ptr(), None if kp is None else kp.data_ptr(),
+                                 B, T, H, Hkv, L, D, float(scale), int(bool(causal)), int(window), int(sinks),
+                                 _DTYPE_CODE[q.dtype], torch.cuda.current_stream().cuda_stream)
+    _lib.check("nlfa_fwd_cached", st)
+    return (o, lse) if return_lse else o
+
+
 def sdpa_reference(q, k, v, scale):
     """What nanolab does without the kernel (reference: ``flash_cuda.py:282-294``):
     widen KV heads, transpose, call torch SDPA.  A comparison arm for the

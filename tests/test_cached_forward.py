@@ -1,0 +1,104 @@
+"""The KV-cached block forward: the oracle against what nanolab's own ``forward_hidden_window`` fed to
+and got from SDPA (``tests/golden/cached_forward.npz``), host-side argument checks, and -- on the GPU --
+the kernel against the same recorded calls and against the oracle at a decode-sized shape."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from oracle import cached_f64
+
+D_ = np.load(GOLDEN / "cached_forward.npz")
+CALLS = sorted({k.rsplit("/", 1)[0] for k in D_.files})
+
+
+def _call(name):
+    causal, window, sinks = (int(x) for x in D_[name + "/meta"])
+    return dict(q=D_[name + "/q"], k=D_[name + "/k"], v=D_[name + "/v"], y=D_[name + "/y"], mask=D_[name + "/mask"],
+                qpos=D_[name + "/qpos"], kpos=D_[name + "/kpos"], scale=float(D_[name + "/scale"]),
+                causal=bool(causal), window=window, sinks=sinks)
+
+
+@pytest.mark.parametrize("name", CALLS)
+def test_oracle_reproduces_nanolabs_masks_and_sdpa_results(name):
+    c = _call(name)
+    keep = cached_f64.keep_mask(c["qpos"], c["kpos"], c["causal"], c["window"], c["sinks"])
+    assert np.array_equal(keep, c["mask"])
+    y, _ = cached_f64.forward(c["q"], c["k"], c["v"], c["scale"], c["qpos"], c["kpos"], c["causal"], c["window"],
+                              c["sinks"])
+    assert np.abs(y - c["y"]).max() <= 1e-12
+
+
+def test_fixture_covers_eviction():
+    gaps = [n for n in CALLS if n.startswith("swa") and np.any(np.diff(D_[n + "/kpos"]) > 1)]
+    assert gaps, "no recorded call has non-contiguous key positions"
+
+
+def test_entry_point_refuses_bad_arguments_before_any_launch():
+    from machinelearning_b200 import _build, _lib
+    _build.build()
+    f = _lib.load().nlfa_fwd_cached
+    args = lambda **kw: [kw.get("q", 16), 16, 16, 16, None, None, None, kw.get("B", 1), kw.get("T", 4), kw.get("H", 4),
+                         kw.get("Hkv", 2), kw.get("L", 8), kw.get("D", 64), 0.125, kw.get("causal", 1),
+                         kw.get("window", 0), kw.get("sinks", 0), kw.get("dtype", 2), None]
+    assert f(*args(D=48)) == 4
+    assert f(*args(dtype=7)) == 3
+    assert f(*args(Hkv=3)) == 2
+    assert f(*args(window=4, sinks=4)) == 5
+    assert f(*args(window=4, causal=0)) == 5          # a window needs a causal block
+    assert f(*args(T=9, L=8)) == 2                    # contiguous default: the block is part of the keys
+    assert f(*args(q=None)) == 1
+    assert f(*args(B=0)) == 0
+
+
+def test_python_wrapper_rejects_cpu_tensors_and_bidirectional_windows():
+    from machinelearning_b200 import flash_cuda
+    q, k = torch.zeros(1, 4, 2, 64), torch.zeros(1, 1, 8, 64)
+    with pytest.raises(ValueError):
+        flash_cuda.flash_attn_cached(q, k, k)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("name", CALLS)
+def test_kernel_matches_nanolabs_recorded_calls(name, dtype):
+    """fp32: max-abs 1e-5 against SDPA's float64 result; bf16: 2e-2 relative against the oracle on the
+    same rounded inputs (``max|x - ref| / max|ref|``)."""
+    from machinelearning_b200 import flash_cuda
+    c = _call(name)
+    t = lambda a: torch.from_numpy(a).to("cuda", dtype)
+    q, k, v = t(c["q"]), t(c["k"]), t(c["v"])
+    y, lse = flash_cuda.flash_attn_cached(q, k, v, c["scale"], qpos=torch.from_numpy(c["qpos"]),
+                                          kpos=torch.from_numpy(c["kpos"]), causal=c["causal"], window=c["window"],
+                                          sinks=c["sinks"], return_lse=True)
+    if dtype == torch.float32:
+        assert np.abs(y.double().cpu().numpy() - c["y"]).max() <= 1e-5
+    ref, lse_ref = cached_f64.forward(q.double().cpu().numpy(), k.double().cpu().numpy(), v.double().cpu().numpy(),
+                                      c["scale"], c["qpos"], c["kpos"], c["causal"], c["window"], c["sinks"])
+    tol = 1e-5 if dtype == torch.float32 else 2e-2 * np.abs(ref).max()
+    assert np.abs(y.double().cpu().numpy() - ref).max() <= tol
+    assert np.abs(lse.double().cpu().numpy() - lse_ref).max() <= (1e-5 if dtype == torch.float32 else 1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [32, 64, 128])
+def test_decode_sized_block_with_default_positions_and_an_unseen_row(D):
+    """A 32-token block over 1,000 cached keys, GQA 8/2, contiguous default positions, against the oracle;
+    and a window case whose explicit positions leave one query row with no visible key (zeros, -inf)."""
+    from machinelearning_b200 import flash_cuda
+    g = torch.Generator().manual_seed(D)
+    B, T, H, Hkv, L = 2, 32, 8, 2, 1032
+    q = torch.randn(B, T, H, D, generator=g).bfloat16().cuda()
+    k = torch.randn(B, Hkv, L, D, generator=g).bfloat16().cuda()
+    v = torch.randn(B, Hkv, L, D, generator=g).bfloat16().cuda()
+    for causal, window, sinks in ((False, 0, 0), (True, 0, 0), (True, 200, 4)):
+        y = flash_cuda.flash_attn_cached(q, k, v, causal=causal, window=window, sinks=sinks)
+        ref, _ = cached_f64.forward(q.double().cpu().numpy(), k.double().cpu().numpy(), v.double().cpu().numpy(),
+                                    1.0 / np.sqrt(D), np.arange(L - T, L), np.arange(L), causal, window, sinks)
+        assert np.abs(y.double().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max()
+    qpos = torch.tensor([5] + list(range(L - T + 1, L)))           # row 0 sits before every key it could reach
+    kpos = torch.arange(100, 100 + L)
+    y, lse = flash_cuda.flash_attn_cached(q, k, v, qpos=qpos, kpos=kpos, causal=True, window=64, sinks=0,
+                                          return_lse=True)
+    assert torch.count_nonzero(y[:, 0]).item() == 0 and torch.isinf(lse[:, :, 0]).all()
+    assert torch.isfinite(y.float()).all()
