@@ -2,6 +2,9 @@
 
     python oracle/build_ref.py [/path/to/reference]      # -> oracle/_ref/nanolab_flash_attn.so
 
+Without an argument the reference checkout is looked for beside this repository (a sibling
+directory named ``reference``).
+
 The reference's single CUDA source (``nanolab/csrc/flash_attn_cuda.cu``) is compiled where
 it lies, with one direct nvcc command (no ninja, none of the reference's own build code),
 into a Python extension module under ``oracle/_ref/`` (git-ignored; it travels to the GPU
@@ -23,8 +26,9 @@ HERE = pathlib.Path(__file__).resolve().parent
 OUT = HERE / "_ref" / "nanolab_flash_attn.so"
 
 
-def build(ref_root: str = "/root/reference", force: bool = False) -> pathlib.Path | None:
-    src = pathlib.Path(ref_root) / "nanolab" / "csrc" / "flash_attn_cuda.cu"
+def build(ref_root: str | None = None, force: bool = False) -> pathlib.Path | None:
+    root = pathlib.Path(ref_root) if ref_root else HERE.parent.parent / "reference"
+    src = root / "nanolab" / "csrc" / "flash_attn_cuda.cu"
     if not src.exists():
         return OUT if OUT.exists() else None
     if OUT.exists() and not force and OUT.stat().st_mtime >= src.stat().st_mtime:
@@ -60,4 +64,5 @@ def load():
 
 
 if __name__ == "__main__":
-    print(build(*(sys.argv[1:2]), force="--force" in sys.argv))
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(build(args[0] if args else None, force="--force" in sys.argv))

@@ -6,8 +6,6 @@ source does not).  Where that file is absent the tests skip.  The reference kern
 plain-causal only, so windows are not compared here (the float64 oracle covers them)."""
 import json
 import math
-import os
-import pathlib
 
 import numpy as np
 import pytest
@@ -94,8 +92,5 @@ def test_faster_than_the_reference_kernel_at_the_124m_shape(ref):
             "these_kernels_ms": {"fwd": t_own[0], "bwd": t_own[1]},
             "reference_tflops": flops / sum(t_ref) / 1e9, "these_tflops": flops / sum(t_own) / 1e9,
             "speedup": sum(t_ref) / sum(t_own)}
-    print("\nreference kernel comparison:", json.dumps(line))
-    out = pathlib.Path(os.environ.get("GRAFT_REPO_ROOT", ".")) / "gpurun_out"
-    if out.is_dir():
-        (out / "reference_kernel_times.json").write_text(json.dumps(line))
+    print("\nreference kernel comparison:", json.dumps(line))       # shown with pytest -s
     assert sum(t_own) < sum(t_ref)
