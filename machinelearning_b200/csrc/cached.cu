@@ -86,10 +86,11 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
 #pragma unroll
     for (int d = 0; d < D; ++d) acc[i][d] = 0.f;
   }
-  for (int j0 = 0; j0 < p.L; j0 += 32) {
+  // Which rows of this warp see key j0 + lane; `any`: some row does.
+  auto visible = [&](int j0, bool (&see)[RPW]) -> bool {
     const int j = j0 + lane;
     const int kp = j < p.L ? (p.kpos ? p.kpos[j] : j) : 0;
-    bool see[RPW], any = false;
+    bool any = false;
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
       see[i] = j < p.L && orow[i] >= 0;
@@ -99,16 +100,56 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
       }
       any |= see[i];
     }
-    if (!__syncthreads_or(any)) continue;                  // every thread of the CTA votes on every tile
-    for (int c = threadIdx.x; c < kChunks; c += kWarps * 32) {
+    return any;
+  };
+  // A thread's share of a tile: kPer 16-byte chunks of K and of V, fetched into registers one tile
+  // ahead (while the current tile is being used) when that is few enough registers.
+  constexpr int kPer = kChunks / (kWarps * 32);
+  constexpr bool kAhead = kPer <= 4;
+  uint4 nk[kAhead ? kPer : 1], nv[kAhead ? kPer : 1];
+  auto fetch = [&](int j0) {
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int c = threadIdx.x + u * kWarps * 32;
       const int r = c / kChunksPerRow, cc = c % kChunksPerRow;
       if (j0 + r < p.L) {
         const long long src = static_cast<long long>(j0 + r) * kRowBytes + cc * 16;
-        *reinterpret_cast<uint4*>(ks + r * kPitch + cc * 16) = *reinterpret_cast<const uint4*>(kb + src);
-        *reinterpret_cast<uint4*>(vs + r * kPitch + cc * 16) = *reinterpret_cast<const uint4*>(vb + src);
+        if constexpr (kAhead) {
+          nk[u] = *reinterpret_cast<const uint4*>(kb + src);
+          nv[u] = *reinterpret_cast<const uint4*>(vb + src);
+        } else {
+          *reinterpret_cast<uint4*>(ks + r * kPitch + cc * 16) = *reinterpret_cast<const uint4*>(kb + src);
+          *reinterpret_cast<uint4*>(vs + r * kPitch + cc * 16) = *reinterpret_cast<const uint4*>(vb + src);
+        }
       }
     }
-    __syncthreads();
+  };
+  auto stage = [&]() {                                     // registers -> shared memory (kAhead only)
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int c = threadIdx.x + u * kWarps * 32;
+      const int r = c / kChunksPerRow, cc = c % kChunksPerRow;
+      *reinterpret_cast<uint4*>(ks + r * kPitch + cc * 16) = nk[u];
+      *reinterpret_cast<uint4*>(vs + r * kPitch + cc * 16) = nv[u];
+    }
+  };
+  bool see[RPW];
+  bool cur = __syncthreads_or(visible(0, see)) != 0;       // every thread of the CTA votes on every tile
+  if (kAhead && cur) fetch(0);
+  for (int j0 = 0; j0 < p.L; j0 += 32) {
+    bool see_next[RPW];
+    const bool nxt = j0 + 32 < p.L && __syncthreads_or(visible(j0 + 32, see_next)) != 0;
+    if (cur) {
+      if constexpr (kAhead) stage(); else fetch(j0);
+      __syncthreads();
+    }
+    if (kAhead && nxt) fetch(j0 + 32);                     // in flight while this tile is used
+    if (!cur) {
+      cur = nxt;
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) see[i] = see_next[i];
+      continue;
+    }
     const T* kr = reinterpret_cast<const T*>(ks + lane * kPitch);
     const T* vr = reinterpret_cast<const T*>(vs + lane * kPitch);
 #pragma unroll
@@ -154,6 +195,9 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
       }
     }
     __syncthreads();                                       // the tile may be overwritten
+    cur = nxt;
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) see[i] = see_next[i];
   }
 #pragma unroll
   for (int i = 0; i < RPW; ++i) {
