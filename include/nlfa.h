@@ -208,10 +208,17 @@ int nlfa_head_gate_bwd(const void* g, const void* y, int y_dtype, const void* ga
  * Mask: window > 0 (needs causal): kpos <= qpos and (kpos > qpos - (window - sinks) or
  * kpos < sinks) (mixers.py:417-432; positions stay correct after cache eviction);
  * causal: kpos <= qpos (:433-437); neither: every key.  A row that sees no key gives
- * zeros and lse = -inf. */
+ * zeros and lse = -inf.
+ * `scratch` is optional: with nlfa_fwd_cached_scratch_bytes(...) bytes of device memory the
+ * keys are split over several CTAs when there are few query rows (long caches, small
+ * batches) and a second small kernel combines the partial rows in a fixed order; with
+ * NULL (or too little) one CTA walks all keys of its rows.  Same results up to fp32
+ * rounding. */
+size_t nlfa_fwd_cached_scratch_bytes(int B, int Tq, int H, int Hkv, int L, int D);
 int nlfa_fwd_cached(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
                     const int* qpos, const int* kpos, int B, int Tq, int H, int Hkv, int L, int D,
-                    float scale, int causal, int window, int sinks, int dtype, void* stream);
+                    float scale, int causal, int window, int sinks, int dtype, void* scratch,
+                    size_t scratch_bytes, void* stream);
 
 /* Bytes of device workspace `nlfa_selftest` needs. */
 size_t nlfa_selftest_workspace_bytes(void);

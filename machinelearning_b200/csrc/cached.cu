@@ -33,6 +33,10 @@ struct CachedParams {
   float scale;
   const int* qpos;   // nullptr: the block is the last Tq positions of a contiguous [0, L)
   const int* kpos;   // nullptr: contiguous
+  int splits;        // > 1: blockIdx.y walks its share of the key tiles and leaves a partial result
+  int tiles_per_split;
+  float* part_o;     // [rows][splits][D]: each split's own normalised output row
+  float* part_l;     // [rows][splits]: its base-2 logsumexp (-inf: the split saw no key)
 };
 
 template <int D> __host__ __device__ constexpr int rows_per_warp() { return D <= 64 ? 2 : 1; }
@@ -57,6 +61,9 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
   const int bh = blockIdx.x / chunks;
   const int hk = bh % p.Hkv, b = bh / p.Hkv;
   const float scale2 = p.scale * kLog2e;
+  const int j_begin = static_cast<int>(blockIdx.y) * p.tiles_per_split * 32;        // this CTA's keys
+  const int j_stop = j_begin + p.tiles_per_split * 32;
+  const int j_end = j_stop < p.L ? j_stop : p.L;
 
   int qp[RPW], lo[RPW];
   long long orow[RPW];                                     // row of q / o in [B,Tq,H]; -1: no such row
@@ -89,11 +96,11 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
   // Which rows of this warp see key j0 + lane; `any`: some row does.
   auto visible = [&](int j0, bool (&see)[RPW]) -> bool {
     const int j = j0 + lane;
-    const int kp = j < p.L ? (p.kpos ? p.kpos[j] : j) : 0;
+    const int kp = j < j_end ? (p.kpos ? p.kpos[j] : j) : 0;
     bool any = false;
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
-      see[i] = j < p.L && orow[i] >= 0;
+      see[i] = j < j_end && orow[i] >= 0;
       if (see[i]) {
         if (p.window > 0) see[i] = kp <= qp[i] && (kp > lo[i] || kp < p.sinks);
         else if (p.causal) see[i] = kp <= qp[i];
@@ -112,7 +119,7 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
     for (int u = 0; u < kPer; ++u) {
       const int c = threadIdx.x + u * kWarps * 32;
       const int r = c / kChunksPerRow, cc = c % kChunksPerRow;
-      if (j0 + r < p.L) {
+      if (j0 + r < j_end) {
         const long long src = static_cast<long long>(j0 + r) * kRowBytes + cc * 16;
         if constexpr (kAhead) {
           nk[u] = *reinterpret_cast<const uint4*>(kb + src);
@@ -134,11 +141,11 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
     }
   };
   bool see[RPW];
-  bool cur = __syncthreads_or(visible(0, see)) != 0;       // every thread of the CTA votes on every tile
-  if (kAhead && cur) fetch(0);
-  for (int j0 = 0; j0 < p.L; j0 += 32) {
+  bool cur = __syncthreads_or(visible(j_begin, see)) != 0;  // every thread of the CTA votes on every tile
+  if (kAhead && cur) fetch(j_begin);
+  for (int j0 = j_begin; j0 < j_end; j0 += 32) {
     bool see_next[RPW];
-    const bool nxt = j0 + 32 < p.L && __syncthreads_or(visible(j0 + 32, see_next)) != 0;
+    const bool nxt = j0 + 32 < j_end && __syncthreads_or(visible(j0 + 32, see_next)) != 0;
     if (cur) {
       if constexpr (kAhead) stage(); else fetch(j0);
       __syncthreads();
@@ -206,22 +213,52 @@ fwd_cached_kernel(CachedParams p, const T* __restrict__ q, const T* __restrict__
     for (int off = 16; off > 0; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;       // a row that sees no key gives zeros
     // add the lanes' partial rows: after the butterfly every lane holds every sum; lane d % 32 keeps d
-    float* stage = qs[wi * RPW + i];
+    float* out_row = qs[wi * RPW + i];
 #pragma unroll
     for (int d = 0; d < D; ++d) {
       float x = acc[i][d];
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-      if (lane == (d & 31)) stage[d] = x * inv;
+      if (lane == (d & 31)) out_row[d] = x * inv;
     }
     __syncwarp();
-    if (orow[i] >= 0) {
-      for (int d = lane; d < D; d += 32) o[orow[i] * D + d] = static_cast<T>(stage[d]);
+    if (orow[i] >= 0 && p.splits > 1) {                    // partial result; merge_splits_kernel finishes the row
+      const long long slot = orow[i] * p.splits + blockIdx.y;
+      for (int d = lane; d < D; d += 32) p.part_o[slot * D + d] = out_row[d];
+      if (lane == 0) p.part_l[slot] = lsum > 0.f ? m[i] + log2f(lsum) : -INFINITY;
+    } else if (orow[i] >= 0) {
+      for (int d = lane; d < D; d += 32) o[orow[i] * D + d] = static_cast<T>(out_row[d]);
       if (lse && lane == 0) {
         const long long t = (orow[i] / p.H) % p.Tq, h = orow[i] % p.H;
         lse[(static_cast<long long>(b) * p.H + h) * p.Tq + t] = lsum > 0.f ? (m[i] + log2f(lsum)) * kLn2 : -INFINITY;
       }
     }
+  }
+}
+
+// One warp per query row: the splits' partial rows, each normalised by its own sum, are combined with the
+// weights 2^(lse_s - max lse), in a fixed order.
+template <typename T, int D>
+__global__ void __launch_bounds__(kWarps * 32)
+merge_splits_kernel(CachedParams p, T* __restrict__ o, float* __restrict__ lse) {
+  const int lane = threadIdx.x & 31;
+  const long long row = static_cast<long long>(blockIdx.x) * kWarps + (threadIdx.x >> 5);    // over [B,Tq,H]
+  if (row >= static_cast<long long>(p.B) * p.Tq * p.H) return;
+  const float* pl = p.part_l + row * p.splits;
+  float mx = -INFINITY;
+  for (int s = 0; s < p.splits; ++s) mx = fmaxf(mx, pl[s]);
+  float wsum = 0.f;
+  for (int s = 0; s < p.splits; ++s) wsum += mx > -INFINITY ? exp2f(pl[s] - mx) : 0.f;
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  for (int d = lane; d < D; d += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < p.splits; ++s)
+      if (pl[s] > -INFINITY) acc = fmaf(exp2f(pl[s] - mx), p.part_o[(row * p.splits + s) * D + d], acc);
+    o[row * D + d] = static_cast<T>(acc * inv);
+  }
+  if (lse && lane == 0) {
+    const long long t = (row / p.H) % p.Tq, h = row % p.H, b = row / (static_cast<long long>(p.H) * p.Tq);
+    lse[(b * p.H + h) * p.Tq + t] = wsum > 0.f ? (mx + log2f(wsum)) * kLn2 : -INFINITY;
   }
 }
 
@@ -234,20 +271,45 @@ int launch_for_dim(const CachedParams& p, int D, const void* q, const void* k, c
     constexpr int rpc = kWarps * rows_per_warp<DD>();                                                    \
     const long long grid = static_cast<long long>(p.B) * p.Hkv * ((head_rows + rpc - 1) / rpc);          \
     if (grid >= (1ll << 31)) return NLFA_ERR_BAD_SHAPE;                                                  \
-    fwd_cached_kernel<T, DD><<<static_cast<unsigned>(grid), kWarps * 32, 0, st>>>(                        \
+    fwd_cached_kernel<T, DD><<<dim3(static_cast<unsigned>(grid), p.splits), kWarps * 32, 0, st>>>(        \
         p, (const T*)q, (const T*)k, (const T*)v, (T*)o, lse);                                           \
+    if (p.splits > 1) {                                                                                  \
+      const long long rows = static_cast<long long>(p.B) * p.Tq * p.H;                                   \
+      merge_splits_kernel<T, DD><<<static_cast<unsigned>((rows + kWarps - 1) / kWarps), kWarps * 32, 0, st>>>( \
+          p, (T*)o, lse);                                                                                \
+    }                                                                                                    \
   } while (0)
   if (D == 32) NLFA_GO(32); else if (D == 64) NLFA_GO(64); else NLFA_GO(128);
 #undef NLFA_GO
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
+// How many ways the keys are split: only when the row chunks alone leave most SMs idle.
+int choose_splits(int B, int Tq, int H, int Hkv, int L, int D) {
+  const long long rpc = kWarps * (D <= 64 ? 2 : 1);
+  const long long base = static_cast<long long>(B) * Hkv * ((static_cast<long long>(Tq) * (H / Hkv) + rpc - 1) / rpc);
+  const long long tiles = (L + 31) / 32;
+  if (base <= 0 || base >= 296 || tiles < 8) return 1;
+  long long s = (592 + base - 1) / base;
+  if (s > tiles / 4) s = tiles / 4;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : static_cast<int>(s);
+}
+
 }  // namespace
 }  // namespace nlfa
 
+extern "C" size_t nlfa_fwd_cached_scratch_bytes(int B, int Tq, int H, int Hkv, int L, int D) {
+  if (B <= 0 || Tq <= 0 || H <= 0 || Hkv <= 0 || L <= 0 || H % Hkv != 0) return 0;
+  const int s = nlfa::choose_splits(B, Tq, H, Hkv, L, D);
+  if (s <= 1) return 0;
+  return static_cast<size_t>(B) * Tq * H * s * (static_cast<size_t>(D) + 1) * sizeof(float);
+}
+
 extern "C" int nlfa_fwd_cached(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
                                const int* qpos, const int* kpos, int B, int Tq, int H, int Hkv, int L, int D,
-                               float scale, int causal, int window, int sinks, int dtype, void* stream) {
+                               float scale, int causal, int window, int sinks, int dtype, void* scratch,
+                               size_t scratch_bytes, void* stream) {
   using namespace nlfa;
   if (B < 0 || Tq < 0 || H < 0 || L < 0 || Hkv <= 0 || H % Hkv != 0 || !(scale == scale)) return NLFA_ERR_BAD_SHAPE;
   if (D != 32 && D != 64 && D != 128) return NLFA_ERR_BAD_HEAD_DIM;
@@ -260,7 +322,14 @@ extern "C" int nlfa_fwd_cached(const void* q, const void* k_cache, const void* v
   if (rows == 0) return NLFA_OK;
   if (rows / 4 >= (1ll << 31)) return NLFA_ERR_BAD_SHAPE;
   if (!q || !o || (L > 0 && (!k_cache || !v_cache))) return NLFA_ERR_NULL_POINTER;
-  CachedParams p{B, Tq, H, Hkv, L, causal ? 1 : 0, window, sinks, scale, qpos, kpos};
+  CachedParams p{B, Tq, H, Hkv, L, causal ? 1 : 0, window, sinks, scale, qpos, kpos, 1, (L + 31) / 32, nullptr, nullptr};
+  const size_t need = nlfa_fwd_cached_scratch_bytes(B, Tq, H, Hkv, L, D);
+  if (need > 0 && scratch != nullptr && scratch_bytes >= need) {     // without scratch: one CTA walks all keys
+    p.splits = choose_splits(B, Tq, H, Hkv, L, D);
+    p.tiles_per_split = ((L + 31) / 32 + p.splits - 1) / p.splits;
+    p.part_o = static_cast<float*>(scratch);
+    p.part_l = p.part_o + rows * p.splits * D;
+  }
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == NLFA_DTYPE_BF16) return launch_for_dim<__nv_bfloat16>(p, D, q, k_cache, v_cache, o, lse, st);
   if (dtype == NLFA_DTYPE_F16) return launch_for_dim<__half>(p, D, q, k_cache, v_cache, o, lse, st);

@@ -325,12 +325,15 @@ def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tenso
     q, k_full, v_full = q.detach().contiguous(), k_full.detach().contiguous(), v_full.detach().contiguous()
     o = torch.empty_like(q)
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device) if return_lse else None
+    nbytes = lib.nlfa_fwd_cached_scratch_bytes(B, T, H, Hkv, L, D)      # > 0: the keys are split over CTAs
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
     with torch.cuda.device(q.device):
         st = lib.nlfa_fwd_cached(q.data_ptr(), k_full.data_ptr(), v_full.data_ptr(), o.data_ptr(),
                                  None if lse is None else lse.data_ptr(),
                                  None if qp is None else qp.data_ptr(), None if kp is None else kp.data_ptr(),
                                  B, T, H, Hkv, L, D, float(scale), int(bool(causal)), int(window), int(sinks),
-                                 _DTYPE_CODE[q.dtype], torch.cuda.current_stream().cuda_stream)
+                                 _DTYPE_CODE[q.dtype], None if scratch is None else scratch.data_ptr(), nbytes,
+                                 torch.cuda.current_stream().cuda_stream)
     _lib.check("nlfa_fwd_cached", st)
     return (o, lse) if return_lse else o
 

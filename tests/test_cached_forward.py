@@ -40,7 +40,7 @@ def test_entry_point_refuses_bad_arguments_before_any_launch():
     f = _lib.load().nlfa_fwd_cached
     args = lambda **kw: [kw.get("q", 16), 16, 16, 16, None, None, None, kw.get("B", 1), kw.get("T", 4), kw.get("H", 4),
                          kw.get("Hkv", 2), kw.get("L", 8), kw.get("D", 64), 0.125, kw.get("causal", 1),
-                         kw.get("window", 0), kw.get("sinks", 0), kw.get("dtype", 2), None]
+                         kw.get("window", 0), kw.get("sinks", 0), kw.get("dtype", 2), None, 0, None]
     assert f(*args(D=48)) == 4
     assert f(*args(dtype=7)) == 3
     assert f(*args(Hkv=3)) == 2
@@ -49,6 +49,9 @@ def test_entry_point_refuses_bad_arguments_before_any_launch():
     assert f(*args(T=9, L=8)) == 2                    # contiguous default: the block is part of the keys
     assert f(*args(q=None)) == 1
     assert f(*args(B=0)) == 0
+    sb = _lib.load().nlfa_fwd_cached_scratch_bytes
+    assert sb(8, 32, 12, 4, 1056, 64) == 0                      # enough row chunks: no split
+    assert sb(1, 64, 16, 16, 16448, 128) == 64 * 16 * 3 * 129 * 4      # three splits of a long cache
 
 
 def test_python_wrapper_rejects_cpu_tensors_and_bidirectional_windows():
@@ -102,3 +105,36 @@ def test_decode_sized_block_with_default_positions_and_an_unseen_row(D):
                                           return_lse=True)
     assert torch.count_nonzero(y[:, 0]).item() == 0 and torch.isinf(lse[:, :, 0]).all()
     assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.gpu
+def test_key_split_and_single_walk_agree():
+    """A long cache with few query rows takes the key split (scratch given); without scratch one CTA walks
+    all keys.  Same rows either way, up to fp32 rounding of the combination."""
+    from machinelearning_b200 import _lib, flash_cuda
+    assert flash_cuda.is_available(), flash_cuda.unavailable_reason()
+    lib = _lib.load()
+    B, T, H, Hkv, L, D = 1, 16, 4, 2, 4000, 64
+    nbytes = lib.nlfa_fwd_cached_scratch_bytes(B, T, H, Hkv, L, D)
+    assert nbytes > 0
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(B, T, H, D, generator=g).bfloat16().cuda()
+    k = torch.randn(B, Hkv, L, D, generator=g).bfloat16().cuda()
+    v = torch.randn(B, Hkv, L, D, generator=g).bfloat16().cuda()
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    outs = []
+    for ptr, size in ((scratch.data_ptr(), nbytes), (None, 0)):
+        o = torch.empty_like(q)
+        lse = torch.empty(B, H, T, device="cuda")
+        st = lib.nlfa_fwd_cached(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), None, None,
+                                 B, T, H, Hkv, L, D, 0.125, 1, 0, 0, _lib.DTYPE_BF16, ptr, size,
+                                 torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        outs.append((o.float(), lse))
+    (o1, l1), (o2, l2) = outs
+    assert (o1 - o2).abs().max().item() <= 1e-2 * o2.abs().max().item()
+    assert (l1 - l2).abs().max().item() <= 1e-4
+    ref, lse_ref = cached_f64.forward(q.double().cpu().numpy(), k.double().cpu().numpy(), v.double().cpu().numpy(),
+                                      0.125, np.arange(L - T, L), np.arange(L), True)
+    assert np.abs(o1.double().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max()
+    assert np.abs(l1.double().cpu().numpy() - lse_ref).max() <= 1e-3
