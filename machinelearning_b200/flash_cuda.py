@@ -369,6 +369,52 @@ def _bench_once(fn, iters: int, warmup: int = 5) -> float:
     return statistics.median(times)
 
 
+def _cached_check(args) -> int:
+    """``--cached BLOCK``: the KV-cached block forward against what ``forward_cached`` does today
+    (``nanolab/mixers.py:401-460``: ``torch.cat`` of cache and block, ``repeat_interleave``, a boolean mask,
+    SDPA), causal block, same GPU."""
+    import torch.nn.functional as F
+    dtype = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[args.dtype]
+    B, L, H, Hkv, D, T = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim, args.cached
+    w, s = args.window, args.sinks
+    torch.manual_seed(0)
+    q = torch.randn(B, T, H, D, device="cuda", dtype=dtype)
+    k = torch.randn(B, Hkv, L, D, device="cuda", dtype=dtype)
+    v = torch.randn_like(k)
+    ck, cv, kt, vt = (t.contiguous() for t in (k[:, :, :L - T], v[:, :, :L - T], k[:, :, L - T:], v[:, :, L - T:]))
+    apos, kpos = torch.arange(L - T, L, device="cuda"), torch.arange(L, device="cuda")
+    scale = 1.0 / math.sqrt(D)
+
+    def nanolab_way():
+        kf, vf = torch.cat([ck, kt], 2), torch.cat([cv, vt], 2)
+        if w:
+            keep = (kpos[None, :] <= apos[:, None]) & ((kpos[None, :] > apos[:, None] - (w - s)) | (kpos[None, :] < s))
+        else:
+            keep = torch.cat([torch.ones(T, L - T, dtype=torch.bool, device="cuda"),
+                              torch.tril(torch.ones(T, T, dtype=torch.bool, device="cuda"))], 1)
+        rep = H // Hkv
+        if rep > 1:
+            kf, vf = kf.repeat_interleave(rep, 1), vf.repeat_interleave(rep, 1)
+        y = F.scaled_dot_product_attention(q.transpose(1, 2), kf, vf, attn_mask=keep[None, None], scale=scale)
+        return y.transpose(1, 2).contiguous()
+
+    def kernel_with_cat():
+        return flash_attn_cached(q, torch.cat([ck, kt], 2), torch.cat([cv, vt], 2), scale, causal=True,
+                                 window=w, sinks=s)
+
+    def kernel_only():
+        return flash_attn_cached(q, k, v, scale, causal=True, window=w, sinks=s)
+
+    err = (kernel_only().float() - nanolab_way().float()).abs().max().item()
+    print(f"block {T} over {L} keys, B{B} H{H}/{Hkv} D{D} {args.dtype} window {w} sinks {s}: max |diff| {err:.3e}")
+    kv_bytes = 2 * k.numel() * k.element_size()
+    for name, fn in (("cat + repeat + mask + SDPA", nanolab_way), ("cat + flash_attn_cached", kernel_with_cat),
+                     ("flash_attn_cached", kernel_only)):
+        ms = _bench_once(fn, args.iters)
+        print(f"  {name:28s} {ms * 1e3:9.1f} us   {kv_bytes / ms / 1e6:8.0f} GB/s of K, V")
+    return 0
+
+
 def main() -> int:
     """Correctness against SDPA, then a speed comparison (reference: ``:315-379``)."""
     import argparse
@@ -381,6 +427,11 @@ def main() -> int:
     p.add_argument("--head_dim", type=int, default=64)
     p.add_argument("--dtype", default="bf16", choices=("fp32", "fp16", "bf16"))
     p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--cached", type=int, default=0, metavar="BLOCK",
+                   help="instead: a BLOCK-token active block over --seq keys through flash_attn_cached, "
+                        "against nanolab's cat + repeat_interleave + masked SDPA")
+    p.add_argument("--window", type=int, default=0)
+    p.add_argument("--sinks", type=int, default=0)
     args = p.parse_args()
 
     if not torch.cuda.is_available():
@@ -389,6 +440,8 @@ def main() -> int:
     if not is_available():
         print(f"library unavailable: {unavailable_reason()}")
         return 1
+    if args.cached:
+        return _cached_check(args)
 
     dtype = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[args.dtype]
     B, T, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
