@@ -68,3 +68,59 @@ def test_random_configuration_matches_the_oracle(i, B, T, H, Hkv, D, window, sin
             assert rel(got, want) <= 2e-2
     for t in (o, lse, dq, dk, dv):
         assert torch.isfinite(t.float()).all()
+
+
+def _aux_configs(n=24, seed=977):
+    rng = random.Random(seed)
+    out = []
+    for i in range(n):
+        D = rng.choice([32, 64, 128])
+        out.append((i, rng.choice([1, 2, 3]), rng.choice([1, 2, 7, 33, 100, 257]), rng.choice([1, 2, 3, 5, 12]), D,
+                    rng.choice([torch.float32, torch.bfloat16, torch.float16])))
+    return out
+
+
+AUX = _aux_configs()
+
+
+@pytest.mark.parametrize("i,B,T,H,D,dtype", AUX, ids=[f"{c[0]}-B{c[1]}T{c[2]}H{c[3]}D{c[4]}-{str(c[5])[6:]}" for c in AUX])
+def test_random_prologue_blend_and_gate_match_their_oracles(i, B, T, H, D, dtype):
+    """The elementwise kernels either side of the core on drawn shapes (row counts that do not fill a
+    warp's row groups, one-row tensors, every head dim): fp32 2e-5 max-abs scaled by the reference's
+    magnitude, 16-bit 2e-2 relative with the denominator floored at 1e-2."""
+    from machinelearning_b200 import qk_prologue, value_gate
+    from oracle import epilogue_f64, prologue_f64
+    g = torch.Generator().manual_seed(500 + i)
+    r = lambda *s: torch.randn(*s, generator=g).to(dtype).cuda()
+    np_ = lambda t: t.detach().double().cpu().numpy()
+
+    def close(got, want):
+        err = np.abs(np_(got) - want).max()
+        if dtype == torch.float32:
+            return err <= 2e-5 * max(1.0, np.abs(want).max())
+        return err <= 2e-2 * max(np.abs(want).max(), 1e-2)
+
+    x, gy = r(B, T, H, D).requires_grad_(), r(B, T, H, D)
+    w = (1 + 0.2 * torch.randn(D, generator=g)).cuda().requires_grad_()
+    cos64, sin64 = prologue_f64.rope_tables(T, D)
+    cos, sin = (torch.from_numpy(t).float().cuda() for t in (cos64, sin64))
+    y = qk_prologue.qk_prologue(x, w, cos, sin, out_dtype=dtype)
+    y.backward(gy)
+    ref_y, _ = prologue_f64.forward(np_(x), np_(w), cos64, sin64)
+    ref_dx, ref_dw = prologue_f64.backward(np_(gy), np_(x), np_(w), cos64, sin64)
+    assert close(y, ref_y) and close(x.grad, ref_dx)
+    assert np.abs(np_(w.grad) - ref_dw).max() <= (1e-4 if dtype == torch.float32 else 3e-2) * max(np.abs(ref_dw).max(), 1.0)
+
+    v, v0, gv = r(B, T, H, D).requires_grad_(), r(B, T, H, D).requires_grad_(), r(B, T, H, D)
+    lam = torch.tensor([-0.4], device="cuda", requires_grad=True)
+    out = value_gate.value_blend(v, v0, lam, out_dtype=dtype)
+    out.backward(gv)
+    dv, dv0, dl = epilogue_f64.blend_backward(np_(gv), np_(v), np_(v0), -0.4)
+    assert close(out, epilogue_f64.blend_forward(np_(v), np_(v0), -0.4)) and close(v.grad, dv) and close(v0.grad, dv0)
+    assert abs(lam.grad.item() - dl) <= (1e-4 if dtype == torch.float32 else 3e-2) * max(1.0, abs(dl))
+
+    yy, gate, go = r(B, T, H, D).requires_grad_(), r(B, T, H).requires_grad_(), r(B, T, H, D)
+    o = value_gate.head_gate(yy, gate)
+    o.backward(go)
+    dy, dg = epilogue_f64.gate_backward(np_(go), np_(yy), np_(gate))
+    assert close(o, epilogue_f64.gate_forward(np_(yy), np_(gate))) and close(yy.grad, dy) and close(gate.grad, dg)
