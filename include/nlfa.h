@@ -56,6 +56,8 @@ extern "C" {
 #define NLFA_ERR_SCRATCH_TOO_SMALL 11
 #define NLFA_ERR_SELFTEST_MISMATCH 12
 #define NLFA_ERR_STATIC_SCRATCH_EXCEEDED 13
+#define NLFA_ERR_BAD_ARGUMENT 14
+#define NLFA_ERR_GRAPH_SLOTS 15
 
 /* Library version, bumped when the ABI changes. */
 int nlfa_version(void);
@@ -129,8 +131,8 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
  *    wrote; every call rewrites all rows it later reads, so nothing has to be
  *    cleared.  Two calls whose kernels can overlap on the GPU (different
  *    streams, no dependency) race on it: serialise them.
- *  - Neither this function nor anything it calls uses cudaMalloc, cudaFree or
- *    an allocating library routine.
+ *  - Neither this function nor anything it calls uses cudaMalloc or an allocating
+ *    library routine, and nothing is freed.
  * Arguments, results and gradients are exactly those of nlfa_bwd. */
 size_t nlfa_static_scratch_max_rows(void);
 int nlfa_bwd_static_scratch(const void* dout, const void* q, const void* k, const void* v,
@@ -257,8 +259,41 @@ int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows);
 
 /* Reads (and clears) the device status word that bounded waits inside the
  * kernels write when they give up.  Synchronises the device.  Returns NLFA_OK
- * or NLFA_ERR_DEVICE_TIMEOUT; *raw receives the raw word when raw != NULL. */
+ * or NLFA_ERR_DEVICE_TIMEOUT; *raw receives the raw word when raw != NULL.
+ * Clearing also zeroes the registered host copy (below) and re-arms the
+ * persistent kernels' work counters.
+ *
+ * Error contract of the tensor-core kernels.  Every wait inside them is bounded
+ * (2 s).  A wait that runs out records a code in the status word, its CTA
+ * leaves cleanly, and every CTA and launch that starts while the word is set
+ * does nothing: outputs of such launches are NOT written.  The reference fails
+ * closed in the same spirit (nanolab/flash_cuda.py:91-135 never raises and
+ * records the reason; nanolab/mixers.py:365-370 falls back with one warning). */
 int nlfa_device_status(unsigned* raw);
+
+/* Registers a host-resident copy of the status word for the current device, so
+ * that a give-up is seen without synchronising.  `host_word` must be page-locked
+ * host memory the device can write (cudaHostAlloc / cudaHostRegister with
+ * mapping, torch's pin_memory), owned by the caller for as long as it stays
+ * registered; NULL unregisters.  The kernel that gives up writes its code there
+ * as well, and from then on nlfa_fwd, nlfa_bwd, nlfa_bwd_passes and
+ * nlfa_bwd_static_scratch refuse tensor-core launches on that device with
+ * NLFA_ERR_DEVICE_TIMEOUT until nlfa_device_status has cleared the word.
+ * Synchronises the device (it is a set-up call).  No counterpart in the
+ * reference. */
+int nlfa_set_status_mirror(unsigned* host_word);
+
+/* NLFA_ERR_DEVICE_TIMEOUT if the registered host copy shows a give-up on the
+ * current device, else NLFA_OK.  A plain host memory read: no CUDA call. */
+int nlfa_peek_status(void);
+
+/* Test hook for the error contract: launches one CTA that waits, with
+ * `limit_ns` (at most the kernels' own limit) instead of the built-in one, on a
+ * barrier that nothing ever arrives at.  The wait runs out, the CTA records
+ * the give-up exactly as the attention kernels would, and the kernel returns;
+ * nothing traps, faults or spins without a limit.  No counterpart in the
+ * reference. */
+int nlfa_test_wait_timeout(unsigned long long limit_ns, void* stream);
 
 #ifdef __cplusplus
 }

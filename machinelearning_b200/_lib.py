@@ -59,6 +59,9 @@ SIGNATURES = {
     "nlfa_selftest_tiles": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6),
     "nlfa_check_mask_geometry": (_c_int, [_c_int] * 4),
     "nlfa_device_status": (_c_int, [ctypes.POINTER(ctypes.c_uint)]),
+    "nlfa_set_status_mirror": (_c_int, [_c_void_p]),
+    "nlfa_peek_status": (_c_int, []),
+    "nlfa_test_wait_timeout": (_c_int, [ctypes.c_ulonglong, _c_void_p]),
 }
 
 _lib = None

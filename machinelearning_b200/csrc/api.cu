@@ -1,36 +1,82 @@
 // C-ABI entry points: argument validation, path selection, tensor-map encoding,
 // the device status word, and the host half of the self-test.
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace nlfa {
 
-// Written by bounded waits inside the kernels when they give up.
-__device__ unsigned g_status_word;
+// The status block bounded waits write when they give up: word [0] is the status, words
+// [2..3] hold the device-visible address of the host's copy (ptx.cuh, report_timeout).
+__device__ __align__(16) unsigned g_status_block[4];
+
+// Work counters of the persistent kernels' in-kernel schedulers, two per launch.
+constexpr unsigned kEagerSlots = 1024;       // ring for ordinary launches
+constexpr unsigned kGraphSlots = 15360;      // handed out once each to launches under capture
+__device__ unsigned g_sched[kEagerSlots + kGraphSlots][2];
 
 namespace {
 
 constexpr int kMaxDevices = 64;
+std::mutex g_host_mutex;                     // guards the per-device tables below
 unsigned* g_status_ptr[kMaxDevices];
+unsigned* g_status_mirror[kMaxDevices];      // host address of the registered copy, or null
+unsigned* g_sched_ptr[kMaxDevices];
+int g_sm_count[kMaxDevices];
+std::atomic<unsigned> g_next_eager{0};
+std::atomic<unsigned> g_next_graph{0};
 
-// Device address of the status word on the current device (looked up once per device).
-unsigned* status_word() {
+int current_device() {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+// Device address of the status block on the current device (looked up once per device).
+unsigned* status_word() {
+  const int dev = current_device();
+  if (dev < 0) return nullptr;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
   if (g_status_ptr[dev] == nullptr) {
     void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_status_word) != cudaSuccess) return nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_status_block) != cudaSuccess) return nullptr;
     g_status_ptr[dev] = static_cast<unsigned*>(ptr);
   }
   return g_status_ptr[dev];
+}
+
+// The host's copy of the status word for the current device: non-zero once a wait has given up.
+unsigned host_status() {
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  const unsigned* m = g_status_mirror[dev];
+  return m ? *reinterpret_cast<const volatile unsigned*>(m) : 0u;
+}
+
+// One CTA waits on a barrier nobody arrives at, with the caller's limit.
+__global__ void wait_timeout_kernel(unsigned* status, unsigned long long limit_ns) {
+  __shared__ unsigned long long barrier;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&barrier), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const WaitCtxLimit wctx{&abort_flag, status, limit_ns};
+  if (threadIdx.x == 0) (void)mbar_wait(smem_u32(&barrier), 0, wctx, 0xee);
+  __syncthreads();
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -91,11 +137,32 @@ uint16_t float_to_bits(float x, int dtype) {
 
 }  // namespace
 
-int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, int heads, int D,
-                  int rows) {
+namespace {
+
+struct MapKey {
+  const void* base;
+  int dtype, B, T, heads, D, rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && dtype == o.dtype && B == o.B && T == o.T && heads == o.heads &&
+           D == o.D && rows == o.rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9e3779b97f4a7c15ull;
+    auto mix = [&h](int v) { h = (h ^ static_cast<size_t>(v)) * 0x100000001b3ull; };
+    mix(k.dtype); mix(k.B); mix(k.T); mix(k.heads); mix(k.D); mix(k.rows);
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+std::mutex g_maps_mutex;
+constexpr size_t kMaxCachedMaps = 4096;
+
+int encode_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, int heads, int D,
+                    int rows) {
   EncodeTiledFn fn = encode_tiled();
   if (fn == nullptr) return NLFA_ERR_CUDA;
-  if (!aligned16(base)) return NLFA_ERR_MISALIGNED;
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(heads),
                               static_cast<cuuint64_t>(T), static_cast<cuuint64_t>(B)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(D) * 2,
@@ -111,13 +178,92 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, i
   if (r != CUDA_SUCCESS) {
     // The encoder is a driver entry point and wants a context current on the calling thread.  A
     // host thread that has made no runtime call yet (an autograd worker, say) has none: a
-    // runtime call binds the device's primary context, then the encoding is tried once more.
-    (void)cudaFree(nullptr);
+    // runtime call that needs the context binds the device's primary one, then the encoding
+    // is tried once more.
+    int dev = 0, attr = 0;
+    (void)cudaGetDevice(&dev);
+    (void)cudaDeviceGetAttribute(&attr, cudaDevAttrMultiProcessorCount, dev);
+    size_t free_b = 0, total_b = 0;
+    (void)cudaMemGetInfo(&free_b, &total_b);
     r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }
   return r == CUDA_SUCCESS ? NLFA_OK : NLFA_ERR_CUDA;
+}
+
+}  // namespace
+
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, int heads, int D,
+                  int rows) {
+  if (!aligned16(base)) return NLFA_ERR_MISALIGNED;
+  const MapKey key{base, dtype, B, T, heads, D, rows};
+  {
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *map = it->second;
+      return NLFA_OK;
+    }
+  }
+  const int st = encode_tile_map(map, base, dtype, B, T, heads, D, rows);
+  if (st != NLFA_OK) return st;
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  if (g_maps.size() >= kMaxCachedMaps) g_maps.clear();
+  g_maps.emplace(key, *map);
+  return NLFA_OK;
+}
+
+int sched_counters(cudaStream_t stream, unsigned** out) {
+  const int dev = current_device();
+  if (dev < 0) return NLFA_ERR_CUDA;
+  unsigned* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_host_mutex);
+    if (g_sched_ptr[dev] == nullptr) {
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_sched) != cudaSuccess) return NLFA_ERR_CUDA;
+      g_sched_ptr[dev] = static_cast<unsigned*>(ptr);
+    }
+    base = g_sched_ptr[dev];
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) return NLFA_ERR_CUDA;
+  if (cap == cudaStreamCaptureStatusNone) {
+    *out = base + 2 * (g_next_eager.fetch_add(1u, std::memory_order_relaxed) % kEagerSlots);
+    return NLFA_OK;
+  }
+  const unsigned slot = g_next_graph.fetch_add(1u, std::memory_order_relaxed);
+  if (slot >= kGraphSlots) return NLFA_ERR_GRAPH_SLOTS;   // every slot is bound into some captured graph
+  *out = base + 2 * (kEagerSlots + slot);
+  return NLFA_OK;
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mutex;
+  static std::unordered_map<const void*, unsigned long long> done;   // kernel -> device bit mask
+  const int dev = current_device();
+  if (dev < 0) return NLFA_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(mutex);
+  unsigned long long& mask = done[kernel];
+  if (mask & (1ull << dev)) return NLFA_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+    return NLFA_ERR_CUDA;
+  mask |= 1ull << dev;
+  return NLFA_OK;
+}
+
+int sm_count() {
+  const int dev = current_device();
+  if (dev < 0) return 1;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 1;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
 }
 
 }  // namespace nlfa
@@ -143,6 +289,9 @@ const char* nlfa_strerror(int status) {
     case NLFA_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel gave up";
     case NLFA_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small";
     case NLFA_ERR_SELFTEST_MISMATCH: return "tensor-core self-test disagrees with the host reference";
+    case NLFA_ERR_BAD_ARGUMENT: return "bad argument";
+    case NLFA_ERR_GRAPH_SLOTS:
+      return "no scheduler counters left for launches under stream capture (15360 per process)";
     case NLFA_ERR_STATIC_SCRATCH_EXCEEDED:
       return "problem too large for the built-in scratch array (need B*H*T <= 1048576)";
   }
@@ -190,6 +339,7 @@ int nlfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (resolved == NLFA_PATH_SIMT) return launch_fwd_simt(p, q, k, v, o, lse, s);
   if (!nlfa_device_supported()) return NLFA_ERR_NOT_SM100;
+  if (host_status() != 0) return NLFA_ERR_DEVICE_TIMEOUT;   // an earlier kernel gave up: refuse until cleared
   unsigned* status = status_word();
   if (!status) return NLFA_ERR_CUDA;
   return launch_fwd_tc(p, q, k, v, o, lse, status, s);
@@ -234,6 +384,7 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
   if (resolved == NLFA_PATH_SIMT)
     return launch_bwd_simt(p, dout, q, k, v, o, lse, dq, dk, dv, delta, passes, s);
   if (!nlfa_device_supported()) return NLFA_ERR_NOT_SM100;
+  if (host_status() != 0) return NLFA_ERR_DEVICE_TIMEOUT;   // an earlier kernel gave up: refuse until cleared
   unsigned* status = status_word();
   if (!status) return NLFA_ERR_CUDA;
   return launch_bwd_tc(p, dout, q, k, v, o, lse, dq, dk, dv, delta, passes, status, s);
@@ -381,11 +532,52 @@ int nlfa_device_status(unsigned* raw) {
   if (cudaMemcpy(&word, ptr, sizeof(word), cudaMemcpyDeviceToHost) != cudaSuccess)
     return NLFA_ERR_CUDA;
   if (word != 0) {
+    // Clear the word, the host's copy, and the schedulers' work counters (kernels that left
+    // early did not re-arm theirs).  The device is idle: it was synchronised above.
     const unsigned zero = 0;
     cudaMemcpy(ptr, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+    const int dev = current_device();
+    if (dev >= 0 && g_status_mirror[dev]) *reinterpret_cast<volatile unsigned*>(g_status_mirror[dev]) = 0u;
+    void* sched = nullptr;
+    if (cudaGetSymbolAddress(&sched, g_sched) == cudaSuccess) cudaMemset(sched, 0, sizeof(g_sched));
   }
   if (raw) *raw = word;
   return word == 0 ? NLFA_OK : NLFA_ERR_DEVICE_TIMEOUT;
+}
+
+int nlfa_peek_status(void) {
+  return host_status() != 0 ? NLFA_ERR_DEVICE_TIMEOUT : NLFA_OK;
+}
+
+int nlfa_set_status_mirror(unsigned* host_word) {
+  unsigned* ptr = status_word();
+  const int dev = current_device();
+  if (!ptr || dev < 0) return NLFA_ERR_CUDA;
+  unsigned long long dev_addr = 0;
+  if (host_word != nullptr) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host_word) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return NLFA_ERR_BAD_ARGUMENT;
+    }
+    if (attr.type != cudaMemoryTypeHost || attr.devicePointer == nullptr) return NLFA_ERR_BAD_ARGUMENT;
+    dev_addr = reinterpret_cast<unsigned long long>(attr.devicePointer);
+    *reinterpret_cast<volatile unsigned*>(host_word) = 0u;
+  }
+  if (cudaDeviceSynchronize() != cudaSuccess) return NLFA_ERR_CUDA;
+  if (cudaMemcpy(ptr + 2, &dev_addr, sizeof(dev_addr), cudaMemcpyHostToDevice) != cudaSuccess)
+    return NLFA_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+  g_status_mirror[dev] = host_word;
+  return NLFA_OK;
+}
+
+int nlfa_test_wait_timeout(unsigned long long limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > WAIT_LIMIT_NS) return NLFA_ERR_BAD_ARGUMENT;
+  unsigned* status = status_word();
+  if (!status) return NLFA_ERR_CUDA;
+  wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_ns);
+  return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
 
 }  // extern "C"

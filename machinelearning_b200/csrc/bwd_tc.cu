@@ -28,7 +28,6 @@
 // operands of the output products live in columns of their own behind the outputs.
 // YR is 128 at D = 64 and 64 at D = 128, where shared memory would hold only two
 // stages of 128-row tiles (one load in flight) and TMEM no separate P / dS columns.
-#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -36,27 +35,6 @@
 
 namespace nlfa {
 
-#ifdef NLFA_TRACE
-// Debug-only timeline of CTA 0: (clock64, tag) pairs per role, staged in shared memory.
-__device__ long long g_btrace[4][1024];
-__device__ int g_btrace_n[4];
-#define NLFA_BTRACE(role, tag)                                        \
-  do {                                                                \
-    if (blockIdx.x == 0 && tr_n < 256) {                              \
-      tr_buf[((role) * 256 + tr_n) * 2] = clock64();                  \
-      tr_buf[((role) * 256 + tr_n) * 2 + 1] = (tag);                  \
-      ++tr_n;                                                         \
-      g_btrace_n[role] = tr_n;                                        \
-    }                                                                 \
-  } while (0)
-#else
-#define NLFA_BTRACE(role, tag)
-#endif
-
-// Work counters for the in-kernel scheduler: [slot][0] next unit, [slot][1] CTAs
-// finished.  The last CTA of a launch to finish zeroes its slot again.
-constexpr int kSchedSlots = 256;
-__device__ unsigned g_bwd_sched[kSchedSlots][2];
 
 namespace {
 
@@ -94,12 +72,7 @@ struct BwdSmem {
   static constexpr int kTmemSlot = kSched + 32 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
-#ifdef NLFA_TRACE
-  static constexpr int kTrace = (kTotal + 15) / 16 * 16;
-  static constexpr int kDynamic = kTrace + 4 * 256 * 16 + 1024;
-#else
   static constexpr int kDynamic = kTotal + 1024;
-#endif
 };
 
 // One work unit: a stationary tile and the list of streamed tiles it meets.
@@ -185,10 +158,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
   uint8_t* gen = smem_raw + (base - raw);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-#ifdef NLFA_TRACE
-  long long* tr_buf = reinterpret_cast<long long*>(gen + L::kTrace);
-  int tr_n = 0;
-#endif
 
   auto bar = [&](int i) -> uint32_t { return base + L::kBar + 8u * i; };
   constexpr int X_FULL = 0, X_EMPTY = XBUF, T_FULL = 2 * XBUF, T_CONSUMED = T_FULL + 1,
@@ -519,7 +488,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
           if (ok) {
             tc_fence_after();
             issue_t(nxt_xb, g + 1);
-            if (leader) NLFA_BTRACE(2, 20);
           }
         };
         // The next iteration's T products go first, also across a unit boundary, so that the
@@ -529,9 +497,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         const bool early = kSep && have_next && (!crossed || XBUF > 1);
         if (early) issue_next_t();
         if (!ok) break;
-        if (leader) NLFA_BTRACE(2, 10);
         if (!(ok = wait_all(bar(PD_FULL), g & 1, 34))) break;
-        if (leader) NLFA_BTRACE(2, 11);
         tc_fence_after();
         // a unit's first output product overwrites the accumulators: the epilogue warps must
         // have pulled the previous unit's out of TMEM
@@ -624,7 +590,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         if (inner == w.n_inner) inner = 0;
         const int s = g % STAGES;
         const int idx = w.streamed_index(inner);
-        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 1);
         if (MODE == MODE_DQ && it + 1 == w.n_iters) {
           // The next unit's row statistics are requested now (its descriptor is published well
           // ahead), so that their memory latency passes during this unit's last iteration.
@@ -643,7 +608,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 2);
 
         uint32_t sv[kCh][32], dv[kCh][32];
 #pragma unroll
@@ -653,7 +617,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         tc_wait_ld();
         tc_fence_before();
         mbar_arrive(bar(T_CONSUMED));
-        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 3);
 
         // positions of the (stationary tile) x (streamed tile) rectangle
         const int q_lo = MODE == MODE_DQ ? w.tile * kTile : idx * YR;
@@ -777,7 +740,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         } else {
           each_chunk([&](auto ch_c) { chunk(ch_c); });
         }
-        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 4);
         // the previous iteration's output products must be done reading P / dS
         wait_out(g);
         if (!ok) break;
@@ -791,7 +753,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(PD_FULL));
-        if ((threadIdx.x & 127) == 0) NLFA_BTRACE(half, 5);
       }
       if (!ok) break;
 
@@ -806,10 +767,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
-#ifdef NLFA_TRACE
-  if (blockIdx.x == 0)
-    for (int i = threadIdx.x; i < 4 * 512; i += blockDim.x) (&g_btrace[0][0])[i] = tr_buf[i];
-#endif
   // scheduler bookkeeping: the last CTA of the launch to get here re-arms the counters
   if (threadIdx.x == 0) {
     __threadfence();
@@ -820,34 +777,6 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
       __threadfence();
     }
   }
-}
-
-int sm_count_bwd() {
-  static int cached[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 1;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
-// Device address of a fresh pair of scheduler counters on the current device.
-unsigned* sched_slot() {
-  static unsigned* base[64];
-  static std::atomic<unsigned> next_slot{0};   // launches may come from several host threads
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (base[dev] == nullptr) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_bwd_sched) != cudaSuccess) return nullptr;
-    base[dev] = static_cast<unsigned*>(ptr);
-  }
-  const unsigned slot = next_slot.fetch_add(1u, std::memory_order_relaxed) % kSchedSlots;
-  return base[dev] + 2 * slot;
 }
 
 template <typename T, int D, int MODE, int STAGES, int XBUF, int YR>
@@ -873,8 +802,7 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   if (mst != NLFA_OK) return mst;
   using L = BwdSmem<D, STAGES, XBUF, YR>;
   auto kern = bwd_tc_kernel<T, D, MODE, STAGES, XBUF, YR>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
-      cudaSuccess)
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kDynamic) != NLFA_OK)
     return NLFA_ERR_CUDA;
   BwdParams bp;
   bp.T = p.T;
@@ -893,9 +821,9 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   bp.out0 = out0;
   bp.out1 = out1;
   bp.status = status;
-  bp.sched = sched_slot();
-  if (bp.sched == nullptr) return NLFA_ERR_CUDA;
-  const int grid = bp.total_units < sm_count_bwd() ? bp.total_units : sm_count_bwd();
+  const int sst = sched_counters(stream, &bp.sched);
+  if (sst != NLFA_OK) return sst;
+  const int grid = bp.total_units < sm_count() ? bp.total_units : sm_count();
   kern<<<grid, 512, L::kDynamic, stream>>>(mx0, mx1, my0, my1, mo0, mo1, bp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
 }
@@ -939,16 +867,5 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
               : launch_both<__half, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream);
 }
 
-#ifdef NLFA_TRACE
-extern "C" int nlfa_btrace_read(long long* events, int* counts) {
-  int zero[4] = {0, 0, 0, 0};
-  if (cudaDeviceSynchronize() != cudaSuccess) return NLFA_ERR_CUDA;
-  if (cudaMemcpyFromSymbol(events, g_btrace, sizeof(long long) * 4 * 1024) != cudaSuccess ||
-      cudaMemcpyFromSymbol(counts, g_btrace_n, sizeof(int) * 4) != cudaSuccess ||
-      cudaMemcpyToSymbol(g_btrace_n, zero, sizeof(zero)) != cudaSuccess)
-    return NLFA_ERR_CUDA;
-  return NLFA_OK;
-}
-#endif
 
 }  // namespace nlfa

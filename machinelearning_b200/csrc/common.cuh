@@ -114,8 +114,23 @@ int launch_selftest_tiles(int dtype, int head_dim, const void* q, const void* k,
                           float* s_out, float* o_out, unsigned* status, cudaStream_t stream);
 
 // Encodes a 4-D tensor map over a contiguous [B,T,heads,D] 16-bit tensor with a
-// box of 64 elements x 1 head x `rows` rows x 1 batch and 128-byte swizzle.
+// box of 64 elements x 1 head x `rows` rows x 1 batch and 128-byte swizzle.  Encoded maps are
+// kept in a small host-side table keyed by (base, dtype, shape, rows): a training loop calls
+// with the same buffers step after step, and the driver's encoder costs a microsecond or two
+// per map (ten maps per forward + backward).
 int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, int heads, int D,
                   int rows);
+
+// Two work counters for one launch of a persistent kernel ([0] next unit, [1] CTAs finished;
+// the last CTA of a launch zeroes them again).  Launches on a capturing stream draw from a
+// range of their own whose entries are never handed out twice, because a captured graph keeps
+// the address for as long as it is replayed; eager launches take turns on a ring.  Returns an
+// NLFA_* status (NLFA_ERR_GRAPH_SLOTS when the graph range is used up).
+int sched_counters(cudaStream_t stream, unsigned** out);
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize), once per kernel and device.
+int ensure_dynamic_smem(const void* kernel, int bytes);
+
+int sm_count();
 
 }  // namespace nlfa

@@ -21,34 +21,11 @@
 // Computes what nanolab/csrc/flash_attn_cuda.cu:583-797 computes (softmax in
 // base 2, L = m ln2 + log l at :279), with the sliding-window mask of
 // nanolab/mixers.py:125-132 and skipping of key blocks no row can see.
-#include <atomic>
-
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace nlfa {
 
-#ifdef NLFA_TRACE
-// Debug-only timeline of CTA 0: (clock64, tag) pairs per role, staged in shared memory.
-__device__ long long g_trace[4][1024];
-__device__ int g_trace_n[4];
-#define NLFA_TRACE_EVENT(role, tag)                                   \
-  do {                                                                \
-    if (blockIdx.x == 0 && tr_n < 512) {                              \
-      tr_buf[((role) * 512 + tr_n) * 2] = clock64();                  \
-      tr_buf[((role) * 512 + tr_n) * 2 + 1] = (tag);                  \
-      ++tr_n;                                                         \
-      g_trace_n[role] = tr_n;                                         \
-    }                                                                 \
-  } while (0)
-#else
-#define NLFA_TRACE_EVENT(role, tag)
-#endif
-
-// Work counters for the in-kernel scheduler: [slot][0] next unit, [slot][1] CTAs
-// finished.  The last CTA of a launch to finish zeroes its slot again.
-constexpr int kFwdSchedSlots = 256;
-__device__ unsigned g_fwd_sched[kFwdSchedSlots][2];
 
 namespace {
 
@@ -80,12 +57,7 @@ struct FwdSmem {
   static constexpr int kTmemSlot = kSched + 64 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kTotal = kAbort + 4;
-#ifdef NLFA_TRACE
-  static constexpr int kTrace = (kTotal + 15) / 16 * 16;
-  static constexpr int kDynamic = kTrace + 4 * 512 * 16 + 1024;
-#else
   static constexpr int kDynamic = kTotal + 1024;            // slack for 1024-byte alignment
-#endif
 };
 
 __device__ __forceinline__ bool tile_sees_block(const TileRange& r, int j) {
@@ -161,10 +133,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-#ifdef NLFA_TRACE
-  long long* tr_buf = reinterpret_cast<long long*>(gen + L::kTrace);
-  int tr_n = 0;
-#endif
 
   auto bar = [&](int i) -> uint32_t { return base + L::kBar + 8u * i; };
   constexpr int Q_FULL = 0, Q_EMPTY = QBUF, S_FULL = 2 * QBUF, S_CONSUMED = S_FULL + NT,
@@ -294,7 +262,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const uint32_t ph = (git / STAGES) & 1;
           const int j = w.block_at(it);
           if (!(ok = mbar_wait(bar(K_EMPTY + s), ph ^ 1, wctx, 1))) break;
-          NLFA_TRACE_EVENT(3, 100 + it);
           mbar_arrive_expect_tx(bar(K_FULL + s), L::kTileBytes);
           for (int x = 0; x < kBoxes; ++x)
             tma_load_4d(base + L::kK + s * L::kTileBytes + x * kBoxBytes, &tm_k, bar(K_FULL + s),
@@ -355,9 +322,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           ok = wait_all(bar(S_CONSUMED + t), (s_issued[t] - 1) & 1, 12);
         if (!ok) return;
         tc_fence_after();
-        if (leader) NLFA_TRACE_EVENT(2, 40 + t);
         issue_s(qb, t, s);
-        if (leader) NLFA_TRACE_EVENT(2, 50 + t);
         umma_commit(leader, bar(S_FULL + t));
         ++s_issued[t];
       };
@@ -381,17 +346,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // the previous unit: wait for its Q tiles and first K block; one tile's product; release.
       // `g0` is the global index of the unit's first key block.
       auto pro_wait = [&](int uc, int g0) {
-        if (leader) NLFA_TRACE_EVENT(2, 1);
         ok = wait_all(bar(Q_FULL + uc % QBUF), (uc / QBUF) & 1, 3);
         if (ok) ok = wait_all(bar(K_FULL + g0 % STAGES), (g0 / STAGES) & 1, 4);
-        if (leader) NLFA_TRACE_EVENT(2, 2);
       };
       auto pro_s = [&](const Unit<NT>& w, int uc, int g0, int t) {
         if (ok && w.sees(t, w.block_at(0))) start_s(uc % QBUF, t, g0 % STAGES);
       };
       auto pro_done = [&](int g0) {
         if (ok) umma_commit(leader, bar(K_EMPTY + g0 % STAGES));
-        if (leader) NLFA_TRACE_EVENT(2, 3);
       };
       // With two Q buffers and P in its own columns, the next unit's first S products are
       // issued during this unit's last key block.  Otherwise the first tile of a causal pair,
@@ -412,13 +374,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         bool o_started[NT];
         for (int t = 0; t < NT; ++t) o_started[t] = false;
         auto do_pv = [&](int t, int stage) {
-          if (leader) NLFA_TRACE_EVENT(2, 10 + t);
           if (!(ok = wait_all(bar(P_FULL + t), p_count[t] & 1, 7))) return;
-          if (leader) NLFA_TRACE_EVENT(2, 20 + t);
           ++p_count[t];
           tc_fence_after();
           issue_pv(t, stage, o_started[t]);
-          if (leader) NLFA_TRACE_EVENT(2, 30 + t);
           umma_commit(leader, bar(O_READY + t));
           o_started[t] = true;
         };
@@ -566,13 +525,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       for (int it = 0; it < w.n_iters; ++it) {
         const int j = w.block_at(it);
         if (!tile_sees_block(w.tr[t], j)) continue;
-        if (row == 0) NLFA_TRACE_EVENT(t, 1);
         ok = mbar_wait(bar(S_FULL + t), s_count & 1, wctx, 8);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         ++s_count;
         tc_fence_after();
-        if (row == 0) NLFA_TRACE_EVENT(t, 2);
 
         // the whole row of S into registers; from then on S_t belongs to the MMA issuer again
         uint32_t sv[4][32];
@@ -636,7 +593,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           }
         }
         const float mx = fmaxf(b0, b1) * p.scale_log2;
-        if (row == 0) NLFA_TRACE_EVENT(t, 3);
 
         float alpha = 1.f;
         bool rescale = false;
@@ -648,7 +604,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           rescale = true;
           l *= alpha;
         }
-        if (row == 0) NLFA_TRACE_EVENT(t, 31);
 
         // all exponentials of the row first (P stays in registers) ...
         const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
@@ -676,7 +631,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           unpack_f2(fadd2(acc0, acc1), lo, hi);
           l += lo + hi;
         }
-        if (row == 0) NLFA_TRACE_EVENT(t, 32);
         // ... and only then the hand-off that needs the previous block's PV product to be
         // complete (O may be rescaled, P's columns may be overwritten); by now it long is.
         // Every O_READY phase is observed exactly once, in order.
@@ -701,15 +655,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         first = false;
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_st16(p_addr + 16 * c, pk[c]);
-        if (row == 0) NLFA_TRACE_EVENT(t, 4);
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar(P_FULL + t));
         if (QBUF > 1 && row == 0) release_pending();
-        if (row == 0) NLFA_TRACE_EVENT(t, 5);
       }
       if (!ok) break;
-      if (row == 0) NLFA_TRACE_EVENT(t, 6);
 
       ok = mbar_wait(bar(O_READY + t), o_count & 1, wctx, 9);
       ok = __all_sync(0xffffffffu, ok);
@@ -756,7 +707,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       if (qpos < p.T)
         p.lse[(static_cast<long long>(w.b) * p.H + w.h) * p.T + qpos] = (m_ref + log2f(l)) * kLn2;
-      if (row == 0) NLFA_TRACE_EVENT(t, 7);
       // the next unit's first PV product overwrites O_t: it is only issued after this
       // thread's next P arrival, which follows these loads in program order
       tc_fence_before();
@@ -773,10 +723,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     tc_fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
-#ifdef NLFA_TRACE
-  if (blockIdx.x == 0)
-    for (int i = threadIdx.x; i < 4 * 1024; i += blockDim.x) (&g_trace[0][0])[i] = tr_buf[i];
-#endif
   // scheduler bookkeeping: the last CTA of the launch to get here re-arms the counters
   if (threadIdx.x == 0) {
     __threadfence();
@@ -789,41 +735,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
 }
 
-// Device address of a fresh pair of scheduler counters on the current device.
-unsigned* fwd_sched_slot() {
-  static unsigned* base[64];
-  static std::atomic<unsigned> next_slot{0};   // launches may come from several host threads
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (base[dev] == nullptr) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_fwd_sched) != cudaSuccess) return nullptr;
-    base[dev] = static_cast<unsigned*>(ptr);
-  }
-  const unsigned slot = next_slot.fetch_add(1u, std::memory_order_relaxed) % kFwdSchedSlots;
-  return base[dev] + 2 * slot;
-}
-
-int sm_count() {
-  static int cached[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 1;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 template <typename T, int D, int NT, int STAGES, int QBUF>
 int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
              const CUtensorMap& mo, void* o, float* lse, unsigned* status, cudaStream_t stream) {
   using L = FwdSmem<D, NT, STAGES, QBUF>;
   auto kern = fwd_tc_kernel<T, D, NT, STAGES, QBUF>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic) !=
-      cudaSuccess)
+  if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kDynamic) != NLFA_OK)
     return NLFA_ERR_CUDA;
   FwdParams fp;
   fp.T = p.T;
@@ -838,8 +755,8 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
   fp.o = o;
   fp.lse = lse;
   fp.status = status;
-  fp.sched = fwd_sched_slot();
-  if (fp.sched == nullptr) return NLFA_ERR_CUDA;
+  const int sst = sched_counters(stream, &fp.sched);
+  if (sst != NLFA_OK) return sst;
   const int grid = fp.total_units < sm_count() ? fp.total_units : sm_count();
   kern<<<grid, NT * 128 + 128, L::kDynamic, stream>>>(mq, mk, mv, mo, fp);
   return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
@@ -870,16 +787,5 @@ int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v,
               : launch_t<__half, 128, 2, 2, 1>(p, mq, mk, mv, mo, o, lse, status, stream);
 }
 
-#ifdef NLFA_TRACE
-extern "C" int nlfa_trace_read(long long* events, int* counts) {
-  int zero[4] = {0, 0, 0, 0};
-  if (cudaDeviceSynchronize() != cudaSuccess) return NLFA_ERR_CUDA;
-  if (cudaMemcpyFromSymbol(events, g_trace, sizeof(long long) * 4 * 1024) != cudaSuccess ||
-      cudaMemcpyFromSymbol(counts, g_trace_n, sizeof(int) * 4) != cudaSuccess ||
-      cudaMemcpyToSymbol(g_trace_n, zero, sizeof(zero)) != cudaSuccess)
-    return NLFA_ERR_CUDA;
-  return NLFA_OK;
-}
-#endif
 
 }  // namespace nlfa

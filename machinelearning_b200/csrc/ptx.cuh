@@ -83,22 +83,46 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Per-CTA context for bounded waits: a flag in shared memory that any thread
-// raises when it gives up, and the library's global status word.
+// raises when it gives up, the library's global status word, and how long a
+// wait may last.
 struct WaitCtx {
   volatile int* abort_flag;   // shared memory
-  unsigned* status;           // global memory
+  unsigned* status;           // global memory: the status block (see report_timeout)
+  __device__ __forceinline__ unsigned long long limit() const { return WAIT_LIMIT_NS; }
+};
+// The same with a limit chosen at run time (the error-contract test hook).
+struct WaitCtxLimit {
+  volatile int* abort_flag;
+  unsigned* status;
+  unsigned long long limit_ns;
+  __device__ __forceinline__ unsigned long long limit() const { return limit_ns; }
 };
 
-static __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                            unsigned where) {
+// The status block in global memory is four 32-bit words: [0] the status word, [1] unused,
+// [2..3] the address of an optional host-resident copy (page-locked memory the device can
+// write, registered by the host; zero when there is none).  The first wait that gives up
+// records its code in both, so that the host learns of it by reading its own memory, without
+// a device synchronisation.
+static __device__ __noinline__ void report_timeout(unsigned* status, unsigned code) {
+  if (atomicCAS(status, STATUS_OK, code) != STATUS_OK) return;
+  unsigned* mirror = *reinterpret_cast<unsigned* volatile*>(status + 2);
+  if (mirror != nullptr) {
+    *reinterpret_cast<volatile unsigned*>(mirror) = code;
+    __threadfence_system();
+  }
+}
+
+template <class Ctx>
+static __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const Ctx& ctx,
+                                                      unsigned where) {
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t spins = 1;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 0xffu) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (globaltimer_ns() - t0 > ctx.limit()) {
         *ctx.abort_flag = 1;
-        atomicCAS(ctx.status, STATUS_OK, STATUS_WAIT_TIMEOUT | (where & 0xffu));
+        report_timeout(ctx.status, STATUS_WAIT_TIMEOUT | (where & 0xffu));
         return false;
       }
     }
@@ -117,16 +141,17 @@ static __device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t par
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 0x3fu) == 0u) {
       if (*ctx.abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (globaltimer_ns() - t0 > ctx.limit()) {
         *ctx.abort_flag = 1;
-        atomicCAS(ctx.status, STATUS_OK, STATUS_WAIT_TIMEOUT | (where & 0xffu));
+        report_timeout(ctx.status, STATUS_WAIT_TIMEOUT | (where & 0xffu));
         return false;
       }
     }
   }
 }
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
+template <class Ctx>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Ctx& ctx,
                                           unsigned where) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, ctx, where);

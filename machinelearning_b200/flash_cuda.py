@@ -50,6 +50,41 @@ _load_error: str | None = None
 _load_attempted = False
 _mma_ok = False
 _mma_error: str | None = None
+_status_words: dict[int, torch.Tensor] = {}       # device index -> pinned int32 word the kernels write
+
+
+def _watch_device(lib, index: int) -> None:
+    """Give the library a page-locked word for device ``index`` (once per device).  A kernel whose
+    bounded wait runs out writes its code there, so the next call learns of it from host memory,
+    with no synchronisation on the hot path."""
+    if index in _status_words:
+        return
+    word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    with torch.cuda.device(index):
+        st = lib.nlfa_set_status_mirror(word.data_ptr())
+    _lib.check("nlfa_set_status_mirror", st)
+    _status_words[index] = word
+
+
+def device_timed_out() -> bool:
+    """True when a kernel on any watched device has given up a wait since the last reset."""
+    return any(int(w[0]) != 0 for w in _status_words.values())
+
+
+def reset_device_status() -> int:
+    """Read and clear the status word of every watched device (synchronises them).  Returns the
+    last non-zero raw word seen, 0 when there was none.  After this the kernels run again."""
+    import ctypes
+    seen = 0
+    lib = _load()
+    if lib is None:
+        return 0
+    for index in list(_status_words):
+        raw = ctypes.c_uint(0)
+        with torch.cuda.device(index):
+            lib.nlfa_device_status(ctypes.byref(raw))
+        seen = raw.value or seen
+    return seen
 
 
 def _probe_mma(lib) -> tuple[bool, str]:
@@ -97,17 +132,29 @@ def _load():
     _mma_ok, _mma_error = _probe_mma(_ext)
     if not _mma_ok:
         log.warning("tensor-core path off (%s); using the SIMT kernels", _mma_error)
+    try:
+        _watch_device(_ext, torch.cuda.current_device())
+    except Exception as e:                                    # noqa: BLE001
+        log.warning("status word not mirrored to the host (%s)", e)
     return _ext
 
 
+_TIMED_OUT = ("a kernel gave up a bounded wait (status 10: a bounded wait inside a kernel gave up); "
+              "outputs of that launch are not valid; call reset_device_status() to re-arm")
+
+
 def is_available() -> bool:
-    """True once the library is loaded on a machine with a CUDA device."""
-    return _load() is not None
+    """True once the library is loaded on a machine with a CUDA device -- and no kernel has given
+    up a wait since the last ``reset_device_status()``: like the reference's loader
+    (``flash_cuda.py:91-135``) this fails closed, so the mixer falls back instead of training on."""
+    return _load() is not None and not device_timed_out()
 
 
 def unavailable_reason() -> str:
     _load()
-    return "" if _ext is not None else (_load_error or "unknown")
+    if _ext is None:
+        return _load_error or "unknown"
+    return _TIMED_OUT if device_timed_out() else ""
 
 
 def mma_available() -> bool:
@@ -173,6 +220,8 @@ def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0):
         raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
     B, T, H, D = q.shape
     Hkv = k.shape[2]
+    if q.device.index not in _status_words:
+        _watch_device(lib, q.device.index)
     o = torch.empty_like(q)
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
@@ -192,6 +241,8 @@ def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sin
         raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
     B, T, H, D = q.shape
     Hkv = k.shape[2]
+    if q.device.index not in _status_words:
+        _watch_device(lib, q.device.index)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     nbytes = lib.nlfa_bwd_scratch_bytes(B, T, H)
     scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=q.device)
@@ -339,34 +390,32 @@ def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tenso
 
 
 def sdpa_reference(q, k, v, scale):
-    """What nanolab does without the kernel (reference: ``flash_cuda.py:282-294``):
-    widen KV heads, transpose, call torch SDPA.  A comparison arm for the
-    self-check below, on the same device as its inputs; not used by ``flash_attn``."""
-    import torch.nn.functional as F
-    group = q.shape[2] // k.shape[2]
-    qs = q.transpose(1, 2)
-    ks = k.repeat_interleave(group, dim=2).transpose(1, 2)
-    vs = v.repeat_interleave(group, dim=2).transpose(1, 2)
-    y = F.scaled_dot_product_attention(qs, ks, vs, is_causal=True, scale=scale)
-    return y.transpose(1, 2).contiguous()
+    """nanolab's attention without the kernel (the role of the reference's ``sdpa_reference``,
+    ``flash_cuda.py:282-294``): torch SDPA on ``[B,H,T,D]`` views with the KV heads repeated for
+    the group.  The self-check's comparison arm; ``flash_attn`` never calls it."""
+    heads_per_kv = q.shape[2] // k.shape[2]
+    widen = (lambda t: t) if heads_per_kv == 1 else (lambda t: t.repeat_interleave(heads_per_kv, dim=2))
+    out = torch.nn.functional.scaled_dot_product_attention(
+        q.permute(0, 2, 1, 3), widen(k).permute(0, 2, 1, 3), widen(v).permute(0, 2, 1, 3),
+        is_causal=True, scale=scale)
+    return out.permute(0, 2, 1, 3).contiguous()
 
 
-def _bench_once(fn, iters: int, warmup: int = 5) -> float:
-    """Median milliseconds per call, GPU-synchronised (reference: ``:297-312``)."""
-    import statistics
+def _median_ms(fn, iters: int, warmup: int = 5) -> float:
+    """Median device time of ``fn`` in milliseconds: one CUDA-event pair per call, each call
+    synchronised, after ``warmup`` untimed calls (what the reference's ``_bench_once`` reports)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    times = []
-    for _ in range(iters):
-        start = torch.cuda.Event(enable_timing=True)
-        end = torch.cuda.Event(enable_timing=True)
-        start.record()
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for first, last in pairs:
+        first.record()
         fn()
-        end.record()
-        torch.cuda.synchronize()
-        times.append(start.elapsed_time(end))
-    return statistics.median(times)
+        last.record()
+        last.synchronize()
+    ms = sorted(first.elapsed_time(last) for first, last in pairs)
+    mid = len(ms) // 2
+    return ms[mid] if len(ms) % 2 else 0.5 * (ms[mid - 1] + ms[mid])
 
 
 def _cached_check(args) -> int:
@@ -410,30 +459,32 @@ def _cached_check(args) -> int:
     kv_bytes = 2 * k.numel() * k.element_size()
     for name, fn in (("cat + repeat + mask + SDPA", nanolab_way), ("cat + flash_attn_cached", kernel_with_cat),
                      ("flash_attn_cached", kernel_only)):
-        ms = _bench_once(fn, args.iters)
+        ms = _median_ms(fn, args.iters)
         print(f"  {name:28s} {ms * 1e3:9.1f} us   {kv_bytes / ms / 1e6:8.0f} GB/s of K, V")
     return 0
 
 
-def main() -> int:
-    """Correctness against SDPA, then a speed comparison (reference: ``:315-379``)."""
+_CLI_DTYPES = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+def _cli_args():
     import argparse
+    ap = argparse.ArgumentParser(description="self-check against torch SDPA, then timings")
+    for flag, default in (("--batch", 8), ("--seq", 1024), ("--heads", 12), ("--kv_heads", 4),
+                          ("--head_dim", 32), ("--iters", 20), ("--window", 0), ("--sinks", 0)):
+        ap.add_argument(flag, type=int, default=default)
+    ap.add_argument("--dtype", default="bf16", choices=tuple(_CLI_DTYPES))
+    ap.add_argument("--cached", type=int, default=0, metavar="BLOCK",
+                    help="instead: a BLOCK-token active block over --seq keys through flash_attn_cached, "
+                         "against nanolab's cat + repeat_interleave + masked SDPA")
+    return ap.parse_args()
 
-    p = argparse.ArgumentParser(description=__doc__)
-    p.add_argument("--batch", type=int, default=8)
-    p.add_argument("--seq", type=int, default=1024)
-    p.add_argument("--heads", type=int, default=12)
-    p.add_argument("--kv_heads", type=int, default=4)
-    p.add_argument("--head_dim", type=int, default=64)
-    p.add_argument("--dtype", default="bf16", choices=("fp32", "fp16", "bf16"))
-    p.add_argument("--iters", type=int, default=20)
-    p.add_argument("--cached", type=int, default=0, metavar="BLOCK",
-                   help="instead: a BLOCK-token active block over --seq keys through flash_attn_cached, "
-                        "against nanolab's cat + repeat_interleave + masked SDPA")
-    p.add_argument("--window", type=int, default=0)
-    p.add_argument("--sinks", type=int, default=0)
-    args = p.parse_args()
 
+def main() -> int:
+    """``python -m machinelearning_b200.flash_cuda``: the job of the reference's self-check
+    (``flash_cuda.py:315-379``, same flags and default shape B8 T1024 H12/4 D32 bf16): agreement
+    with SDPA is printed before any timing, then forward and forward+backward medians per arm."""
+    args = _cli_args()
     if not torch.cuda.is_available():
         print("no CUDA device -- nothing to run")
         return 1
@@ -443,46 +494,42 @@ def main() -> int:
     if args.cached:
         return _cached_check(args)
 
-    dtype = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}[args.dtype]
-    B, T, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
+    dtype = _CLI_DTYPES[args.dtype]
+    shape_q = (args.batch, args.seq, args.heads, args.head_dim)
+    shape_kv = (args.batch, args.seq, args.kv_heads, args.head_dim)
     torch.manual_seed(0)
-    q = torch.randn(B, T, H, D, device="cuda", dtype=dtype, requires_grad=True)
-    k = torch.randn(B, T, Hkv, D, device="cuda", dtype=dtype, requires_grad=True)
-    v = torch.randn(B, T, Hkv, D, device="cuda", dtype=dtype, requires_grad=True)
-    scale = 1.0 / math.sqrt(D)
+    q, k, v = (torch.randn(sh, device="cuda", dtype=dtype, requires_grad=True)
+               for sh in (shape_q, shape_kv, shape_kv))
+    upstream = torch.randn(shape_q, device="cuda", dtype=dtype)
+    scale = 1.0 / math.sqrt(args.head_dim)
+    tensor_cores = mma_available() and _tensor_path_fits(dtype, args.head_dim)
+    print(f"q {shape_q} k/v {shape_kv} {args.dtype}; tensor-core kernels "
+          + ("on" if tensor_cores else f"off ({mma_unavailable_reason() or 'dtype / head dim'})"))
 
-    print(f"shape B{B} T{T} H{H}/{Hkv} D{D} {args.dtype}")
-    if mma_available():
-        print("  tensor-core path: on (self-test passed)")
-    else:
-        print(f"  tensor-core path: OFF -- {mma_unavailable_reason()}")
+    arms = {"SDPA": lambda: sdpa_reference(q, k, v, scale),
+            "simt": lambda: flash_attn(q, k, v, scale, use_mma=False)}
+    if tensor_cores:
+        arms["tc"] = lambda: flash_attn(q, k, v, scale, use_mma=True)
 
-    mma_usable = mma_available() and _tensor_path_fits(dtype, D)
-    arms = [("SDPA", lambda: sdpa_reference(q, k, v, scale)),
-            ("simt", lambda: flash_attn(q, k, v, scale, use_mma=False))]
-    if mma_usable:
-        arms.append(("tc", lambda: flash_attn(q, k, v, scale, use_mma=True)))
+    def with_grads(arm):
+        out = arm()
+        return out, torch.autograd.grad(out, (q, k, v), upstream)
 
-    y_ref = sdpa_reference(q, k, v, scale)
-    do = torch.randn_like(y_ref)
-    gr = torch.autograd.grad(y_ref, (q, k, v), do, retain_graph=False)
-    for name, fn in arms[1:]:
-        y = fn()
-        g = torch.autograd.grad(y, (q, k, v), do, retain_graph=False)
-        fe = (y.float() - y_ref.float()).abs().max().item()
-        be = max((a.float() - b.float()).abs().max().item() for a, b in zip(g, gr))
-        print(f"  {name:4s} vs SDPA:  max |dO| {fe:.3e}   max |dgrad| {be:.3e}")
+    want, want_grads = with_grads(arms["SDPA"])
+    for name, arm in arms.items():
+        if name == "SDPA":
+            continue
+        got, got_grads = with_grads(arm)
+        worst_grad = max(float((g.float() - w.float()).abs().max()) for g, w in zip(got_grads, want_grads))
+        print(f"{name:>5} - SDPA   max|O| {float((got.float() - want.float()).abs().max()):.3e}   "
+              f"max|grad| {worst_grad:.3e}")
 
-    def _fwd_bwd(fn):
-        torch.autograd.grad(fn(), (q, k, v), do, retain_graph=False)
-
-    print(f"  {'arm':4s} {'fwd ms':>10s} {'fwd+bwd ms':>12s} {'vs SDPA fwd':>13s}")
-    base = None
-    for name, fn in arms:
-        t_f = _bench_once(fn, args.iters)
-        t_fb = _bench_once(lambda fn=fn: _fwd_bwd(fn), args.iters)
-        base = base if base is not None else t_f
-        print(f"  {name:4s} {t_f:10.3f} {t_fb:12.3f} {base / t_f:12.2f}x")
+    rows = [(name, _median_ms(arm, args.iters), _median_ms(lambda arm=arm: with_grads(arm), args.iters))
+            for name, arm in arms.items()]
+    sdpa_fwd, sdpa_both = rows[0][1], rows[0][2]
+    print(f"{'':>5} {'forward':>11} {'fwd + bwd':>11} {'speed-up over SDPA':>22}")
+    for name, t_fwd, t_both in rows:
+        print(f"{name:>5} {t_fwd:9.3f}ms {t_both:9.3f}ms {sdpa_fwd / t_fwd:10.2f}x {sdpa_both / t_both:9.2f}x")
     return 0
 
 

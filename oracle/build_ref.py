@@ -14,6 +14,13 @@ are the ones ``torch.utils.cpp_extension`` passes for the reference's own JIT bu
 
 Only the tests and the self-check table use the result, as a checker and a same-box
 baseline; the product never loads it.  Takes about five minutes on eight cores.
+
+``stage_nanolab()`` puts the reference's ``nanolab`` Python package (the caller of this
+path: ``mixers.py``, ``model.py``, ``config.py``, ``optim.py``, ``bench_gpu.py`` and what they
+import) beside it as ``oracle/_ref/nanolab/`` -- a git-ignored staging copy, like the built
+module, so that the drop-in tests and the whole-model benchmark can run nanolab's own code,
+unmodified, on a machine that has no reference checkout.  ``nanolab_on_path()`` makes it
+importable.
 """
 from __future__ import annotations
 
@@ -24,10 +31,44 @@ import sysconfig
 
 HERE = pathlib.Path(__file__).resolve().parent
 OUT = HERE / "_ref" / "nanolab_flash_attn.so"
+STAGED = HERE / "_ref" / "nanolab"
+# the modules the attention caller imports, directly or not (nanolab/model.py:22-23,
+# nanolab/bench_gpu.py:24-27); flash_cuda.py is staged too, as the module this package replaces
+NANOLAB_MODULES = ("__init__", "config", "mixers", "model", "optim", "utils", "bench_gpu", "flash_cuda",
+                   "schedules")
+
+
+def _reference_root(ref_root: str | None) -> pathlib.Path:
+    return pathlib.Path(ref_root) if ref_root else HERE.parent.parent / "reference"
+
+
+def stage_nanolab(ref_root: str | None = None) -> pathlib.Path | None:
+    """Copy the reference's nanolab modules into ``oracle/_ref/nanolab/`` (no-op without a checkout)."""
+    import shutil
+    src = _reference_root(ref_root) / "nanolab"
+    if not (src / "mixers.py").exists():
+        return STAGED if (STAGED / "mixers.py").exists() else None
+    STAGED.mkdir(parents=True, exist_ok=True)
+    for name in NANOLAB_MODULES:
+        f = src / f"{name}.py"
+        dst = STAGED / f.name
+        if f.exists() and (not dst.exists() or dst.stat().st_mtime < f.stat().st_mtime):
+            shutil.copyfile(f, dst)
+    return STAGED
+
+
+def nanolab_on_path() -> bool:
+    """Put the staged package's parent on ``sys.path``; False when nothing is staged."""
+    if not (STAGED / "mixers.py").exists():
+        return False
+    parent = str(STAGED.parent)
+    if parent not in sys.path:
+        sys.path.insert(0, parent)
+    return True
 
 
 def build(ref_root: str | None = None, force: bool = False) -> pathlib.Path | None:
-    root = pathlib.Path(ref_root) if ref_root else HERE.parent.parent / "reference"
+    root = _reference_root(ref_root)
     src = root / "nanolab" / "csrc" / "flash_attn_cuda.cu"
     if not src.exists():
         return OUT if OUT.exists() else None
@@ -66,3 +107,4 @@ def load():
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     print(build(args[0] if args else None, force="--force" in sys.argv))
+    print(stage_nanolab(args[0] if args else None))

@@ -59,6 +59,46 @@ def test_compiled_caller_matches_eager(window, sinks):
         assert torch.equal(a, b)
 
 
+@pytest.mark.gpu
+def test_caller_compiled_with_inductor_keeps_the_operator_whole():
+    """nanolab compiles its model with torch's default backend (``nanolab/train.py:213``).  The
+    operators must pass through inductor as opaque nodes (``fullgraph=True``: a graph break would
+    raise) and still run the library's kernels; the code inductor generates for the caller's own
+    operations either side may round differently from eager, hence a tolerance, not bit-equality."""
+    from machinelearning_b200 import flash_cuda
+    assert flash_cuda.is_available(), flash_cuda.unavailable_reason()
+    torch.manual_seed(0)
+    B, T, H, Hkv, D = 2, 256, 4, 2, 64
+    q, k, v = (torch.randn(B, T, h, D, device="cuda", dtype=torch.bfloat16, requires_grad=True) for h in (H, Hkv, Hkv))
+    w = (torch.randn(H * D, H * D, device="cuda") / 16).bfloat16().requires_grad_()
+    do = torch.randn(B, T, H * D, device="cuda", dtype=torch.bfloat16)
+    calls = {"n": 0}
+    real = flash_cuda.fwd
+
+    def counted(*a, **kw):
+        calls["n"] += 1
+        return real(*a, **kw)
+
+    def layer(q, k, v, w):
+        y = flash_cuda.flash_attn(torch.nn.functional.silu(q) + q, k, v, 1.0 / math.sqrt(D), window=96, sinks=4)
+        return torch.nn.functional.gelu(y.reshape(B, T, H * D) @ w)
+
+    eager = layer(q, k, v, w)
+    g_eager = torch.autograd.grad(eager, (q, k, v, w), do)
+    flash_cuda.fwd = counted
+    try:
+        compiled = torch.compile(layer, backend="inductor", fullgraph=True)
+        out = compiled(q, k, v, w)
+        g_out = torch.autograd.grad(out, (q, k, v, w), do)
+    finally:
+        flash_cuda.fwd = real
+    assert calls["n"] == 1                        # the compiled graph ran the library's forward
+    rel = lambda a, b: float((a.detach().float() - b.detach().float()).abs().max() / b.detach().float().abs().max())
+    assert rel(out, eager) <= 2e-2
+    for a, b in zip(g_out, g_eager):
+        assert rel(a, b) <= 2e-2
+
+
 def test_prologue_and_epilogue_operators_have_shape_functions():
     with FakeTensorMode():
         x = torch.empty(2, 50, 4, 64, dtype=torch.bfloat16, device="cuda")

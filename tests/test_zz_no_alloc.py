@@ -5,8 +5,10 @@ scratch buffer -- their device memory is already committed elsewhere, or they
 may not call anything that allocates.  It keeps the Delta tape in a fixed array
 inside the library, so consecutive calls reuse the same memory; this test makes
 two calls in a row, with different upstream gradients, and holds each to the
-result of `nlfa_bwd` on the same inputs.  It is collected last on purpose, and
-passes both alone in a fresh process and after the rest of the suite.
+result of `nlfa_bwd` on the same inputs.  Both entry points run the same
+kernels on the same inputs and the kernels are bit-reproducible, so the results
+must be equal bit for bit.  It is collected last on purpose, and passes both
+alone in a fresh process and after the rest of the suite.
 """
 import math
 
@@ -15,39 +17,52 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-REL_16BIT = 2e-2        # the suite's tolerance for 16-bit tensors: max|x - ref| / max|ref|
+
+def _static_bwd(lib, L, dout, q, k, v, o, lse, scale, window, sinks, path):
+    B, T, H, D = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    code = {torch.float32: L.DTYPE_F32, torch.float16: L.DTYPE_F16, torch.bfloat16: L.DTYPE_BF16}[q.dtype]
+    st = lib.nlfa_bwd_static_scratch(
+        dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+        dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, T, H, k.shape[2], D, scale, window, sinks,
+        code, path, torch.cuda.current_stream().cuda_stream)
+    assert st == 0, L.strerror(st)
+    return dq, dk, dv
 
 
-def rel(a, b):
-    return float((a.float() - b.float()).abs().max() / b.float().abs().max())
+# (B, T, H, Hkv, D, dtype, tensor cores, window, sinks)
+CASES = {
+    "bf16_gqa": (2, 300, 4, 2, 64, torch.bfloat16, True, 0, 0),
+    "bf16_window_with_sinks": (2, 300, 4, 2, 64, torch.bfloat16, True, 96, 4),
+    "fp32_simt": (2, 100, 4, 2, 32, torch.float32, False, 0, 0),
+    "at_the_limit_1048576_rows": (64, 1024, 16, 16, 32, torch.bfloat16, True, 0, 0),
+}
 
 
-def test_static_scratch_backward_matches_nlfa_bwd_twice_in_a_row():
-    from machinelearning_b200 import _lib, flash_cuda as fc
+@pytest.mark.parametrize("case", list(CASES))
+def test_static_scratch_backward_equals_nlfa_bwd_twice_in_a_row(case):
+    from machinelearning_b200 import _lib as L, flash_cuda as fc
     assert fc.is_available(), fc.unavailable_reason()
     assert fc.mma_available(), fc.mma_unavailable_reason()
-    lib = _lib.load()
-    B, T, H, Hkv, D = 2, 300, 4, 2, 64
+    lib = L.load()
+    B, T, H, Hkv, D, dtype, tensor, window, sinks = CASES[case]
     assert B * H * T <= lib.nlfa_static_scratch_max_rows()
+    if case.startswith("at_the_limit"):
+        assert B * H * T == lib.nlfa_static_scratch_max_rows()
     scale = 1.0 / math.sqrt(D)
     torch.manual_seed(7)
-    mk = lambda h: torch.randn(B, T, h, D, device="cuda").bfloat16()
+    mk = lambda h: torch.randn(B, T, h, D, device="cuda").to(dtype)
     q, k, v = mk(H), mk(Hkv), mk(Hkv)
-    o, lse = fc.fwd(q, k, v, scale, True)
-    stream = torch.cuda.current_stream().cuda_stream
+    o, lse = fc.fwd(q, k, v, scale, tensor, window, sinks)
+    path = L.PATH_TENSOR if tensor else L.PATH_SIMT
     for call in range(2):
         dout = mk(H) * (1.0 + call)                       # second call: other gradients, larger
-        want = fc.bwd(dout, q, k, v, o, lse, scale, True)  # the existing entry point
-        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        st = lib.nlfa_bwd_static_scratch(
-            dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-            lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, T, H, Hkv, D, scale,
-            0, 0, _lib.DTYPE_BF16, _lib.PATH_TENSOR, stream)
-        assert st == 0, _lib.strerror(st)
+        want = fc.bwd(dout, q, k, v, o, lse, scale, tensor, window, sinks)   # the existing entry point
+        got = _static_bwd(lib, L, dout, q, k, v, o, lse, scale, window, sinks, path)
         torch.cuda.synchronize()
-        for name, got, ref in zip(("dq", "dk", "dv"), (dq, dk, dv), want):
-            assert torch.isfinite(got).all(), (call, name)
-            assert rel(got, ref) <= REL_16BIT, (call, name)
+        for name, g, w in zip(("dq", "dk", "dv"), got, want):
+            assert torch.isfinite(g.float()).all(), (call, name)
+            assert torch.equal(g, w), (call, name, float((g.float() - w.float()).abs().max()))
 
 
 def test_static_scratch_refuses_problems_beyond_its_limit():
