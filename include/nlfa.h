@@ -108,10 +108,33 @@ int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, cons
 #define NLFA_PASS_DKV 2
 #define NLFA_PASS_DQ 4
 #define NLFA_PASS_ALL 7
+#define NLFA_PASS_FUSED 8 /* dK, dV and dQ in one pass (see nlfa_bwd_fused); excludes DKV and DQ */
 int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* v, const void* o,
                     const float* lse, void* dq, void* dk, void* dv, void* scratch,
                     size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
                     int window, int sinks, int dtype, int path, int passes, void* stream);
+
+/* The backward with dQ formed in the dK/dV pass: P and dS are computed once per
+ * (query tile, key block) instead of once in each of the reference's two passes
+ * (nanolab/csrc/flash_attn_cuda.cu:806-971 and :983-1191 both recompute them, by
+ * design, :48-52).  Every key block adds its 128 x 64 share dS K to fp32 sums of
+ * the query tile in `scratch`; the additions happen in a fixed order (ascending
+ * key block, enforced by a turn counter per query tile), so the gradients stay
+ * bit-reproducible like the reference's (nanolab/tests.py:415-420); a second
+ * small kernel turns the sums into dQ.  Tensor-core path with D <= 64; for other
+ * inputs this is nlfa_bwd.  `scratch` must be 16-byte aligned and hold
+ * nlfa_bwd_fused_scratch_bytes(B, T, H, D) bytes (the Delta tape, the counters,
+ * and B * H * ceil(T / 128) * 32 KiB of sums); nothing in it needs initialising.
+ * Same arguments and results as nlfa_bwd, to rounding: dQ is summed block by
+ * block in fp32 here and inside one accumulator there; dK and dV are identical.
+ * An alternative layout, not the default: on B200 the two passes of nlfa_bwd
+ * are faster at these head dims (B=32, H=12, T=1024, D=64 bf16: 0.32 ms against
+ * 0.26 ms, both without the Delta kernel). */
+size_t nlfa_bwd_fused_scratch_bytes(int B, int T, int H, int D);
+int nlfa_bwd_fused(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                   const float* lse, void* dq, void* dk, void* dv, void* scratch,
+                   size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
+                   int window, int sinks, int dtype, int path, void* stream);
 
 /* The backward without a caller-supplied scratch buffer.  No counterpart in the
  * reference (its backward allocates its own tape with at::empty).
@@ -250,8 +273,10 @@ int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, c
  * element-wise predicate of nanolab/mixers.py:125-132 evaluated for every
  * (query, key) pair, (1) the range of key blocks a 128-row query tile is given,
  * (2) the "every pair visible" claim for each (128-row tile) x (stream_rows-row
- * tile) rectangle, in both orientations, and (3) the claim that only the causal
- * edge or only the window's lower edge cuts a rectangle.  stream_rows is 64 or
+ * tile) rectangle, in both orientations, (3) the claim that only the causal
+ * edge or only the window's lower edge cuts a rectangle, and (4, stream_rows
+ * 128) that the key blocks which meet a query tile in the one-pass backward take
+ * the turns 0 .. n-1 once each, in ascending block order.  stream_rows is 64 or
  * 128.  Returns 0 when all agree, otherwise 1 + the index of the first failing
  * check (negative: bad arguments).  Needs no device.  No counterpart in the
  * reference. */

@@ -14,7 +14,7 @@ LIB_PATH = PKG / "libnlfa.so"
 
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TENSOR = 0, 1, 2
-PASS_DELTA, PASS_DKV, PASS_DQ, PASS_ALL = 1, 2, 4, 7
+PASS_DELTA, PASS_DKV, PASS_DQ, PASS_ALL, PASS_FUSED = 1, 2, 4, 7, 8
 OK = 0
 ERR_DEVICE_TIMEOUT = 10
 ERR_SELFTEST_MISMATCH = 12
@@ -33,6 +33,9 @@ SIGNATURES = {
                  + [_c_int] * 4 + [_c_void_p]),
     "nlfa_bwd_passes": (_c_int, [_c_void_p] * 10 + [_c_size_t] + [_c_int] * 5 + [_c_float]
                         + [_c_int] * 5 + [_c_void_p]),
+    "nlfa_bwd_fused_scratch_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
+    "nlfa_bwd_fused": (_c_int, [_c_void_p] * 10 + [_c_size_t] + [_c_int] * 5 + [_c_float]
+                       + [_c_int] * 4 + [_c_void_p]),
     "nlfa_static_scratch_max_rows": (_c_size_t, []),
     "nlfa_bwd_static_scratch": (_c_int, [_c_void_p] * 9 + [_c_int] * 5 + [_c_float]
                                 + [_c_int] * 4 + [_c_void_p]),

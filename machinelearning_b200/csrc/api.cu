@@ -358,23 +358,51 @@ int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, cons
                          D, scale, window, sinks, dtype, path, NLFA_PASS_ALL, stream);
 }
 
+namespace {
+size_t round256(size_t n) { return (n + 255) / 256 * 256; }
+}  // namespace
+
+size_t nlfa_bwd_fused_scratch_bytes(int B, int T, int H, int D) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  const size_t base = round256(nlfa_bwd_scratch_bytes(B, T, H));
+  if (D > 64) return base;                              // no fused pass: the two passes need the tape only
+  const size_t tiles = static_cast<size_t>(B) * H * ((T + kTile - 1) / kTile);
+  return base + round256(tiles * sizeof(unsigned)) + tiles * kTile * 64 * sizeof(float);
+}
+
+int nlfa_bwd_fused(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                   const float* lse, void* dq, void* dk, void* dv, void* scratch,
+                   size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
+                   int window, int sinks, int dtype, int path, void* stream) {
+  const int resolved = nlfa_resolve_path(dtype, D, path);
+  const bool fused = resolved == NLFA_PATH_TENSOR && D <= 64;
+  return nlfa_bwd_passes(dout, q, k, v, o, lse, dq, dk, dv, scratch, scratch_bytes, B, T, H, Hkv,
+                         D, scale, window, sinks, dtype, path,
+                         fused ? (NLFA_PASS_DELTA | NLFA_PASS_FUSED) : NLFA_PASS_ALL, stream);
+}
+
 int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* v, const void* o,
                     const float* lse, void* dq, void* dk, void* dv, void* scratch,
                     size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
                     int window, int sinks, int dtype, int path, int passes, void* stream) {
-  if (passes <= 0 || passes > NLFA_PASS_ALL) return NLFA_ERR_UNSUPPORTED_PATH;
+  if (passes <= 0 || passes > (NLFA_PASS_ALL | NLFA_PASS_FUSED)) return NLFA_ERR_UNSUPPORTED_PATH;
+  const bool want_fused = (passes & NLFA_PASS_FUSED) != 0;
+  if (want_fused && (passes & (NLFA_PASS_DKV | NLFA_PASS_DQ))) return NLFA_ERR_UNSUPPORTED_PATH;
   Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype};
   int st = check_problem(p);
   if (st != NLFA_OK) return st;
   const int resolved = nlfa_resolve_path(dtype, D, path);
   if (resolved < 0) return -resolved;
+  if (want_fused && (resolved != NLFA_PATH_TENSOR || D > 64)) return NLFA_ERR_UNSUPPORTED_PATH;
   if (B == 0 || T == 0 || H == 0) return NLFA_OK;
   if (!dout || !q || !k || !v || !o || !lse || !dq || !dk || !dv || !scratch)
     return NLFA_ERR_NULL_POINTER;
   if (!aligned16(dout) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) ||
       !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
     return NLFA_ERR_MISALIGNED;
-  if (scratch_bytes < nlfa_bwd_scratch_bytes(B, T, H)) return NLFA_ERR_SCRATCH_TOO_SMALL;
+  if (want_fused && !aligned16(scratch)) return NLFA_ERR_MISALIGNED;
+  if (scratch_bytes < (want_fused ? nlfa_bwd_fused_scratch_bytes(B, T, H, D) : nlfa_bwd_scratch_bytes(B, T, H)))
+    return NLFA_ERR_SCRATCH_TOO_SMALL;
   if (p.window > 0 && p.window - p.sinks >= p.T) {
     p.window = 0;
     p.sinks = 0;
@@ -387,7 +415,15 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
   if (host_status() != 0) return NLFA_ERR_DEVICE_TIMEOUT;   // an earlier kernel gave up: refuse until cleared
   unsigned* status = status_word();
   if (!status) return NLFA_ERR_CUDA;
-  return launch_bwd_tc(p, dout, q, k, v, o, lse, dq, dk, dv, delta, passes, status, s);
+  FusedScratch fs{nullptr, nullptr};
+  if (want_fused) {
+    uint8_t* ws = static_cast<uint8_t*>(scratch) + round256(nlfa_bwd_scratch_bytes(B, T, H));
+    const size_t tiles = static_cast<size_t>(B) * H * ((T + kTile - 1) / kTile);
+    fs.dq_turn = reinterpret_cast<unsigned*>(ws);
+    fs.dq_acc = reinterpret_cast<float*>(ws + round256(tiles * sizeof(unsigned)));
+  }
+  return launch_bwd_tc(p, dout, q, k, v, o, lse, dq, dk, dv, delta, passes, status, s,
+                       want_fused ? &fs : nullptr);
 }
 
 int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,
@@ -453,6 +489,22 @@ int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows) {
           ++check;
         }
       }
+  // (4) fused backward: the key blocks that stream query tile t take the turns 0 .. count - 1
+  //     exactly once each, in ascending block order, the diagonal block last
+  if (stream_rows == kTile)
+    for (int t = 0; t < n128; ++t) {
+      int expect = 0, count = 0;
+      for (int j = 0; j < n128; ++j) {
+        if (t < j || t > last_query_tile_of_block(j, n128, kTile, window, sinks)) continue;
+        const int turn = dq_turn_of_block(j, t, window, sinks, &count);
+        if (turn != expect) return 1 + check;
+        ++expect;
+        if ((turn == count - 1) != (j == t)) return 1 + check;
+      }
+      ++check;
+      if (expect != count) return 1 + check;
+      ++check;
+    }
   return 0;
 }
 

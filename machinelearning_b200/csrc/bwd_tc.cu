@@ -38,7 +38,7 @@ namespace nlfa {
 
 namespace {
 
-enum { MODE_DQ = 0, MODE_DKV = 1 };
+enum { MODE_DQ = 0, MODE_DKV = 1, MODE_FUSED = 2 };
 
 struct BwdParams {
   int T, H, Hkv;
@@ -54,24 +54,31 @@ struct BwdParams {
   void* out1;            // --  | dV
   unsigned* status;
   unsigned* sched;       // this launch's two counters
+  // fused pass only
+  float* dq_acc;         // per (b, h, query tile): 128 x 64 fp32 partial sums, rows permuted (see drain)
+  unsigned* dq_turn;     // per (b, h, query tile): how many key blocks have added their share
+  int sched_group;       // (batch, KV head) pairs whose units are handed out together
 };
 
-template <int D, int STAGES, int XBUF, int YR>
+template <int D, int STAGES, int XBUF, int YR, bool FUSED = false>
 struct BwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;              // stationary tile: 128 rows
   static constexpr int kYTileBytes = YR * D * 2;                // streamed tile: YR rows
   static constexpr int kX = 0;                                  // [XBUF] x (X0, X1)
   static constexpr int kY = kX + XBUF * 2 * kTileBytes;         // per stage: Y0, Y1
-  static constexpr int kVec = kY + STAGES * 2 * kYTileBytes;    // per stage: -lse2[YR], -delta[YR]
+  static constexpr int kDs = kY + STAGES * 2 * kYTileBytes;     // fused pass: dS^T [128 keys][128 queries] 16-bit
+  static constexpr int kVec = kDs + (FUSED ? kTile * YR * 2 : 0);   // per stage: -lse2[YR], -delta[YR]
   static constexpr int kBar = kVec + STAGES * 1024;
   // barriers: x_full[XBUF], x_empty[XBUF], t_full, t_consumed, pd_full, out_ready,
   //           sched_full[kRing], y_full[S], y_empty[S]
   static constexpr int kRing = 8;
-  static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES + 2;
+  //           unit_done, out_drained, dq_ready, dq_drained, group, issued[4]
+  static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES + 9;
   static constexpr int kSched = (kBar + 8 * kNumBars + 15) / 16 * 16;   // ring of unit descriptors (8 ints each)
   static constexpr int kTmemSlot = kSched + 32 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
-  static constexpr int kTotal = kAbort + 4;
+  static constexpr int kTurnOk = kAbort + 4;                    // fused pass: iterations whose dQ turn has come
+  static constexpr int kTotal = kTurnOk + 8;
   static constexpr int kDynamic = kTotal + 1024;
 };
 
@@ -91,8 +98,22 @@ struct BwdUnit {
 template <int MODE, int YR>
 __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p) {
   BwdUnit<MODE> w;
-  const int rank = u / p.BH;
-  const int bh = u - rank * p.BH;
+  // Heaviest units first (rank = stationary tile), all (batch, head) pairs of one rank together.
+  // The fused pass does this in groups of `sched_group` (batch, KV head) pairs, so that a head's
+  // fp32 dQ sums and its tiles are still in L2 when its next key block comes round, while a key
+  // block still starts a whole wave of units after the block below it, whose dQ turns it waits for.
+  int rank, bh;
+  if (MODE == MODE_FUSED) {
+    const int per_group = p.sched_group * p.n_tiles;
+    const int g0 = (u / per_group) * p.sched_group;              // first pair of this group
+    const int size = p.BH - g0 < p.sched_group ? p.BH - g0 : p.sched_group;
+    const int v = u - (u / per_group) * per_group;
+    rank = v / size;
+    bh = g0 + (v - rank * size);
+  } else {
+    rank = u / p.BH;
+    bh = u - rank * p.BH;
+  }
   const int group = p.H / p.Hkv;
   if (MODE == MODE_DQ) {
     w.tile = p.n_tiles - 1 - rank;              // late query tiles see the most keys
@@ -115,17 +136,38 @@ __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p
     w.hk = bh - w.b * p.Hkv;
     w.h = w.hk * group;
     w.s_lo = w.tile * (kTile / YR);             // first query tile that reaches the block
-    int s_hi = p.n_ytiles - 1;
-    if (p.window > 0 && w.tile >= (p.sinks + kTile - 1) / kTile) {
-      const int last_q = w.tile * kTile + kTile - 1 + (p.window - p.sinks) - 1;
-      const int hi = last_q / YR;
-      s_hi = hi < s_hi ? hi : s_hi;
-    }
+    const int s_hi = last_query_tile_of_block(w.tile, p.n_ytiles, YR, p.window, p.sinks);
     w.extra = 0;
     w.n_inner = s_hi - w.s_lo + 1;
     w.n_iters = w.n_inner * group;
   }
   return w;
+}
+
+// Fused pass, second step: dQ from the fp32 sums.  The sums of a tile are laid out [piece of
+// four columns][row][4]; a thread takes one piece of one row, so a warp reads 512 contiguous bytes.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dq_convert_kernel(const float* __restrict__ acc, void* __restrict__ dq, int T_len, int H, int n_tiles,
+                  int d_real, float scale, long long pieces) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= pieces) return;
+  const int row = static_cast<int>(i & (kTile - 1));
+  const int piece = static_cast<int>((i >> 7) & 15);
+  const long long slot = i >> 11;                        // (b * H + h) * n_tiles + tile
+  const int tile = static_cast<int>(slot % n_tiles);
+  const long long bh = slot / n_tiles;
+  const int h = static_cast<int>(bh % H);
+  const long long b = bh / H;
+  const int qpos = tile * kTile + row;
+  const int col = 4 * piece;
+  if (qpos >= T_len || col >= d_real) return;
+  const float4 v = __ldcs(reinterpret_cast<const float4*>(acc) + i);
+  uint2 out;
+  out.x = Pack2<T>::pack(v.x * scale, v.y * scale);
+  out.y = Pack2<T>::pack(v.z * scale, v.w * scale);
+  uint8_t* dst = static_cast<uint8_t*>(dq) + (((b * T_len + qpos) * H + h) * d_real + col) * 2;
+  *reinterpret_cast<uint2*>(dst) = out;
 }
 
 // tm_x0 / tm_x1: the stationary tensors (dQ: Q, dO; dK/dV: K, V), boxes of 128 rows;
@@ -136,8 +178,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
               const __grid_constant__ CUtensorMap tm_y0, const __grid_constant__ CUtensorMap tm_y1,
               const __grid_constant__ CUtensorMap tm_out0,
               const __grid_constant__ CUtensorMap tm_out1, const BwdParams p) {
-  using L = BwdSmem<D, STAGES, XBUF, YR>;
+  using L = BwdSmem<D, STAGES, XBUF, YR, MODE == MODE_FUSED>;
   static_assert(YR == 64 || YR == 128, "streamed tiles are 64 or 128 rows");
+  static_assert(MODE != MODE_FUSED || (D == 64 && YR == 128), "the fused pass exists for 64-wide tiles");
   constexpr int kBoxes = D / 64;
   constexpr int kBoxBytes = kTile * 128;          // one 64-column box of a stationary tile
   constexpr int kYBoxBytes = YR * 128;            // ... of a streamed tile
@@ -145,10 +188,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
   constexpr bool kBf16 = Pack2<T>::kIsBf16;
   constexpr uint32_t kT1Col = YR;                 // T0 at column 0, T1 behind it
   constexpr uint32_t kOutCol = 2 * YR;
+  constexpr bool kKeyStat = MODE != MODE_DQ;         // K, V stationary (dK/dV pass, fused pass)
+  constexpr bool kFused = MODE == MODE_FUSED;        // ... and dQ formed in the same pass
   constexpr int kOutCols = MODE == MODE_DQ ? D : 2 * D;
   constexpr bool kSep = (2 * YR + kOutCols + YR) <= 512;       // room for separate P / dS columns
   constexpr uint32_t kPCol = kSep ? 2 * YR + kOutCols : 0;     // P  (dK/dV only)
   constexpr uint32_t kDsCol = kSep ? 2 * YR + kOutCols + YR / 2 : YR;
+  // Fused pass: dS^T goes to shared memory (it is the A operand of dK += dS^T Q, K-major, and of
+  // dQ = dS K, MN-major), and its TMEM columns hold the dQ accumulator instead.
+  constexpr uint32_t kDqCol = kDsCol;
   constexpr int kRing = L::kRing;
   constexpr int kRegsLaunch = 128, kRegsCompute = 200, kRegsOther = 56;    // per thread
 
@@ -163,7 +211,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
   constexpr int X_FULL = 0, X_EMPTY = XBUF, T_FULL = 2 * XBUF, T_CONSUMED = T_FULL + 1,
                 PD_FULL = T_FULL + 2, OUT_READY = T_FULL + 3, SCHED_FULL = T_FULL + 4,
                 Y_FULL = SCHED_FULL + kRing, Y_EMPTY = Y_FULL + STAGES,
-                UNIT_DONE = Y_EMPTY + STAGES, OUT_DRAINED = UNIT_DONE + 1;
+                UNIT_DONE = Y_EMPTY + STAGES, OUT_DRAINED = UNIT_DONE + 1,
+                DQ_READY = UNIT_DONE + 2, DQ_DRAINED = UNIT_DONE + 3, GROUP = UNIT_DONE + 4,
+                ISSUED = UNIT_DONE + 5;          // [4]: iteration g uses ISSUED + (g & 3)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
   volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
@@ -181,6 +231,12 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
     mbar_init(bar(OUT_READY), 1);
     mbar_init(bar(UNIT_DONE), 1);
     mbar_init(bar(OUT_DRAINED), 128);
+    mbar_init(bar(DQ_READY), 1);
+    mbar_init(bar(DQ_DRAINED), 128);
+    mbar_init(bar(GROUP), 128);
+    for (int i = 0; i < 4; ++i) mbar_init(bar(ISSUED + i), 128);
+    reinterpret_cast<volatile int*>(gen + L::kTurnOk)[0] = 0;      // iterations whose turn has come
+    reinterpret_cast<volatile int*>(gen + L::kTurnOk)[1] = 0;      // iterations whose share has been released
     for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(Y_FULL + s), 1);
@@ -225,8 +281,83 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
   // warps that shrink must free at least what the eight that grow take.
   static_assert((kRegsLaunch - kRegsOther) * 8 >= (kRegsCompute - kRegsLaunch) * 8,
                 "register reallocation does not balance");
-  if (dead || warp == 10 || warp == 11) {
+  if (dead || ((warp == 10 || warp == 11) && (!kFused || lane != 0))) {
     // nothing to do (spare warps only complete the warpgroup)
+  } else if (warp == 10 || warp == 11) {
+    // ===================== fused pass: turn watcher (warp 10), releaser (warp 11) ==================
+    // The dQ shares of a query tile are added to its fp32 sums in a fixed order -- ascending key
+    // block, see dq_turn_of_block -- kept by a turn counter per (batch, head, query tile) in
+    // global memory.  Two lanes keep the latency of that protocol off the drain warps' path:
+    //  * the watcher goes through this CTA's iterations ahead of the drain warps, waits until the
+    //    counter of each says that the blocks before this one have added their shares, and
+    //    publishes how far it has got in shared memory;
+    //  * the releaser waits until the drain warps have issued an iteration's share, makes those
+    //    writes visible (the threads' arrivals on the barrier order them before this lane's
+    //    fence, which is cumulative) and advances the tile's counter.  It never waits for another
+    //    CTA and holds nothing back, so no cycle of waits between CTAs can form.
+    // Work units are handed out in ascending key-block order (within a group of heads) and every
+    // CTA of the launch is resident, so a turn only ever waits for a unit that was started earlier.
+    const bool watcher = warp == 10;
+    volatile int* turn_ok = reinterpret_cast<volatile int*>(gen + L::kTurnOk);
+    volatile int* released = turn_ok + 1;
+    bool ok = true;
+    int git = 0;
+    // the releaser collects up to three issued iterations before it pays for one fence
+    unsigned* batch_turn[3];
+    unsigned batch_value[3];
+    int n_batch = 0;
+    auto flush_batch = [&]() {
+      if (n_batch == 0) return;
+      __threadfence();
+      for (int i = 0; i < n_batch; ++i) st_release_gpu(batch_turn[i], batch_value[i]);
+      *released = git;                  // (git counts the iterations taken into batches so far)
+      n_batch = 0;
+    };
+    for (int uc = 0; ok; ++uc) {
+      BwdUnit<MODE> w;
+      const int u = next_unit(uc, ok, w);
+      if (!ok || u < 0) break;
+      int inner = 0, gq = 0;
+      for (int it = 0; ok && it < w.n_iters; ++it, ++inner) {
+        if (inner == w.n_inner) { inner = 0; ++gq; }
+        const int qt = w.s_lo + inner;
+        int n_blocks;
+        const int order = dq_turn_of_block(w.tile, qt, p.window, p.sinks, &n_blocks);
+        unsigned* turn = p.dq_turn + (static_cast<long long>(w.b) * p.H + (w.h + gq)) * p.n_tiles + qt;
+        if (watcher) {
+          if (order > 0) {
+            const unsigned long long t0 = globaltimer_ns();
+            for (uint32_t spins = 1; ld_acquire_gpu(turn) < static_cast<unsigned>(order); ++spins) {
+              __nanosleep(64);
+              if ((spins & 0x3fu) == 0u) {
+                if (*abort_flag) { ok = false; break; }
+                if (globaltimer_ns() - t0 > wctx.limit()) {
+                  *abort_flag = 1;
+                  report_timeout(p.status, STATUS_WAIT_TIMEOUT | 44u);
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (!ok) break;
+          }
+          __threadfence_block();                               // the acquire above before the flag below
+          ++git;
+          *turn_ok = git;
+        } else {
+          const uint32_t b = bar(ISSUED + (git & 3)), parity = (git >> 2) & 1;
+          if (!mbar_try_wait(b, parity)) {
+            flush_batch();                                     // nothing more to collect: release what there is
+            if (!(ok = mbar_wait_idle(b, parity, wctx, 45))) break;
+          }
+          ++git;
+          batch_turn[n_batch] = turn;
+          batch_value[n_batch] = static_cast<unsigned>(order) + 1u;
+          if (++n_batch == 3) flush_batch();
+        }
+      }
+    }
+    if (!watcher && ok) flush_batch();
   } else if (warp >= 12) {
     // ================================ epilogue ===============================
     // One thread per row of the unit's output tiles.  When the unit's last output product has
@@ -238,11 +369,82 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
     const int row = 32 * (warp & 3) + lane;
     const uint32_t sw = static_cast<uint32_t>(row & 7);
     bool ok = true;
+    // Fused pass: the same warps also carry every iteration's dQ share out of TMEM (below).
+    int git = 0;                            // global iteration
+    // Barrier among the four warps of this role, on an mbarrier so that the wait is bounded like
+    // every other.  Its result is uniform within a warp and false once anything in the CTA has
+    // given up (giving up raises the abort flag), so whole warps leave, never single lanes, and
+    // the warps that still wait for them follow at once.
+    uint32_t group_phase = 0;
+    auto group_sync = [&](unsigned where) {
+      mbar_arrive(bar(GROUP));
+      const bool done = mbar_wait(bar(GROUP), group_phase & 1u, wctx, where);
+      ++group_phase;
+      ok = __all_sync(0xffffffffu, done && *abort_flag == 0);
+    };
     for (int uc = 0; ok; ++uc) {
       BwdUnit<MODE> w;
       const int u = next_unit(uc, ok, w);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok || u < 0) break;
+      if constexpr (kFused) {
+        // dQ of query tile i is the sum over the key blocks j that see it of dS_ij K_j.  Each
+        // iteration leaves one such share (128 x 64 fp32) in TMEM.  These warps pull it into
+        // registers (which frees the accumulator) and add it to the tile's fp32 sums in global
+        // memory with vector reductions -- or store it, if it is the tile's first share, so that
+        // nothing has to be zero-filled -- once the watcher says that the tile's earlier shares
+        // are in (see above; normally they have been for a long time).  The sums are laid out
+        // [piece of 4 columns][row][4]: a warp's 32 rows of one piece are 512 contiguous bytes.
+        volatile int* turn_ok = reinterpret_cast<volatile int*>(gen + L::kTurnOk);
+        int inner = 0, gq = 0;
+        for (int it = 0; it < w.n_iters; ++it, ++git, ++inner) {
+          if (inner == w.n_inner) { inner = 0; ++gq; }
+          const int qt = w.s_lo + inner;                       // query tile of this iteration
+          int n_blocks;
+          const int order = dq_turn_of_block(w.tile, qt, p.window, p.sinks, &n_blocks);
+          const long long slot = (static_cast<long long>(w.b) * p.H + (w.h + gq)) * p.n_tiles + qt;
+          float4* acc = reinterpret_cast<float4*>(p.dq_acc + slot * (kTile * D)) + row;
+          ok = mbar_wait(bar(DQ_READY), git & 1, wctx, 43);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          // rare: the watcher is still waiting for this turn, or the releaser is four shares behind
+          if (turn_ok[0] <= git || turn_ok[1] + 4 <= git) {
+            const unsigned long long t0 = globaltimer_ns();
+            for (uint32_t spins = 1; turn_ok[0] <= git || turn_ok[1] + 4 <= git; ++spins) {
+              __nanosleep(64);
+              if ((spins & 0x3fu) == 0u && (*abort_flag || globaltimer_ns() - t0 > wctx.limit())) {
+                ok = false;                                    // (the watcher reports its own timeouts)
+                break;
+              }
+            }
+          }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          __threadfence_block();
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_addr(tmem, lane_base, kDqCol + c), r);
+            tc_wait_ld();
+            if (c + 32 >= D) {
+              tc_fence_before();
+              mbar_arrive(bar(DQ_DRAINED));       // the next iteration's dQ product may be issued
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4* dst = acc + (c / 4 + i) * kTile;
+              if (order == 0)
+                *dst = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                   __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+              else
+                red_add_f32x4(dst, r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            }
+          }
+          mbar_arrive(bar(ISSUED + (git & 3)));                // the releaser takes it from here
+        }
+        if (!ok) break;
+      }
       ok = mbar_wait_idle(bar(UNIT_DONE), uc & 1, wctx, 41);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -252,8 +454,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
 #pragma unroll 1
       for (int c = 0; c < kOutCols; c += 32) {
         // dK/dV: columns [0, D) are dV (over the V tile), [D, 2D) are dK (over the K tile, scaled)
-        const bool second = MODE == MODE_DKV && c >= D;
-        const uint32_t tile_base = (MODE == MODE_DKV && !second) ? stage0 + L::kTileBytes : stage0;
+        const bool second = kKeyStat && c >= D;
+        const uint32_t tile_base = (kKeyStat && !second) ? stage0 + L::kTileBytes : stage0;
         const float mul = (MODE == MODE_DQ || second) ? p.scale : 1.f;
         const int col0 = second ? c - D : c;
         uint32_t r[32];
@@ -277,12 +479,13 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         }
       }
       fence_proxy_async_smem();
-      named_barrier(1, 128);
+      group_sync(48);
+      if (!ok) break;
       if (warp == 12 && lane == 0) {
         const int oh = MODE == MODE_DQ ? w.h : w.hk;
         for (int x = 0; x < kBoxes; ++x) {
           tma_store_4d(&tm_out0, stage0 + x * kBoxBytes, 64 * x, oh, w.tile * kTile, w.b);
-          if (MODE == MODE_DKV)
+          if (kKeyStat)
             tma_store_4d(&tm_out1, stage0 + L::kTileBytes + x * kBoxBytes, 64 * x, oh,
                          w.tile * kTile, w.b);
         }
@@ -368,7 +571,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
                         idx * YR, w.b);
           }
         }
-        if (MODE == MODE_DKV) {
+        if (kKeyStat) {
           // negated base-2 logsumexp and negated Delta of the streamed query tile
           float* vec = reinterpret_cast<float*>(gen + L::kVec + s * 1024);
           const long long row0 = (static_cast<long long>(w.b) * p.H + yh) * p.T;
@@ -404,6 +607,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         ok = __all_sync(0xffffffffu, ok);
         return u;
       };
+      bool ok = true;
       constexpr uint32_t idesc_t = make_idesc(kBf16, 128, YR, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBf16, 128, D, false, true);
 
@@ -428,7 +632,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         }
         umma_commit(leader, bar(T_FULL));
       };
-      auto issue_out = [&](int g, uint32_t acc) {
+      constexpr uint32_t idesc_dq = make_idesc(kBf16, 128, D, true, true);
+      auto issue_out = [&](int xb, int g, uint32_t acc) {
         const int s = g % STAGES;
         const uint32_t y0 = base + L::kY + s * 2 * L::kYTileBytes, y1 = y0 + L::kYTileBytes;
         // 16-bit operand of k-step kk: 8 TMEM columns per step.  The dV and dK steps alternate,
@@ -444,16 +649,37 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
           } else {
             umma_ts(leader, tmem + kOutCol, tmem + kPCol + acol,
                    make_smem_desc(y1 + kk * 2048, kYBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
-            umma_ts(leader, tmem + kOutCol + D, tmem + kDsCol + acol,
-                   make_smem_desc(y0 + kk * 2048, kYBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
+            if constexpr (kFused) {
+              // dK += dS^T Q: dS^T from shared memory, K-major (16 queries = 32 bytes per step)
+              const uint32_t ds = base + L::kDs + (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+              umma_ss(leader, tmem + kOutCol + D, make_smem_desc(ds, 16, 1024),
+                     make_smem_desc(y0 + kk * 2048, kYBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
+            } else {
+              umma_ts(leader, tmem + kOutCol + D, tmem + kDsCol + acol,
+                     make_smem_desc(y0 + kk * 2048, kYBoxBytes, 1024), idesc_o, (acc | (kk > 0)) ? 1u : 0u);
+            }
+          }
+        }
+        if constexpr (kFused) {
+          // dQ share of this (key block, query tile): dS K, the same dS^T tile read MN-major
+          // (queries along M, 16 keys = 16 rows per step), K_j MN-major as the B operand.  The
+          // accumulator is free once the drain warps have pulled the previous share out.
+          if (g > 0) ok = wait_all(bar(DQ_DRAINED), (g - 1) & 1, 49);
+          if (ok) {
+            tc_fence_after();
+            const uint32_t x0 = base + L::kX + xb * 2 * L::kTileBytes;
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              umma_ss(leader, tmem + kDqCol, make_smem_desc(base + L::kDs + kk * 2048, kBoxBytes, 1024),
+                     make_smem_desc(x0 + kk * 2048, kBoxBytes, 1024), idesc_dq, kk > 0 ? 1u : 0u);
           }
         }
         umma_commit(leader, bar(OUT_READY));
+        if constexpr (kFused) umma_commit(leader, bar(DQ_READY));
         umma_commit(leader, bar(Y_EMPTY + s));
       };
 
       // cursor over (unit, iteration); `nxt` runs one global iteration ahead of `cur`
-      bool ok = true;
       int uc = 0;                       // units fetched so far
       int cur_n = 0, cur_it = 0, cur_xb = 0;
       int cur_u = next_unit_all(uc, ok, cur_n);
@@ -505,7 +731,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
           if (!(ok = wait_all(bar(OUT_DRAINED), (cur_uc - 1) & 1, 42))) break;
           tc_fence_after();
         }
-        issue_out(g, cur_it > 0 ? 1u : 0u);
+        issue_out(cur_xb, g, cur_it > 0 ? 1u : 0u);
+        if (!ok) break;
         if (cur_it + 1 == cur_n) {
           umma_commit(leader, bar(X_EMPTY + cur_xb));
           umma_commit(leader, bar(UNIT_DONE));
@@ -743,11 +970,23 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         // the previous iteration's output products must be done reading P / dS
         wait_out(g);
         if (!ok) break;
-        if constexpr (kCh == 2) {
-          if (MODE == MODE_DKV) tmem_st32(p_dst, pp);
+        if constexpr (kFused) {
+          // P^T to TMEM as before; dS^T to shared memory as a 128B-swizzled [keys][queries] tile
+          // (this thread's 64 queries are one 128-byte row of box `half`)
+          tmem_st32(p_dst, pp);
+          const uint32_t ds_row = base + L::kDs + static_cast<uint32_t>(half) * kBoxBytes +
+                                  static_cast<uint32_t>(row) * 128u;
+          const uint32_t sw = static_cast<uint32_t>(row & 7);
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            st_shared_v4(ds_row + ((static_cast<uint32_t>(c) ^ sw) << 4), dd[4 * c], dd[4 * c + 1],
+                         dd[4 * c + 2], dd[4 * c + 3]);
+          fence_proxy_async_smem();
+        } else if constexpr (kCh == 2) {
+          if (kKeyStat) tmem_st32(p_dst, pp);
           tmem_st32(ds_dst, dd);
         } else {
-          if (MODE == MODE_DKV) tmem_st16(p_dst, pp);
+          if (kKeyStat) tmem_st16(p_dst, pp);
           tmem_st16(ds_dst, dd);
         }
         tc_wait_st();
@@ -782,7 +1021,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
 template <typename T, int D, int MODE, int STAGES, int XBUF, int YR>
 int launch_mode(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                 const float* lse, const float* delta, void* out0, void* out1, unsigned* status,
-                cudaStream_t stream) {
+                cudaStream_t stream, void* dq = nullptr, const FusedScratch* fused = nullptr) {
   // stationary tensors in boxes of 128 rows, streamed tensors in boxes of YR rows; output tiles
   // leave through TMA stores: dQ is [B,T,H,D], dK and dV are [B,T,Hkv,D]
   const void* x0 = MODE == MODE_DQ ? q : k;
@@ -800,7 +1039,8 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   if (mst == NLFA_OK)
     mst = make_tile_map(&mo1, MODE == MODE_DQ ? out0 : out1, p.dtype, p.B, p.T, x_heads, p.D, kTile);
   if (mst != NLFA_OK) return mst;
-  using L = BwdSmem<D, STAGES, XBUF, YR>;
+  using L = BwdSmem<D, STAGES, XBUF, YR, MODE == MODE_FUSED>;
+  static_assert(L::kDynamic <= 232448, "over the shared memory a CTA can have");
   auto kern = bwd_tc_kernel<T, D, MODE, STAGES, XBUF, YR>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kDynamic) != NLFA_OK)
     return NLFA_ERR_CUDA;
@@ -821,18 +1061,42 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   bp.out0 = out0;
   bp.out1 = out1;
   bp.status = status;
+  bp.dq_acc = fused ? fused->dq_acc : nullptr;
+  bp.dq_turn = fused ? fused->dq_turn : nullptr;
+  if (MODE == MODE_FUSED) {
+    if (fused == nullptr || dq == nullptr) return NLFA_ERR_NULL_POINTER;
+    // every (batch, head, query tile) starts with no share added
+    if (cudaMemsetAsync(fused->dq_turn, 0, sizeof(unsigned) * static_cast<size_t>(p.B) * p.H * bp.n_tiles,
+                        stream) != cudaSuccess)
+      return NLFA_ERR_CUDA;
+  }
   const int sst = sched_counters(stream, &bp.sched);
   if (sst != NLFA_OK) return sst;
   const int grid = bp.total_units < sm_count() ? bp.total_units : sm_count();
+  bp.sched_group = grid;
   kern<<<grid, 512, L::kDynamic, stream>>>(mx0, mx1, my0, my1, mo0, mo1, bp);
-  return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
+  if (cudaGetLastError() != cudaSuccess) return NLFA_ERR_CUDA;
+  if (MODE == MODE_FUSED) {
+    // the fp32 sums, complete now, become dQ: scaled, converted, rows put back in order
+    const long long pieces = static_cast<long long>(p.B) * p.H * bp.n_tiles * kTile * 16;
+    dq_convert_kernel<T><<<static_cast<unsigned>((pieces + 255) / 256), 256, 0, stream>>>(
+        fused->dq_acc, dq, p.T, p.H, bp.n_tiles, p.D, p.scale, pieces);
+    if (cudaGetLastError() != cudaSuccess) return NLFA_ERR_CUDA;
+  }
+  return NLFA_OK;
 }
 
 template <typename T, int D, int STAGES, int XBUF, int YR>
 int launch_both(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                 const float* lse, const float* delta, void* dq, void* dk, void* dv, int passes,
-                unsigned* status, cudaStream_t stream) {
+                unsigned* status, cudaStream_t stream, const FusedScratch* fused) {
   int st = NLFA_OK;
+  if constexpr (D == 64 && YR == 128) {
+    // one pass for all three gradients: three streamed stages (the dS tile takes the fourth's room)
+    if (passes & NLFA_PASS_FUSED)
+      return launch_mode<T, D, MODE_FUSED, 3, XBUF, YR>(p, dout, q, k, v, lse, delta, dk, dv, status, stream,
+                                                       dq, fused);
+  }
   if (passes & NLFA_PASS_DKV)
     st = launch_mode<T, D, MODE_DKV, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dk, dv, status, stream);
   if (st != NLFA_OK) return st;
@@ -845,9 +1109,10 @@ int launch_both(const Problem& p, const void* dout, const void* q, const void* k
 
 int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                   const void* o, const float* lse, void* dq, void* dk, void* dv, float* delta,
-                  int passes, unsigned* status, cudaStream_t stream) {
+                  int passes, unsigned* status, cudaStream_t stream, const FusedScratch* fused) {
   if (p.dtype != NLFA_DTYPE_F16 && p.dtype != NLFA_DTYPE_BF16) return NLFA_ERR_UNSUPPORTED_PATH;
   if (p.D != 32 && p.D != 64 && p.D != 128) return NLFA_ERR_UNSUPPORTED_PATH;
+  if ((passes & NLFA_PASS_FUSED) && p.D > 64) return NLFA_ERR_UNSUPPORTED_PATH;
   // Head dim 32 runs the 64-wide kernels: the tensor maps describe the real 32 columns, the
   // TMA boxes are 64 wide, so loads fill columns 32-63 with zeros (which add nothing to any
   // product) and stores drop them.
@@ -857,14 +1122,14 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D <= 64) {
     // 128-row streamed tiles, four stages, two stationary buffers
-    return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream)
-                : launch_both<__half, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream);
+    return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused)
+                : launch_both<__half, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused);
   }
   // D = 128: shared memory holds one stationary pair (64 KB) and 128 KB of streamed tiles.
   // As 64-row tiles that is four stages in flight instead of two, and the narrower T tiles
   // leave TMEM columns for separate P / dS operands, i.e. for the one-iteration lookahead.
-  return bf16 ? launch_both<__nv_bfloat16, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream)
-              : launch_both<__half, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream);
+  return bf16 ? launch_both<__nv_bfloat16, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused)
+              : launch_both<__half, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused);
 }
 
 

@@ -91,6 +91,29 @@ __host__ __device__ inline int rect_edges(int q_lo, int q_hi, int k_lo, int k_hi
   return EDGE_BOTH;
 }
 
+// Key-block-stationary passes (dK/dV, fused): the last streamed query tile (of `rows` rows each,
+// `n_ytiles` in all) that reaches 128-key block `block`; the first is block * (128 / rows).
+__host__ __device__ inline int last_query_tile_of_block(int block, int n_ytiles, int rows, int window,
+                                                        int sinks) {
+  int hi = n_ytiles - 1;
+  if (window > 0 && block >= (sinks + kTile - 1) / kTile) {      // blocks with sink keys are seen by all
+    const int last_q = block * kTile + kTile - 1 + (window - sinks) - 1;
+    hi = last_q / rows < hi ? last_q / rows : hi;
+  }
+  return hi;
+}
+
+// Fused backward: key block `block`'s place in the fixed order in which the blocks that see
+// 128-row query tile `tile` add their dQ shares (ascending block index: sink blocks below the
+// window first, then the window's blocks up to the diagonal, which closes the sum).  *count is
+// the number of such blocks.
+__host__ __device__ inline int dq_turn_of_block(int block, int tile, int window, int sinks, int* count) {
+  const TileRange r = tile_range(tile, window, sinks);
+  const int extra = r.sink_blocks < r.lo ? r.sink_blocks : r.lo;
+  *count = extra + (tile - r.lo + 1);
+  return block < extra ? block : extra + (block - r.lo);
+}
+
 __host__ __device__ inline bool key_visible(int q, int k, int window, int sinks) {
   if (k > q) return false;
   if (window == 0) return true;
@@ -107,9 +130,15 @@ int launch_delta(const Problem& p, const void* dout, const void* o, float* delta
                  cudaStream_t stream);
 int launch_fwd_tc(const Problem& p, const void* q, const void* k, const void* v, void* o,
                   float* lse, unsigned* status, cudaStream_t stream);
+// Scratch of the fused backward pass (head dim <= 64), behind the Delta tape in the caller's
+// buffer: per (batch, head, 128-row query tile) a turn counter and 128 x 64 fp32 partial sums.
+struct FusedScratch {
+  float* dq_acc;
+  unsigned* dq_turn;
+};
 int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                   const void* o, const float* lse, void* dq, void* dk, void* dv, float* delta,
-                  int passes, unsigned* status, cudaStream_t stream);
+                  int passes, unsigned* status, cudaStream_t stream, const FusedScratch* fused);
 int launch_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, const void* v,
                           float* s_out, float* o_out, unsigned* status, cudaStream_t stream);
 

@@ -52,7 +52,8 @@ struct FwdSmem {
   // barriers (8 bytes each): q_full[QBUF], q_empty[QBUF], s_full[NT], s_consumed[NT],
   // p_full[NT], o_ready[NT], k_full[S], k_empty[S], v_full[S], v_empty[S], sched_full[kRing]
   static constexpr int kRing = 8;
-  static constexpr int kNumBars = 2 * QBUF + 4 * NT + 4 * STAGES + kRing;
+  // ..., group[NT]
+  static constexpr int kNumBars = 2 * QBUF + 4 * NT + 4 * STAGES + kRing + NT;
   static constexpr int kSched = (kBar + 8 * kNumBars + 15) / 16 * 16;   // ring of unit descriptors (16 ints each)
   static constexpr int kTmemSlot = kSched + 64 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
@@ -138,7 +139,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   constexpr int Q_FULL = 0, Q_EMPTY = QBUF, S_FULL = 2 * QBUF, S_CONSUMED = S_FULL + NT,
                 P_FULL = S_CONSUMED + NT, O_READY = P_FULL + NT, K_FULL = O_READY + NT,
                 K_EMPTY = K_FULL + STAGES, V_FULL = K_EMPTY + STAGES, V_EMPTY = V_FULL + STAGES,
-                SCHED_FULL = V_EMPTY + STAGES;
+                SCHED_FULL = V_EMPTY + STAGES, GROUP = SCHED_FULL + kRing;
   volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
@@ -158,6 +159,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       mbar_init(bar(S_CONSUMED + t), 128);
       mbar_init(bar(P_FULL + t), 128);
       mbar_init(bar(O_READY + t), 1);
+      mbar_init(bar(GROUP + t), 128);
     }
     for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -482,6 +484,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t p_addr = tmem_addr(tmem, lane_base, kSepP ? kPBase + 64 * t : 128 * t);
     const uint64_t scale2 = pack_f2(p.scale_log2, p.scale_log2);
     int s_count = 0, o_count = 0;      // S_FULL / O_READY phases this thread has observed
+    uint32_t group_phase = 0;          // uses of this warpgroup's barrier (GROUP + t)
     // With two Q buffers the thread that issued a tile's TMA store does not wait for it on the
     // spot (that would hold up its whole warpgroup); it releases the buffer one block later,
     // when the store has long finished reading shared memory.
@@ -693,7 +696,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      named_barrier(1 + t, 128);
+      // the warpgroup's four warps meet on an mbarrier, so that this wait is bounded like every
+      // other: its result is false once anything in the CTA has given up, and then whole warps leave
+      mbar_arrive(bar(GROUP + t));
+      ok = mbar_wait(bar(GROUP + t), group_phase & 1u, wctx, 14);
+      ++group_phase;
+      ok = __all_sync(0xffffffffu, ok && *abort_flag == 0);
+      if (!ok) break;
       if (row == 0) {
         for (int x = 0; x < kBoxes; ++x)
           tma_store_4d(&tm_o, stage + x * kBoxBytes, 64 * x, w.h, tile * kTile, w.b);

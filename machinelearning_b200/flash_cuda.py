@@ -41,6 +41,11 @@ MMA_DTYPES = (torch.float16, torch.bfloat16)      # tcgen05 kind::f16 operands
 MMA_HEAD_DIMS = (32, 64, 128)
 MMA_BWD_HEAD_DIMS = (32, 64, 128)
 _PROBE_HEAD_DIMS = (64, 128)                      # kernel instantiations the load-time probe runs
+# Backward layout on the tensor-core path at head dims up to 64: the reference's two independent
+# passes, or -- with NLFA_FUSED_BACKWARD=1 -- one pass that forms dQ inside the dK/dV pass.  Both
+# are bit-reproducible; on B200 the two passes are the faster ones at these head dims (the one
+# pass saves the second computation of P and dS but pays for a reduction of dQ across CTAs).
+FUSED_BACKWARD = os.environ.get("NLFA_FUSED_BACKWARD", "0") == "1"
 
 _DTYPE_CODE = {torch.float32: _lib.DTYPE_F32, torch.float16: _lib.DTYPE_F16,
                torch.bfloat16: _lib.DTYPE_BF16}
@@ -59,16 +64,20 @@ def _watch_device(lib, index: int) -> None:
     with no synchronisation on the hot path."""
     if index in _status_words:
         return
+    import ctypes
     word = torch.zeros(1, dtype=torch.int32).pin_memory()
     with torch.cuda.device(index):
         st = lib.nlfa_set_status_mirror(word.data_ptr())
     _lib.check("nlfa_set_status_mirror", st)
+    word.view = ctypes.c_uint.from_address(word.data_ptr())      # read without going through torch
     _status_words[index] = word
 
 
 def device_timed_out() -> bool:
     """True when a kernel on any watched device has given up a wait since the last reset."""
-    return any(int(w[0]) != 0 for w in _status_words.values())
+    if torch.compiler.is_compiling():          # a traced caller is checked when it runs, by the C entry points
+        return False
+    return any(w.view.value != 0 for w in _status_words.values())
 
 
 def reset_device_status() -> int:
@@ -234,8 +243,14 @@ def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0):
     return o, lse
 
 
-def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sinks: int = 0):
-    """(dQ, dK, dV) through the C ABI (reference: ``flash_attn_cuda.cu:1744-1813``)."""
+def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sinks: int = 0,
+        fused: bool | None = None):
+    """(dQ, dK, dV) through the C ABI (reference: ``flash_attn_cuda.cu:1744-1813``).
+
+    ``fused`` picks the backward's layout on the tensor-core path at head dims up to 64: the
+    reference's two independent passes (``nlfa_bwd``; the default) or one pass that forms dQ inside
+    the dK/dV pass (``nlfa_bwd_fused``).  Both are bit-reproducible.  Elsewhere there are only the
+    two passes."""
     lib = _load()
     if lib is None:
         raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
@@ -243,17 +258,23 @@ def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sin
     Hkv = k.shape[2]
     if q.device.index not in _status_words:
         _watch_device(lib, q.device.index)
+    can_fuse = bool(use_mma) and D <= 64
+    if fused is None:
+        fused = can_fuse and FUSED_BACKWARD
+    elif fused and not can_fuse:
+        raise ValueError("the fused backward exists on the tensor-core path for head dims up to 64")
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    nbytes = lib.nlfa_bwd_scratch_bytes(B, T, H)
-    scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=q.device)
+    nbytes = lib.nlfa_bwd_fused_scratch_bytes(B, T, H, D) if fused else lib.nlfa_bwd_scratch_bytes(B, T, H)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    entry = lib.nlfa_bwd_fused if fused else lib.nlfa_bwd
     with torch.cuda.device(q.device):
-        st = lib.nlfa_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                          lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                          scratch.data_ptr(), scratch.numel(), B, T, H, Hkv, D, float(scale),
-                          int(window), int(sinks), _DTYPE_CODE[q.dtype],
-                          _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
-                          torch.cuda.current_stream().cuda_stream)
-    _lib.check("nlfa_bwd", st)
+        st = entry(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                   lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                   scratch.data_ptr(), scratch.numel(), B, T, H, Hkv, D, float(scale),
+                   int(window), int(sinks), _DTYPE_CODE[q.dtype],
+                   _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
+                   torch.cuda.current_stream().cuda_stream)
+    _lib.check("nlfa_bwd_fused" if fused else "nlfa_bwd", st)
     return dq, dk, dv
 
 

@@ -42,7 +42,7 @@ def test_ctypes_signatures_cover_the_header():
 def test_strerror_and_version(lib):
     assert lib.nlfa_version() >= 1
     assert lib.nlfa_strerror(0) == b"ok"
-    for code in range(1, 13):
+    for code in range(1, 16):
         assert lib.nlfa_strerror(code) not in (b"", b"ok", b"unknown status")
     assert lib.nlfa_strerror(999) == b"unknown status"
 
@@ -80,6 +80,17 @@ def test_argument_checks_answer_without_a_gpu(lib):
     bwd = lib.nlfa_bwd(one, one, one, one, one, one, one, one, one, one, 8, 1, 8, 2, 1, 64,
                        0.125, 0, 0, L.DTYPE_F32, L.PATH_AUTO, None)
     assert bwd == 11                                        # scratch too small
+    # the one-pass backward: its own scratch size, refusals before anything touches a device
+    tape = lib.nlfa_bwd_scratch_bytes(2, 300, 4)
+    assert lib.nlfa_bwd_fused_scratch_bytes(2, 300, 4, 128) == (tape + 255) // 256 * 256      # no fused pass at 128
+    tiles = 2 * 4 * 3
+    assert lib.nlfa_bwd_fused_scratch_bytes(2, 300, 4, 64) == (tape + 255) // 256 * 256 + 256 + tiles * 128 * 64 * 4
+    passes = lambda mask, D=64, dtype=L.DTYPE_BF16, path=L.PATH_TENSOR, nbytes=1 << 30: lib.nlfa_bwd_passes(
+        one, one, one, one, one, one, one, one, one, one, nbytes, 1, 300, 2, 1, D, 0.125, 0, 0, dtype, path, mask, None)
+    assert passes(L.PASS_FUSED | L.PASS_DKV) == 7 and passes(L.PASS_FUSED | L.PASS_DQ) == 7 and passes(16) == 7
+    assert passes(L.PASS_FUSED, D=128) == 7                 # tensor-core path, head dims up to 64 only
+    assert passes(L.PASS_FUSED, dtype=L.DTYPE_F32, path=L.PATH_AUTO) == 7
+    assert passes(L.PASS_FUSED, nbytes=lib.nlfa_bwd_scratch_bytes(1, 300, 2)) == 11
     errs = (ctypes.c_float * 2)()
     assert lib.nlfa_selftest(L.DTYPE_BF16, 64, one, 16, errs, None) == 11
     assert lib.nlfa_selftest(L.DTYPE_F32, 64, one, 1 << 20, errs, None) == 7

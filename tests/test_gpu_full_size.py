@@ -11,12 +11,15 @@ from oracle import attention_f64 as orc
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def fc():
+@pytest.fixture(scope="module", params=["one_pass_backward", "two_pass_backward"])
+def fc(request):
     from machinelearning_b200 import flash_cuda
     assert flash_cuda.is_available(), flash_cuda.unavailable_reason()
     assert flash_cuda.mma_available(), flash_cuda.mma_unavailable_reason()
-    return flash_cuda
+    before = flash_cuda.FUSED_BACKWARD
+    flash_cuda.FUSED_BACKWARD = request.param == "one_pass_backward"
+    yield flash_cuda
+    flash_cuda.FUSED_BACKWARD = before
 
 
 def sample_heads(B, H, n, seed=0):

@@ -21,13 +21,18 @@ REL_16BIT = 2e-2
 ABS_F32 = 1e-5
 
 
-@pytest.fixture(scope="module")
-def fc():
+@pytest.fixture(scope="module", params=["one_pass_backward", "two_pass_backward"])
+def fc(request):
+    """The module under both backward layouts the tensor-core path has at head dims up to 64: dQ
+    formed inside the dK/dV pass (the default), and the reference's two independent passes."""
     from machinelearning_b200 import flash_cuda
     assert torch.cuda.is_available(), "these tests need a CUDA device"
     assert flash_cuda.is_available(), flash_cuda.unavailable_reason()
     assert flash_cuda.mma_available(), flash_cuda.mma_unavailable_reason()
-    return flash_cuda
+    before = flash_cuda.FUSED_BACKWARD
+    flash_cuda.FUSED_BACKWARD = request.param == "one_pass_backward"
+    yield flash_cuda
+    flash_cuda.FUSED_BACKWARD = before
 
 
 def rel(got, ref):
