@@ -5,8 +5,11 @@
 
 A step is one forward plus one backward of the causal bf16 attention path over
 one batch of synthetic input (B=32, H=12, T=1024, D=64, scale 1/8: the nanolab
-124M-model shape).  Each rank owns its own batch (weak scaling: the path shards
-by batch x head with no exchange step), so N ranks process N batches per step.
+124M-model shape).  With N ranks that batch is partitioned (``sharding.plan``:
+32 / N batch elements per GPU, no exchange step in the path: strong scaling);
+after the timed region the shards of O, LSE, dQ, dK and dV are gathered over
+NCCL and compared, bit for bit, with rank 0's own run of the whole batch.  The
+figure for N full batches on N GPUs (weak scaling) rides along as ``weak``.
 
 Prints one JSON line:
   value      whole-job TFLOP/s, algorithmic FLOPs (2 forward + 5 backward GEMMs
@@ -46,16 +49,17 @@ ROOT = pathlib.Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 WORKLOADS = {
-    # name: (B, T, H, Hkv, D, window, sinks)
+    # name: (B, T, H, Hkv, D, window, sinks): the whole job's shape; N GPUs split B
     "c2": (32, 1024, 12, 12, 64, 0, 0),
     "c3": (16, 4096, 16, 16, 64, 256, 0),
-    "c5": (1, 16384, 16, 16, 128, 0, 0),      # one batch element of B=8 per GPU
+    "c5": (8, 16384, 16, 16, 128, 0, 0),
 }
 WORKLOAD_TEXT = {
-    "c2": "causal bf16 attention fwd+bwd, B=32 H=12 T=1024 D=64, scale 1/8 (per GPU)",
-    "c3": "sliding-window bf16 attention fwd+bwd, B=16 H=16 T=4096 D=64 window=256 (per GPU)",
-    "c5": "long-context causal bf16 attention fwd+bwd, B=1 of 8, H=16 T=16384 D=128 (per GPU)",
+    "c2": "causal bf16 attention fwd+bwd, B=32 H=12 T=1024 D=64, scale 1/8",
+    "c3": "sliding-window bf16 attention fwd+bwd, B=16 H=16 T=4096 D=64 window=256",
+    "c5": "long-context causal bf16 attention fwd+bwd, B=8 H=16 T=16384 D=128, scale 1/sqrt(128)",
 }
+ALGORITHMIC_BYTES_PER_ELEMENT = 2      # every tensor of the path is bf16; LSE and Delta are fp32 rows
 WHOLE_MODEL = "c4"
 WHOLE_MODEL_TEXT = ("nanolab GPT training step, flash_cuda on: 12 layers d_model=768 12x64 heads RoPE RMSNorm "
                     "QK-norm SwiGLU(2048) vocab=50304 context=1024, global batch 64 sequences, bf16 autocast, "
@@ -80,6 +84,14 @@ def flops(B, T, H, D, window, sinks):
     """(forward, backward) algorithmic FLOPs: 2 and 5 GEMMs over the unmasked pairs."""
     n = pairs(T, window, sinks)
     return 4.0 * D * n * B * H, 10.0 * D * n * B * H
+
+
+def measured_hbm():
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(path.read_text())["hbm_gbs"])
+    except Exception:                                             # noqa: BLE001
+        return 6650.0
 
 
 def measured_peak():
@@ -166,10 +178,19 @@ def make_inputs(shape, seed, device, pin=False):
 # CPU arm: the reference's own attention path on host cores
 # ----------------------------------------------------------------------------
 
-def cpu_fwd_bwd_tflops(shape, sample_batch, reps, warmup=1):
+def cpu_sample_batch(shape):
+    """Batch elements of the workload one CPU step covers (a bounded sample: seconds, not minutes)."""
+    B, T = shape[0], shape[1]
+    return 1 if T > 8192 else max(1, B // 4)
+
+
+def cpu_fwd_bwd_tflops(shape, reps, warmup):
+    """The reference's CPU attention (``oracle/sdpa_port.py``: torch SDPA + autograd, the chunked
+    window path for SWA) on all host cores, over a sample of the batch: median of ``reps`` timed
+    forward+backward runs after ``warmup`` untimed ones.  Both arms measure it this way."""
     from oracle import sdpa_port            # test infrastructure: only timed here, never shipped
     B, T, H, Hkv, D, window, sinks = shape
-    sb = min(sample_batch, B)
+    sb = cpu_sample_batch(shape)
     torch.set_num_threads(os.cpu_count() or 1)
     q, k, v, do = make_inputs((sb, T, H, Hkv, D, window, sinks), 1234, "cpu")
     scale = 1.0 / math.sqrt(D)
@@ -185,34 +206,29 @@ def cpu_fwd_bwd_tflops(shape, sample_batch, reps, warmup=1):
     return (ff + fb) / sec / 1e12, sec, sb
 
 
+def cpu_baseline_record(shape, reps, warmup):
+    tf, sec, sb = cpu_fwd_bwd_tflops(shape, reps, warmup)
+    sample = (f"{sb} of {shape[0]} batch elements per step, torch CPU SDPA + autograd in bf16 "
+              f"(oracle/sdpa_port.py), {warmup} warm-up + {reps} timed steps, median {sec:.3f} s")
+    return {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": sample}, sec, sb
+
+
 def run_reference_arm(args, shape, rank, world):
     if rank != 0:
         return
-    B, T, H, Hkv, D, window, sinks = shape
-    sample_b = max(1, B // 4)
-    times = []
-    tf = None
-    for i in range(args.warmup + args.steps):
-        tf_i, sec, sb = cpu_fwd_bwd_tflops(shape, sample_b, reps=1, warmup=0)
-        if i >= args.warmup:
-            times.append(sec)
-            tf = tf_i
-    sec = statistics.median(times)
-    ff, fb = flops(sb, T, H, D, window, sinks)
-    value = (ff + fb) / sec / 1e12
-    cores = torch.get_num_threads()
-    sample = (f"{sb} of {B} batch elements per step, torch CPU SDPA + autograd in bf16 "
-              f"(oracle/sdpa_port.py), {args.steps} timed steps, median")
+    B = shape[0]
+    cpu, sec, sb = cpu_baseline_record(shape, reps=args.steps, warmup=args.warmup)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s",
+        "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": sec * 1e3 * B / sb, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": sec * 1e3 * B / sb, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD_TEXT[args.workload], "cpu_sample": sample,
-                   "ms_per_step": "sample time scaled by B / sample size"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": sample},
-        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+        "config": {"workload": WORKLOAD_TEXT[args.workload]},
+        "cpu_sample": {"what": cpu["sample"], "ms_per_step": "sample time scaled by B / sample size"},
+        "cpu_baseline": cpu,
+        "e2e": {"value": cpu["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -239,7 +255,7 @@ class Step:
         self.o = torch.empty_like(q)
         self.lse = torch.empty(self.B, self.H, self.T, dtype=torch.float32, device=q.device)
         self.dq, self.dk, self.dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        self.scratch = torch.empty(self.lib.nlfa_bwd_scratch_bytes(self.B, self.T, self.H),
+        self.scratch = torch.empty(self.lib.nlfa_bwd_fused_scratch_bytes(self.B, self.T, self.H, self.D),
                                    dtype=torch.uint8, device=q.device)
 
     def _dims(self):
@@ -264,7 +280,23 @@ class Step:
         self.fwd()
         self.bwd()
 
+    def outputs(self):
+        return {"o": self.o, "lse": self.lse, "dq": self.dq, "dk": self.dk, "dv": self.dv}
+
     launches_per_step = 4          # forward, Delta, dK/dV, dQ
+
+    def captured(self):
+        """The same step as one CUDA graph (replayed, the host issues one launch per step)."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            self.step()                         # attributes and tensor maps are set up outside the capture
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                self.step()
+        torch.cuda.current_stream().wait_stream(side)
+        return graph
 
 
 def time_region(fn, iters):
@@ -283,8 +315,11 @@ def kernel_times(step: Step, iters=10):
     """Average device time of each kernel, timed alone with CUDA events on its stream."""
     L = step.L
     out = {}
-    for name, fn in (("fwd", step.fwd), ("delta", lambda: step.bwd(L.PASS_DELTA)),
-                     ("dkv", lambda: step.bwd(L.PASS_DKV)), ("dq", lambda: step.bwd(L.PASS_DQ))):
+    names = [("fwd", step.fwd), ("delta", lambda: step.bwd(L.PASS_DELTA)),
+             ("dkv", lambda: step.bwd(L.PASS_DKV)), ("dq", lambda: step.bwd(L.PASS_DQ))]
+    if step.D <= 64:
+        names.append(("one_pass_bwd", lambda: step.bwd(L.PASS_FUSED)))     # the alternative layout, for the record
+    for name, fn in names:
         for _ in range(3):
             fn()
         out[name] = time_region(fn, iters)
@@ -301,24 +336,69 @@ def dram_traffic(kernel, workload):
     return None
 
 
+def algorithmic_bytes(B, T, H, Hkv, D):
+    """(forward, backward) bytes that have to move: every input and output once, plus the fp32 rows."""
+    qo, kv, rows = B * T * H * D * 2, B * T * Hkv * D * 2, B * H * T * 4
+    fwd = 2 * qo + 2 * kv + rows                            # q, o, k, v, lse
+    bwd = 4 * qo + 4 * kv + 3 * rows                        # q, o, dO, dq, k, v, dk, dv, lse, Delta w+r
+    return fwd, bwd
+
+
+def other_workload(name, dev, iters=5):
+    """Kernel-only forward+backward of another named shape (whole batch on this GPU), CUDA events."""
+    shape = WORKLOADS[name]
+    B, T, H, Hkv, D, window, sinks = shape
+    q, k, v, do = make_inputs(shape, 4321, dev)
+    step = Step(shape, q, k, v, do)
+    for _ in range(3):
+        step.step()
+    ms = time_region(step.step, iters)
+    ff, fb = flops(B, T, H, D, window, sinks)
+    bf, bb = algorithmic_bytes(B, T, H, Hkv, D)
+    rec = {"workload": WORKLOAD_TEXT[name], "ms_per_step": ms, "tflops": (ff + fb) / (ms * 1e-3) / 1e12,
+           "algorithmic_gb_per_s": (bf + bb) / (ms * 1e-3) / 1e9, "iters": iters}
+    del step, q, k, v, do
+    torch.cuda.empty_cache()
+    return rec
+
+
 def run_gpu_arm(args, shape, rank, world, local_rank):
     import torch.distributed as dist
     from machinelearning_b200 import flash_cuda, host_pipeline, sharding
 
+    B, T, H, Hkv, D, window, sinks = shape
+    if B % world:
+        raise SystemExit(f"batch {B} does not split over {world} ranks")
+    # the CPU baseline first, before this process has started any CUDA work: the same measurement the
+    # reference arm makes (rank 0, one GPU only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu, _, _ = cpu_baseline_record(shape, reps=5, warmup=2)
+
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    B, T, H, Hkv, D, window, sinks = shape
-    q, k, v, do = make_inputs(shape, 1000 + rank, dev)
-    step = Step(shape, q, k, v, do)
+    # every rank draws the whole job's inputs from the same seed and keeps its share: what the
+    # ranks compute together is then exactly what one GPU computes alone
+    gq, gk, gv, gdo = make_inputs(shape, 1000, "cpu")
+    plan = sharding.plan(B, Hkv, world, rank)
+    hq, hk, hv, hdo = (t.contiguous() for t in sharding.take_shard(gq, gk, gv, gdo, plan))
+    local_shape = (hq.shape[0], T, hq.shape[2], hk.shape[2], D, window, sinks)
+    q, k, v, do = (t.to(dev) for t in (hq, hk, hv, hdo))
+    step = Step(local_shape, q, k, v, do)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- kernel-only throughput, inputs resident in HBM
-    for _ in range(max(args.warmup, 3)):
-        step.step()
+    # ---- kernel-only throughput, inputs resident in HBM.  One GPU: eager launches (a step is
+    # hundreds of microseconds, the host keeps ahead).  Several GPUs: the per-GPU share shrinks to
+    # tens of microseconds, so the step is replayed from a CUDA graph -- the GPU is timed, not Python.
+    graph = step.captured() if world > 1 else None
+    run = graph.replay if graph is not None else step.step
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        run()
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -327,7 +407,7 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
     end = torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
-        step.step()
+        run()
     end.record()
     barrier()
     ms_local = start.elapsed_time(end) / args.steps
@@ -335,18 +415,48 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
     if sampler:
         t_end = time.time() + 1.0
         while time.time() < t_end:
-            step.step()
+            run()
         torch.cuda.synchronize()
         sampler.__exit__(None, None, None)
     ms = sharding.max_over_ranks(ms_local, dev)
-    ff, fb = flops(B, T, H, D, window, sinks)
-    value = world * (ff + fb) / (ms * 1e-3) / 1e12
+    ff, fb = flops(B, T, H, D, window, sinks)               # the whole job's
+    value = (ff + fb) / (ms * 1e-3) / 1e12
+
+    # ---- several GPUs: the shards gathered over NCCL against one GPU's run of the whole batch
+    verified = None
+    eager_ms = None
+    weak = None
+    if world > 1:
+        eager_ms = sharding.max_over_ranks(time_region(step.step, args.steps), dev)
+        step.step()
+        torch.cuda.synchronize()
+        gathered = {n: sharding.gather_batch_shards(t, B) for n, t in step.outputs().items()}
+        if rank == 0:
+            full = Step(shape, *(t.to(dev) for t in (gq, gk, gv, gdo)))
+            full.step()
+            torch.cuda.synchronize()
+            verified = {n: bool(torch.equal(gathered[n], t)) for n, t in full.outputs().items()}
+            del full
+        del gathered
+        torch.cuda.empty_cache()
+        barrier()
+        # weak scaling beside it: every rank a whole batch of its own, no graph needed at that size
+        wq, wk, wv, wdo = make_inputs(shape, 2000 + rank, dev)
+        wstep = Step(shape, wq, wk, wv, wdo)
+        for _ in range(3):
+            wstep.step()
+        barrier()
+        wms = sharding.max_over_ranks(time_region(wstep.step, args.steps), dev)
+        weak = {"value": world * (ff + fb) / (wms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": wms,
+                "global_batch": B * world}
+        del wstep, wq, wk, wv, wdo
+        torch.cuda.empty_cache()
+        barrier()
 
     # ---- end to end through the public API, host buffers, copies inside the timed region
-    hq, hk, hv, hdo = make_inputs(shape, 1000 + rank, "cpu", pin=True)        # pinned host
+    hq, hk, hv, hdo = (t.pin_memory() for t in (hq, hk, hv, hdo))
     host_out = [torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)]
     scale = 1.0 / math.sqrt(D)
-
     # batch slices: copy-in, flash_attn + autograd and copy-out of neighbouring slices overlap
     pipe = host_pipeline.HostPipeline(tuple(hq.shape), tuple(hk.shape), hq.dtype, dev, n_slices=8)
 
@@ -359,67 +469,68 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
     e2e_iters = max(3, min(args.steps, 10))
     e2e_ms = sharding.max_over_ranks(time_region(e2e_step, e2e_iters), dev)
     barrier()
-    e2e_value = world * (ff + fb) / (e2e_ms * 1e-3) / 1e12
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
-    d2h = sum(t.numel() * t.element_size() for t in host_out)
-
-    # ---- verification glue (NCCL only here): every rank's output checksum must be finite
-    checksum = torch.stack([step.o.float().sum(), step.dq.float().sum(),
-                            step.dk.float().sum(), step.dv.float().sum()]).double()
-    if world > 1:
-        gathered = [torch.empty_like(checksum) for _ in range(world)]
-        dist.all_gather(gathered, checksum)
-        checksum = torch.stack(gathered)
-    finite = bool(torch.isfinite(checksum).all().item())
+    e2e_value = (ff + fb) / (e2e_ms * 1e-3) / 1e12
+    h2d = world * sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
+    d2h = world * sum(t.numel() * t.element_size() for t in host_out)
 
     if rank != 0:
         return
     # ---- per-kernel times and the roofline of the dominant one (rank 0, kernels timed alone)
     kt = kernel_times(step)
-    # FLOPs per launch.  Algorithmic: the backward's 5 GEMMs are S, dP, dV, dK (dK/dV kernel) and
-    # dQ (dQ kernel); the dQ kernel's own S and dP are recomputation and are not counted.
-    # Executed counts them (what the tensor pipe actually ran).
-    gemm = 2.0 * D * pairs(T, window, sinks) * B * H
+    # FLOPs per launch on this rank's share.  Algorithmic: the backward's 5 GEMMs are S, dP, dV, dK
+    # (dK/dV kernel) and dQ (dQ kernel); the dQ kernel's own S and dP are recomputation and are not
+    # counted.  Executed counts them (what the tensor pipe actually ran).
+    gemm = 2.0 * D * pairs(T, window, sinks) * local_shape[0] * H
     kflops = {"fwd": 2 * gemm, "dkv": 4 * gemm, "dq": 1 * gemm}
     kexec = {"fwd": 2 * gemm, "dkv": 4 * gemm, "dq": 3 * gemm}
     dominant = max(("fwd", "dkv", "dq"), key=lambda n: kt[n])
     peak, peak_src = measured_peak()
     achieved = kflops[dominant] / (kt[dominant] * 1e-3) / 1e12
     clocks = sampler.summary() if sampler else None
-
-    cpu_tf, cpu_sec, cpu_b = (None, None, None)
-    cpu = None
-    if world == 1 and not args.no_cpu_baseline:
-        cpu_tf, cpu_sec, cpu_b = cpu_fwd_bwd_tflops(shape, max(1, B // 4), reps=3)
-        cpu = {"value": cpu_tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-               "kind": "port",
-               "sample": f"{cpu_b} of {B} batch elements, 1 warm-up + 3 timed fwd+bwd, median "
-                         f"{cpu_sec:.3f} s, torch CPU SDPA + autograd in bf16 (oracle/sdpa_port.py)"}
+    traffic = dram_traffic(dominant, args.workload) if world == 1 else None
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD_TEXT[args.workload], "global_batch": B * world,
-                   "parallelism": f"batch-sharded x{world}, no collective in the path",
+        "steps": args.steps, "warmup": warm, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD_TEXT[args.workload], "global_batch": B,
+                   "per_gpu_batch": local_shape[0],
+                   "parallelism": f"batch split over {world} GPU(s) (sharding.plan), no collective in the path",
+                   "timing": ("CUDA graph replay of forward+backward (4 kernels) between two events"
+                              if graph is not None else "eager launches between two events"),
                    "l2": "working set (q,k,v,o,dO,dq,dk,dv) larger than the 126 MB L2"
-                         if 8 * q.numel() * 2 > 126e6 else "working set smaller than L2",
-                   "flops_per_step_per_gpu": ff + fb},
+                         if 8 * q.numel() * 2 > 126e6 else
+                         "per-GPU working set smaller than the 126 MB L2 (the named shape, split)",
+                   "flops_per_step": ff + fb},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "pipeline": "8 batch slices; copy-in, kernels and copy-out on three streams"},
+                "pipeline": "8 batch slices per GPU; copy-in, kernels and copy-out on three streams"},
         "gpu_launches": Step.launches_per_step * args.steps,
         "kernel_ms": kt,
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peak_src,
                      "flops_per_launch": kflops[dominant],
                      "executed_tflops": kexec[dominant] / (kt[dominant] * 1e-3) / 1e12,
-                     "traffic": dram_traffic(dominant, args.workload)},
+                     "traffic": traffic,
+                     "traffic_source": "ncu capture of this kernel on this workload (profiles/dram_traffic.json), "
+                                       "not measured by this run"},
         "frac_of_peak_fwd_bwd": value / world / peak,
         "clocks": clocks,
-        "outputs_finite": finite,
     }
+    if world > 1:
+        line["verified_against_single_gpu"] = verified
+        line["eager_ms_per_step"] = eager_ms
+        line["weak"] = weak
+    else:
+        others = {}
+        for name in ("c3", "c5"):
+            if name != args.workload and not args.no_other_workloads:
+                others[name] = other_workload(name, dev)
+        if "c3" in others:
+            others["c3"]["frac_of_hbm_peak"] = others["c3"]["algorithmic_gb_per_s"] / measured_hbm()
+        if others:
+            line["other_workloads"] = others
     if cpu:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
@@ -471,6 +582,53 @@ def run_whole_model_reference_arm(args, rank):
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def nanolab_own_bench(batch):
+    """nanolab's own ``bench_gpu.bench`` (``nanolab/bench_gpu.py:41-110``: its GPT, Muon + AdamW, eager
+    launches, wall clock), unmodified, with this package injected as ``nanolab.flash_cuda`` -- flag on and
+    off.  Runs in a child process (``nanolab.mixers`` binds the module at import time); needs the staged
+    copy of the reference's caller (``oracle/build_ref.py``) and answers why not when it is absent."""
+    code = f"""
+import sys, json
+sys.path.insert(0, {str(ROOT)!r})
+from oracle import build_ref
+if not build_ref.nanolab_on_path():
+    print(json.dumps({{"unavailable": "the reference's nanolab package is not staged (python oracle/build_ref.py)"}}))
+    raise SystemExit(0)
+import torch
+from machinelearning_b200 import mixer_glue, flash_cuda
+mixer_glue.install()
+from nanolab import bench_gpu, mixers
+from nanolab.config import build_config
+assert mixers.flash_cuda is flash_cuda
+torch.backends.cuda.matmul.allow_tf32 = True
+out = {{"caller": "nanolab", "what": "nanolab.bench_gpu.bench(cfg), phase1 preset, batch {batch} x 1024, bf16, "
+       "Muon + AdamW, eager, 5 warm-up + 20 timed steps, wall clock"}}
+calls = {{"n": 0}}
+real = flash_cuda.fwd
+def counted(*a, **k):
+    calls["n"] += 1
+    return real(*a, **k)
+flash_cuda.fwd = counted
+for flag in (True, False):
+    cfg = build_config("phase1", dict(run_name="bench", batch_size={batch}, block_size=1024, grad_accum=1,
+                                      flash_cuda=flag, compile=False, dtype="bf16"))
+    calls["n"] = 0
+    r = bench_gpu.bench(cfg, peak_flops=1.0)
+    out["flash_cuda_on" if flag else "flash_cuda_off"] = {{
+        "tokens_per_s": r["tok_s"], "ms_per_step": r["ms_per_step"], "fwd_ms": r["fwd_ms"], "bwd_ms": r["bwd_ms"],
+        "opt_ms": r["opt_ms"], "loss": r["loss"], "library_forward_calls": calls["n"]}}
+    torch.cuda.empty_cache()
+print(json.dumps(out))
+"""
+    try:
+        r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=900)
+        if r.returncode != 0:
+            return {"unavailable": f"child exited {r.returncode}: {r.stderr.strip().splitlines()[-1:]}"}
+        return json.loads(r.stdout.strip().splitlines()[-1])
+    except Exception as e:                                        # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"}
 
 
 def run_whole_model_arm(args, rank, world, local_rank):
@@ -530,7 +688,13 @@ def run_whole_model_arm(args, rank, world, local_rank):
     def measure(flag, steps, warmup, sample_clocks):
         model, step = build(flag)
         x, y = x_pin.to(dev), y_pin.to(dev)
-        first_loss = step.step(x, y).item()        # same weights and tokens in both arms: comparable
+        # Same weights and tokens in both arms.  The output projections start at zero, so the first
+        # step's loss cannot tell the kernels from SDPA; the loss after three optimiser steps can.
+        for key in calls:
+            calls[key] = 0
+        losses = [step.step(x, y).item() for _ in range(4)]        # the fourth loss has seen three updates
+        eager_calls = {key: n // 4 for key, n in calls.items()}       # per step, counted while launching eagerly
+        first_loss, third_loss = losses[0], losses[3]
         captured[flag] = False
         if not args.no_graph:
             try:                                   # the whole step as one CUDA graph (both arms alike)
@@ -545,10 +709,8 @@ def run_whole_model_arm(args, rank, world, local_rank):
         sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
         if sampler:
             sampler.__enter__()
-        for key in calls:
-            calls[key] = 0
         resident = time_region(lambda: step.step(x, y), steps)
-        n_calls = dict(calls)
+        n_calls = {key: n * steps for key, n in eager_calls.items()}   # a replayed graph makes no Python calls
         if sampler:
             sampler.__exit__(None, None, None)
         barrier()
@@ -561,7 +723,7 @@ def run_whole_model_arm(args, rank, world, local_rank):
         barrier()
         e2e = time_region(host_step, max(3, min(steps, 10)))
         barrier()
-        loss = first_loss
+        loss = (first_loss, third_loss)
         flops_tok = model.flops_per_token()
         del model, step
         torch.cuda.empty_cache()
@@ -592,11 +754,14 @@ def run_whole_model_arm(args, rank, world, local_rank):
                                    "value_blend": n_calls["blend"] // steps, "head_gate": n_calls["gate"] // steps},
         "model_flops_utilisation": flops_tok * tok_s / world / 1e12 / peak,
         "peak_source": peak_src,
-        "first_step_loss": loss,
+        "first_step_loss": loss[0], "loss_after_3_steps": loss[1],
         "flag_off_sdpa": {"tokens_per_s": tokens / (sdpa_ms * 1e-3), "ms_per_step": sdpa_ms,
-                          "first_step_loss": sdpa_loss},
+                          "first_step_loss": sdpa_loss[0], "loss_after_3_steps": sdpa_loss[1]},
+        "flag_on_off_loss_rel_diff_after_3_steps": abs(loss[1] - sdpa_loss[1]) / abs(sdpa_loss[1]),
         "clocks": clocks,
     }
+    if world == 1:
+        line["nanolab_bench_gpu"] = nanolab_own_bench(GLOBAL_BATCH)
     if world == 1 and not args.no_cpu_baseline:
         cpu_tok_s, sec = whole_model_cpu_tokens_per_s(2, reps=2)
         line["cpu_baseline"] = {"value": cpu_tok_s, "unit": "tokens/s", "cores": torch.get_num_threads(),
@@ -614,6 +779,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=("b200", "reference"))
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + [WHOLE_MODEL])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-other-workloads", action="store_true", help="skip the c3 / c5 kernel-only figures")
     ap.add_argument("--no-graph", action="store_true", help="c4: launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
 
@@ -632,11 +798,6 @@ def main():
     import torch.distributed as dist
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # stdout carries the one JSON line: keep NCCL's version banner (NCCL_DEBUG=VERSION prints
-        # it to stdout) out of it; an explicit INFO / TRACE request goes to stderr instead
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
