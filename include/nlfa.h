@@ -245,6 +245,17 @@ int nlfa_fwd_cached(const void* q, const void* k_cache, const void* v_cache, voi
                     float scale, int causal, int window, int sinks, int dtype, void* scratch,
                     size_t scratch_bytes, void* stream);
 
+/* The same with the kernel family chosen by the caller (NLFA_PATH_*).  AUTO, which is what
+ * nlfa_fwd_cached does, takes the tensor-core kernel (TMA + tcgen05, keys in blocks of 128, the
+ * query rows of a KV head's whole group in one tile) for 16-bit inputs when the block has at
+ * least 16 rows per KV head (Tq x group) and the cache at least 256 keys, on a compute-capability
+ * 10.x device with 16-byte-aligned pointers and a positive scale; otherwise the fp32 kernel.
+ * TENSOR returns NLFA_ERR_UNSUPPORTED_PATH when those conditions do not hold. */
+int nlfa_fwd_cached_path(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
+                         const int* qpos, const int* kpos, int B, int Tq, int H, int Hkv, int L, int D,
+                         float scale, int causal, int window, int sinks, int dtype, int path,
+                         void* scratch, size_t scratch_bytes, void* stream);
+
 /* Bytes of device workspace `nlfa_selftest` needs. */
 size_t nlfa_selftest_workspace_bytes(void);
 

@@ -56,6 +56,8 @@ SIGNATURES = {
     "nlfa_fwd_cached_scratch_bytes": (_c_size_t, [_c_int] * 6),
     "nlfa_fwd_cached": (_c_int, [_c_void_p] * 7 + [_c_int] * 6 + [_c_float] + [_c_int] * 4
                         + [_c_void_p, _c_size_t, _c_void_p]),
+    "nlfa_fwd_cached_path": (_c_int, [_c_void_p] * 7 + [_c_int] * 6 + [_c_float] + [_c_int] * 5
+                             + [_c_void_p, _c_size_t, _c_void_p]),
     "nlfa_selftest_workspace_bytes": (_c_size_t, []),
     "nlfa_selftest": (_c_int, [_c_int, _c_int, _c_void_p, _c_size_t,
                                ctypes.POINTER(_c_float), _c_void_p]),

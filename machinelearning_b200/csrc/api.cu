@@ -194,6 +194,8 @@ int encode_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T,
 
 }  // namespace
 
+unsigned* status_block() { return status_word(); }
+
 int make_tile_map(CUtensorMap* map, const void* base, int dtype, int B, int T, int heads, int D,
                   int rows) {
   if (!aligned16(base)) return NLFA_ERR_MISALIGNED;

@@ -99,11 +99,13 @@ template <int MODE, int YR>
 __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p) {
   BwdUnit<MODE> w;
   // Heaviest units first (rank = stationary tile), all (batch, head) pairs of one rank together.
-  // The fused pass does this in groups of `sched_group` (batch, KV head) pairs, so that a head's
-  // fp32 dQ sums and its tiles are still in L2 when its next key block comes round, while a key
-  // block still starts a whole wave of units after the block below it, whose dQ turns it waits for.
+  // The key-block-stationary passes do this in groups of `sched_group` (batch, KV head) pairs (one
+  // per CTA of the launch), so that a head's tiles -- and in the fused pass its fp32 dQ sums -- are
+  // still in L2 when its next key block comes round (dK/dV pass at B=32, H=12, T=1024: 0.145 ->
+  // 0.139 ms), while a key block still starts a whole wave of units after the block below it,
+  // whose dQ turns the fused pass waits for.
   int rank, bh;
-  if (MODE == MODE_FUSED) {
+  if (MODE == MODE_FUSED || p.sched_group < p.BH) {
     const int per_group = p.sched_group * p.n_tiles;
     const int g0 = (u / per_group) * p.sched_group;              // first pair of this group
     const int size = p.BH - g0 < p.sched_group ? p.BH - g0 : p.sched_group;
@@ -1073,7 +1075,7 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   const int sst = sched_counters(stream, &bp.sched);
   if (sst != NLFA_OK) return sst;
   const int grid = bp.total_units < sm_count() ? bp.total_units : sm_count();
-  bp.sched_group = grid;
+  bp.sched_group = MODE == MODE_DQ ? bp.BH : grid;      // (the dQ pass gains nothing from groups)
   kern<<<grid, 512, L::kDynamic, stream>>>(mx0, mx1, my0, my1, mo0, mo1, bp);
   if (cudaGetLastError() != cudaSuccess) return NLFA_ERR_CUDA;
   if (MODE == MODE_FUSED) {

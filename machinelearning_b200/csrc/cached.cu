@@ -296,21 +296,55 @@ int choose_splits(int B, int Tq, int H, int Hkv, int L, int D) {
   return s < 1 ? 1 : static_cast<int>(s);
 }
 
+template <typename T>
+int merge_for_dim(const CachedParams& p, int D, void* o, float* lse, cudaStream_t st) {
+  const long long rows = static_cast<long long>(p.B) * p.Tq * p.H;
+  const unsigned grid = static_cast<unsigned>((rows + kWarps - 1) / kWarps);
+  if (D == 32) merge_splits_kernel<T, 32><<<grid, kWarps * 32, 0, st>>>(p, (T*)o, lse);
+  else if (D == 64) merge_splits_kernel<T, 64><<<grid, kWarps * 32, 0, st>>>(p, (T*)o, lse);
+  else merge_splits_kernel<T, 128><<<grid, kWarps * 32, 0, st>>>(p, (T*)o, lse);
+  return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
+}
+
+size_t split_scratch_bytes(int B, int Tq, int H, int D, int s) {
+  return s <= 1 ? 0 : static_cast<size_t>(B) * Tq * H * s * (static_cast<size_t>(D) + 1) * sizeof(float);
+}
+
 }  // namespace
+
+// tensor-core form (cached_tc.cu)
+bool cached_tc_applies(int Tq, int H, int Hkv, int L, int D, int dtype);
+int cached_tc_splits(int B, int Tq, int H, int Hkv, int L);
+int launch_fwd_cached_tc(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
+                         const int* qpos, const int* kpos, int B, int Tq, int H, int Hkv, int L, int D,
+                         float scale, int causal, int window, int sinks, int dtype, float* part_o,
+                         float* part_l, int splits, unsigned* status, cudaStream_t stream);
+unsigned* status_block();      // api.cu
+
 }  // namespace nlfa
 
 extern "C" size_t nlfa_fwd_cached_scratch_bytes(int B, int Tq, int H, int Hkv, int L, int D) {
   if (B <= 0 || Tq <= 0 || H <= 0 || Hkv <= 0 || L <= 0 || H % Hkv != 0) return 0;
-  const int s = nlfa::choose_splits(B, Tq, H, Hkv, L, D);
-  if (s <= 1) return 0;
-  return static_cast<size_t>(B) * Tq * H * s * (static_cast<size_t>(D) + 1) * sizeof(float);
+  // the larger of what the two kernel families would split into (the family is chosen per call)
+  const size_t simt = nlfa::split_scratch_bytes(B, Tq, H, D, nlfa::choose_splits(B, Tq, H, Hkv, L, D));
+  const size_t tc = H / Hkv <= 128 ? nlfa::split_scratch_bytes(B, Tq, H, D, nlfa::cached_tc_splits(B, Tq, H, Hkv, L)) : 0;
+  return simt > tc ? simt : tc;
 }
 
 extern "C" int nlfa_fwd_cached(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
                                const int* qpos, const int* kpos, int B, int Tq, int H, int Hkv, int L, int D,
                                float scale, int causal, int window, int sinks, int dtype, void* scratch,
                                size_t scratch_bytes, void* stream) {
+  return nlfa_fwd_cached_path(q, k_cache, v_cache, o, lse, qpos, kpos, B, Tq, H, Hkv, L, D, scale, causal, window,
+                              sinks, dtype, NLFA_PATH_AUTO, scratch, scratch_bytes, stream);
+}
+
+extern "C" int nlfa_fwd_cached_path(const void* q, const void* k_cache, const void* v_cache, void* o, float* lse,
+                                    const int* qpos, const int* kpos, int B, int Tq, int H, int Hkv, int L, int D,
+                                    float scale, int causal, int window, int sinks, int dtype, int path,
+                                    void* scratch, size_t scratch_bytes, void* stream) {
   using namespace nlfa;
+  if (path != NLFA_PATH_AUTO && path != NLFA_PATH_SIMT && path != NLFA_PATH_TENSOR) return NLFA_ERR_UNSUPPORTED_PATH;
   if (B < 0 || Tq < 0 || H < 0 || L < 0 || Hkv <= 0 || H % Hkv != 0 || !(scale == scale)) return NLFA_ERR_BAD_SHAPE;
   if (D != 32 && D != 64 && D != 128) return NLFA_ERR_BAD_HEAD_DIM;
   if (dtype != NLFA_DTYPE_F32 && dtype != NLFA_DTYPE_F16 && dtype != NLFA_DTYPE_BF16) return NLFA_ERR_BAD_DTYPE;
@@ -323,14 +357,35 @@ extern "C" int nlfa_fwd_cached(const void* q, const void* k_cache, const void* v
   if (rows / 4 >= (1ll << 31)) return NLFA_ERR_BAD_SHAPE;
   if (!q || !o || (L > 0 && (!k_cache || !v_cache))) return NLFA_ERR_NULL_POINTER;
   CachedParams p{B, Tq, H, Hkv, L, causal ? 1 : 0, window, sinks, scale, qpos, kpos, 1, (L + 31) / 32, nullptr, nullptr};
-  const size_t need = nlfa_fwd_cached_scratch_bytes(B, Tq, H, Hkv, L, D);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) |
+                         reinterpret_cast<uintptr_t>(v_cache) | reinterpret_cast<uintptr_t>(o)) & 15u) == 0;
+  if (path != NLFA_PATH_SIMT && aligned && scale > 0.f && nlfa_device_supported() &&
+      cached_tc_applies(Tq, H, Hkv, L, D, dtype)) {
+    // blocks of a few dozen rows and more over a long cache: the products run on the tensor cores
+    if (nlfa_peek_status() != NLFA_OK) return NLFA_ERR_DEVICE_TIMEOUT;
+    unsigned* status = status_block();
+    if (!status) return NLFA_ERR_CUDA;
+    int splits = cached_tc_splits(B, Tq, H, Hkv, L);
+    if (split_scratch_bytes(B, Tq, H, D, splits) > (scratch ? scratch_bytes : 0)) splits = 1;
+    float* part_o = static_cast<float*>(scratch);
+    float* part_l = splits > 1 ? part_o + rows * splits * D : nullptr;
+    const int rc = launch_fwd_cached_tc(q, k_cache, v_cache, o, lse, qpos, kpos, B, Tq, H, Hkv, L, D, scale, causal,
+                                        window, sinks, dtype, splits > 1 ? part_o : nullptr, part_l, splits, status, st);
+    if (rc != NLFA_OK || splits == 1) return rc;
+    p.splits = splits;
+    p.part_o = part_o;
+    p.part_l = part_l;
+    return dtype == NLFA_DTYPE_BF16 ? merge_for_dim<__nv_bfloat16>(p, D, o, lse, st) : merge_for_dim<__half>(p, D, o, lse, st);
+  }
+  if (path == NLFA_PATH_TENSOR) return NLFA_ERR_UNSUPPORTED_PATH;
+  const size_t need = split_scratch_bytes(B, Tq, H, D, choose_splits(B, Tq, H, Hkv, L, D));
   if (need > 0 && scratch != nullptr && scratch_bytes >= need) {     // without scratch: one CTA walks all keys
     p.splits = choose_splits(B, Tq, H, Hkv, L, D);
     p.tiles_per_split = ((L + 31) / 32 + p.splits - 1) / p.splits;
     p.part_o = static_cast<float*>(scratch);
     p.part_l = p.part_o + rows * p.splits * D;
   }
-  cudaStream_t st = (cudaStream_t)stream;
   if (dtype == NLFA_DTYPE_BF16) return launch_for_dim<__nv_bfloat16>(p, D, q, k_cache, v_cache, o, lse, st);
   if (dtype == NLFA_DTYPE_F16) return launch_for_dim<__half>(p, D, q, k_cache, v_cache, o, lse, st);
   return launch_for_dim<float>(p, D, q, k_cache, v_cache, o, lse, st);

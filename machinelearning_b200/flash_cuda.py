@@ -360,7 +360,7 @@ def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 
 def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tensor, scale: float | None = None, *,
                       qpos: torch.Tensor | None = None, kpos: torch.Tensor | None = None, causal: bool = False,
-                      window: int = 0, sinks: int = 0, return_lse: bool = False):
+                      window: int = 0, sinks: int = 0, return_lse: bool = False, use_mma: bool | None = None):
     """Attention of an active block over [cache | block]: the core of nanolab's ``forward_cached``.
 
     ``q [B,T,H,D]`` is the active block; ``k_full`` / ``v_full [B,Hkv,L,D]`` are the cache with the
@@ -371,6 +371,9 @@ def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tenso
     ``causal``, full to the cache and lower-triangular in the block; otherwise every key.
     Forward only (nanolab runs this path under ``no_grad``); returns ``[B,T,H,D]`` (and the
     logsumexp ``[B,H,T]`` with ``return_lse``).  Raises ``ValueError`` for unsupported inputs.
+    ``use_mma`` as in ``flash_attn``: ``None`` lets the library take its tensor-core kernel where it
+    applies (16-bit inputs, a block of at least 16 rows per KV head over at least 256 keys) and the fp32
+    kernel elsewhere; ``False`` / ``True`` force one (``True`` raises where it does not apply).
     """
     ok = (q.dim() == 4 and k_full.dim() == 4 and v_full.dim() == 4 and q.is_cuda and k_full.is_cuda and v_full.is_cuda
           and q.dtype == k_full.dtype == v_full.dtype and q.dtype in SUPPORTED_DTYPES
@@ -400,12 +403,15 @@ def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tenso
     nbytes = lib.nlfa_fwd_cached_scratch_bytes(B, T, H, Hkv, L, D)      # > 0: the keys are split over CTAs
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
     with torch.cuda.device(q.device):
-        st = lib.nlfa_fwd_cached(q.data_ptr(), k_full.data_ptr(), v_full.data_ptr(), o.data_ptr(),
-                                 None if lse is None else lse.data_ptr(),
-                                 None if qp is None else qp.data_ptr(), None if kp is None else kp.data_ptr(),
-                                 B, T, H, Hkv, L, D, float(scale), int(bool(causal)), int(window), int(sinks),
-                                 _DTYPE_CODE[q.dtype], None if scratch is None else scratch.data_ptr(), nbytes,
-                                 torch.cuda.current_stream().cuda_stream)
+        path = _lib.PATH_AUTO if use_mma is None else (_lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT)
+        st = lib.nlfa_fwd_cached_path(q.data_ptr(), k_full.data_ptr(), v_full.data_ptr(), o.data_ptr(),
+                                      None if lse is None else lse.data_ptr(),
+                                      None if qp is None else qp.data_ptr(), None if kp is None else kp.data_ptr(),
+                                      B, T, H, Hkv, L, D, float(scale), int(bool(causal)), int(window), int(sinks),
+                                      _DTYPE_CODE[q.dtype], path, None if scratch is None else scratch.data_ptr(),
+                                      nbytes, torch.cuda.current_stream().cuda_stream)
+    if st == 7 and use_mma:
+        raise ValueError("flash_attn_cached: use_mma=True but the tensor-core kernel does not apply to these inputs")
     _lib.check("nlfa_fwd_cached", st)
     return (o, lse) if return_lse else o
 

@@ -138,3 +138,59 @@ def test_key_split_and_single_walk_agree():
                                       0.125, np.arange(L - T, L), np.arange(L), True)
     assert np.abs(o1.double().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max()
     assert np.abs(l1.double().cpu().numpy() - lse_ref).max() <= 1e-3
+
+
+TC_SHAPES = [
+    # B, T, H, Hkv, L, D, causal, window, sinks, explicit positions with gaps
+    (8, 32, 12, 4, 1056, 64, True, 0, 0, False),
+    (8, 32, 12, 12, 1056, 64, False, 0, 0, False),       # a bidirectional block, MHA
+    (8, 16, 12, 4, 4112, 64, True, 0, 0, False),
+    (8, 32, 12, 4, 288, 64, True, 256, 4, False),
+    (1, 64, 16, 16, 16448, 128, True, 0, 0, False),      # few rows, a long cache: the keys are split over CTAs
+    (2, 48, 8, 2, 700, 32, True, 0, 0, False),           # head dim 32 on 64-wide tiles; 4 heads x 32 positions per tile
+    (2, 40, 6, 2, 900, 64, True, 300, 8, True),          # positions after eviction: not contiguous
+    (1, 200, 4, 4, 600, 128, True, 0, 0, True),          # more than one query tile per KV head
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,T,H,Hkv,L,D,causal,window,sinks,gaps", TC_SHAPES)
+def test_tensor_core_kernel_matches_oracle_and_the_fp32_kernel(B, T, H, Hkv, L, D, causal, window, sinks, gaps):
+    """The tcgen05 form of the cached block forward (forced with ``use_mma=True``) against the float64
+    oracle (2e-2 relative on bf16, LSE 1e-3) and against the fp32 kernel on the same inputs."""
+    from machinelearning_b200 import flash_cuda
+    assert flash_cuda.mma_available(), flash_cuda.mma_unavailable_reason()
+    g = torch.Generator().manual_seed(L + D)
+    q = torch.randn(B, T, H, D, generator=g).bfloat16().cuda()
+    k = torch.randn(B, Hkv, L, D, generator=g).bfloat16().cuda()
+    v = torch.randn(B, Hkv, L, D, generator=g).bfloat16().cuda()
+    if gaps:                                     # keys keep their order but skip positions; the block comes last
+        kpos_np = np.cumsum(1 + (np.arange(L) % 7 == 0)).astype(np.int64)
+        qpos_np = kpos_np[L - T:].copy()
+        qpos, kpos = torch.from_numpy(qpos_np), torch.from_numpy(kpos_np)
+    else:
+        qpos = kpos = None
+        qpos_np, kpos_np = np.arange(L - T, L), np.arange(L)
+    kw = dict(qpos=qpos, kpos=kpos, causal=causal, window=window, sinks=sinks, return_lse=True)
+    y, lse = flash_cuda.flash_attn_cached(q, k, v, use_mma=True, **kw)
+    y32, lse32 = flash_cuda.flash_attn_cached(q, k, v, use_mma=False, **kw)
+    auto, _ = flash_cuda.flash_attn_cached(q, k, v, **kw)
+    assert torch.equal(auto, y)                  # every shape here is one the library takes the tensor cores for
+    sub = slice(0, min(B, 2))                    # the oracle materialises [T, L] per head: two batch elements suffice
+    ref, lse_ref = cached_f64.forward(q[sub].double().cpu().numpy(), k[sub].double().cpu().numpy(),
+                                      v[sub].double().cpu().numpy(), 1.0 / np.sqrt(D), qpos_np, kpos_np, causal,
+                                      window, sinks)
+    assert np.abs(y[sub].double().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max()
+    assert np.abs(lse[sub].double().cpu().numpy() - lse_ref).max() <= 1e-3
+    assert (y.float() - y32.float()).abs().max().item() <= 2e-2 * y32.float().abs().max().item()
+    assert (lse - lse32).abs().max().item() <= 1e-3
+
+
+@pytest.mark.gpu
+def test_tensor_core_kernel_is_refused_where_it_does_not_apply():
+    from machinelearning_b200 import flash_cuda
+    q = torch.randn(1, 4, 2, 64, device="cuda").bfloat16()           # 4 rows per KV head, 40 keys: fp32 kernel territory
+    k = torch.randn(1, 2, 40, 64, device="cuda").bfloat16()
+    with pytest.raises(ValueError, match="does not apply"):
+        flash_cuda.flash_attn_cached(q, k, k, use_mma=True)
+    assert torch.isfinite(flash_cuda.flash_attn_cached(q, k, k).float()).all()
