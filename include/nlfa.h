@@ -84,6 +84,18 @@ int nlfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
              int H, int Hkv, int D, float scale, int window, int sinks, int dtype, int path,
              void* stream);
 
+/* Forward with the mask given in full: the sliding window above, or -- with block > 0, which
+ * needs window == 0 -- the block-causal mask of nanolab's semi-autoregressive / diffusion mode
+ * (nanolab/mixers.py:78-93, `block_causal_mask`: blk = position / block; keep key k for query q
+ * iff blk[q] >= blk[k], i.e. every position of the query's own block and of all earlier
+ * blocks).  block of 0 or 1 is plain causal attention; block >= T is fully bidirectional.  The
+ * reference runs this mask through SDPA with a [T,T] boolean tensor (mixers.py:319-321); here the
+ * kernels apply it from positions and skip the key blocks beyond a tile's reach.  nlfa_fwd is
+ * this with block = 0. */
+int nlfa_fwd_masked(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T,
+                    int H, int Hkv, int D, float scale, int window, int sinks, int block, int dtype,
+                    int path, void* stream);
+
 /* Bytes of device scratch `nlfa_bwd` needs (the Delta tape, [B,H,T] float32).
  * The reference allocates the same tensor itself (flash_attn_cuda.cu:1770-1773). */
 size_t nlfa_bwd_scratch_bytes(int B, int T, int H);
@@ -113,6 +125,12 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
                     const float* lse, void* dq, void* dk, void* dv, void* scratch,
                     size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
                     int window, int sinks, int dtype, int path, int passes, void* stream);
+
+/* nlfa_bwd_passes with the mask given in full (`block` as in nlfa_fwd_masked). */
+int nlfa_bwd_masked(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                    const float* lse, void* dq, void* dk, void* dv, void* scratch,
+                    size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
+                    int window, int sinks, int block, int dtype, int path, int passes, void* stream);
 
 /* The backward with dQ formed in the dK/dV pass: P and dS are computed once per
  * (query tile, key block) instead of once in each of the reference's two passes
@@ -292,6 +310,8 @@ int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, c
  * check (negative: bad arguments).  Needs no device.  No counterpart in the
  * reference. */
 int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows);
+/* ... for a block-causal mask of `block` positions (window must then be 0). */
+int nlfa_check_mask_geometry_masked(int T, int window, int sinks, int block, int stream_rows);
 
 /* Reads (and clears) the device status word that bounded waits inside the
  * kernels write when they give up.  Synchronises the device.  Returns NLFA_OK

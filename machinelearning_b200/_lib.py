@@ -28,6 +28,9 @@ SIGNATURES = {
     "nlfa_device_supported": (_c_int, []),
     "nlfa_resolve_path": (_c_int, [_c_int, _c_int, _c_int]),
     "nlfa_fwd": (_c_int, [_c_void_p] * 5 + [_c_int] * 5 + [_c_float] + [_c_int] * 4 + [_c_void_p]),
+    "nlfa_fwd_masked": (_c_int, [_c_void_p] * 5 + [_c_int] * 5 + [_c_float] + [_c_int] * 5 + [_c_void_p]),
+    "nlfa_bwd_masked": (_c_int, [_c_void_p] * 10 + [_c_size_t] + [_c_int] * 5 + [_c_float]
+                        + [_c_int] * 6 + [_c_void_p]),
     "nlfa_bwd_scratch_bytes": (_c_size_t, [_c_int, _c_int, _c_int]),
     "nlfa_bwd": (_c_int, [_c_void_p] * 10 + [_c_size_t] + [_c_int] * 5 + [_c_float]
                  + [_c_int] * 4 + [_c_void_p]),
@@ -63,6 +66,7 @@ SIGNATURES = {
                                ctypes.POINTER(_c_float), _c_void_p]),
     "nlfa_selftest_tiles": (_c_int, [_c_int, _c_int] + [_c_void_p] * 6),
     "nlfa_check_mask_geometry": (_c_int, [_c_int] * 4),
+    "nlfa_check_mask_geometry_masked": (_c_int, [_c_int] * 5),
     "nlfa_device_status": (_c_int, [ctypes.POINTER(ctypes.c_uint)]),
     "nlfa_set_status_mirror": (_c_int, [_c_void_p]),
     "nlfa_peek_status": (_c_int, []),

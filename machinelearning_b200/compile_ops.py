@@ -26,12 +26,12 @@ from . import flash_cuda
 
 @torch.library.custom_op("nlfa::attn_fwd", mutates_args=(), device_types="cuda")
 def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, use_mma: bool, window: int,
-             sinks: int) -> tuple[torch.Tensor, torch.Tensor]:
-    return flash_cuda.fwd(q, k, v, scale, use_mma, window, sinks)
+             sinks: int, block: int) -> tuple[torch.Tensor, torch.Tensor]:
+    return flash_cuda.fwd(q, k, v, scale, use_mma, window, sinks, block)
 
 
 @attn_fwd.register_fake
-def _(q, k, v, scale, use_mma, window, sinks):
+def _(q, k, v, scale, use_mma, window, sinks, block):
     B, T, H, _ = q.shape
     return torch.empty_like(q), q.new_empty((B, H, T), dtype=torch.float32)
 
@@ -39,35 +39,35 @@ def _(q, k, v, scale, use_mma, window, sinks):
 @torch.library.custom_op("nlfa::attn_bwd", mutates_args=(), device_types="cuda")
 def attn_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor,
              lse: torch.Tensor, scale: float, use_mma: bool, window: int,
-             sinks: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    return flash_cuda.bwd(dout.contiguous(), q, k, v, o, lse, scale, use_mma, window, sinks)
+             sinks: int, block: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return flash_cuda.bwd(dout.contiguous(), q, k, v, o, lse, scale, use_mma, window, sinks, block=block)
 
 
 @attn_bwd.register_fake
-def _(dout, q, k, v, o, lse, scale, use_mma, window, sinks):
+def _(dout, q, k, v, o, lse, scale, use_mma, window, sinks, block):
     return torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
 
 
 def _setup(ctx, inputs, output):
-    q, k, v, scale, use_mma, window, sinks = inputs
+    q, k, v, scale, use_mma, window, sinks, block = inputs
     o, lse = output
     ctx.save_for_backward(q, k, v, o, lse)
-    ctx.args = (scale, use_mma, window, sinks)
+    ctx.args = (scale, use_mma, window, sinks, block)
 
 
 def _backward(ctx, dout, dlse):
     q, k, v, o, lse = ctx.saved_tensors
     dq, dk, dv = attn_bwd(dout, q, k, v, o, lse, *ctx.args)
-    return dq, dk, dv, None, None, None, None
+    return dq, dk, dv, None, None, None, None, None
 
 
 attn_fwd.register_autograd(_backward, setup_context=_setup)
 
 
-def flash_attn(q, k, v, scale=None, use_mma=None, *, window: int = 0, sinks: int = 0):
+def flash_attn(q, k, v, scale=None, use_mma=None, *, window: int = 0, sinks: int = 0, block: int = 0):
     """``flash_cuda.flash_attn`` through the registered operators (same checks, same casts)."""
-    q, k, v, scale, use_mma = flash_cuda.prepare(q, k, v, scale, use_mma, window, sinks)
-    return attn_fwd(q, k, v, float(scale), bool(use_mma), int(window), int(sinks))[0]
+    q, k, v, scale, use_mma = flash_cuda.prepare(q, k, v, scale, use_mma, window, sinks, block)
+    return attn_fwd(q, k, v, float(scale), bool(use_mma), int(window), int(sinks), int(block))[0]
 
 
 # ---------------------------------------------------------------- q/k prologue, value blend, head gate

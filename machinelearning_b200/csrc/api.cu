@@ -106,6 +106,7 @@ int check_problem(const Problem& p) {
   if (p.D != 32 && p.D != 64 && p.D != 128) return NLFA_ERR_BAD_HEAD_DIM;
   if (p.window < 0 || p.sinks < 0) return NLFA_ERR_BAD_WINDOW;
   if (p.window == 0 ? p.sinks != 0 : p.sinks >= p.window) return NLFA_ERR_BAD_WINDOW;
+  if (p.block < 0 || (p.block > 0 && p.window > 0)) return NLFA_ERR_BAD_WINDOW;   // two masks, one slot (mixers.py:300-304)
   if (!(p.scale == p.scale)) return NLFA_ERR_BAD_SHAPE;
   return NLFA_OK;
 }
@@ -321,7 +322,13 @@ int nlfa_resolve_path(int dtype, int head_dim, int path) {
 int nlfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T,
              int H, int Hkv, int D, float scale, int window, int sinks, int dtype, int path,
              void* stream) {
-  Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype};
+  return nlfa_fwd_masked(q, k, v, o, lse, B, T, H, Hkv, D, scale, window, sinks, 0, dtype, path, stream);
+}
+
+int nlfa_fwd_masked(const void* q, const void* k, const void* v, void* o, float* lse, int B, int T,
+                    int H, int Hkv, int D, float scale, int window, int sinks, int block, int dtype,
+                    int path, void* stream) {
+  Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype, block};
   int st = check_problem(p);
   if (st != NLFA_OK) return st;
   int resolved = nlfa_resolve_path(dtype, D, path);
@@ -338,6 +345,7 @@ int nlfa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, i
     p.window = 0;            // the window never cuts anything: plain causal
     p.sinks = 0;
   }
+  if (p.block == 1) p.block = 0;                            // blocks of one position: plain causal
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (resolved == NLFA_PATH_SIMT) return launch_fwd_simt(p, q, k, v, o, lse, s);
   if (!nlfa_device_supported()) return NLFA_ERR_NOT_SM100;
@@ -387,10 +395,18 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
                     const float* lse, void* dq, void* dk, void* dv, void* scratch,
                     size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
                     int window, int sinks, int dtype, int path, int passes, void* stream) {
+  return nlfa_bwd_masked(dout, q, k, v, o, lse, dq, dk, dv, scratch, scratch_bytes, B, T, H, Hkv, D, scale,
+                         window, sinks, 0, dtype, path, passes, stream);
+}
+
+int nlfa_bwd_masked(const void* dout, const void* q, const void* k, const void* v, const void* o,
+                    const float* lse, void* dq, void* dk, void* dv, void* scratch,
+                    size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
+                    int window, int sinks, int block, int dtype, int path, int passes, void* stream) {
   if (passes <= 0 || passes > (NLFA_PASS_ALL | NLFA_PASS_FUSED)) return NLFA_ERR_UNSUPPORTED_PATH;
   const bool want_fused = (passes & NLFA_PASS_FUSED) != 0;
   if (want_fused && (passes & (NLFA_PASS_DKV | NLFA_PASS_DQ))) return NLFA_ERR_UNSUPPORTED_PATH;
-  Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype};
+  Problem p{B, T, H, Hkv, D, window, sinks, scale, dtype, block};
   int st = check_problem(p);
   if (st != NLFA_OK) return st;
   const int resolved = nlfa_resolve_path(dtype, D, path);
@@ -409,6 +425,7 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
     p.window = 0;
     p.sinks = 0;
   }
+  if (p.block == 1) p.block = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* delta = static_cast<float*>(scratch);
   if (resolved == NLFA_PATH_SIMT)
@@ -439,19 +456,24 @@ int nlfa_selftest_tiles(int dtype, int head_dim, const void* q, const void* k, c
 }
 
 int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows) {
+  return nlfa_check_mask_geometry_masked(T, window, sinks, 0, stream_rows);
+}
+
+int nlfa_check_mask_geometry_masked(int T, int window, int sinks, int block, int stream_rows) {
   if (T <= 0 || window < 0 || sinks < 0 || (window > 0 && sinks >= window) ||
-      (window == 0 && sinks != 0) || (stream_rows != 64 && stream_rows != 128))
+      (window == 0 && sinks != 0) || block < 0 || (block > 0 && window > 0) ||
+      (stream_rows != 64 && stream_rows != 128))
     return -NLFA_ERR_BAD_WINDOW;
   const int n128 = (T + kTile - 1) / kTile;
   const int nys = (T + stream_rows - 1) / stream_rows;
   int check = 0;
   // (1) key blocks given to a query tile cover every block with a visible pair
   for (int t = 0; t < n128; ++t) {
-    const TileRange r = tile_range(t, window, sinks);
+    const TileRange r = tile_range(t, window, sinks, block, n128);
     for (int j = 0; j < n128; ++j, ++check) {
       bool any = false;
       for (int q = t * kTile; q < (t + 1) * kTile && !any; ++q)
-        for (int k = j * kTile; k < (j + 1) * kTile && !any; ++k) any = key_visible(q, k, window, sinks);
+        for (int k = j * kTile; k < (j + 1) * kTile && !any; ++k) any = key_visible(q, k, window, sinks, block, T);
       const bool given = (j >= r.lo && j <= r.hi) || j < r.sink_blocks;
       if (any && !given) return 1 + check;
     }
@@ -467,13 +489,13 @@ int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows) {
         bool all = true, causal_only = true, window_only = true;
         for (int q = q_lo; q <= q_hi; ++q)
           for (int k = k_lo; k <= k_hi; ++k) {
-            const bool vis = key_visible(q, k, window, sinks);
+            const bool vis = key_visible(q, k, window, sinks, block, T);
             all = all && vis;
-            causal_only = causal_only && (vis == (k <= q));
+            causal_only = causal_only && (vis == (k <= last_key_of_query(q, block, T)));
             window_only = window_only && (vis == (k > q - (window - sinks)));
           }
         // (a rectangle made fully visible by sink keys alone may be reported as cut: that only costs a mask)
-        if (rect_fully_visible(q_lo, q_hi, k_lo, k_hi, window, sinks) && !all) return 1 + check;
+        if (rect_fully_visible(q_lo, q_hi, k_lo, k_hi, window, sinks, block, T) && !all) return 1 + check;
         ++check;
         const int e = rect_edges(q_lo, q_hi, k_lo, k_hi, window, sinks);
         if (e == EDGE_CAUSAL && !causal_only) return 1 + check;
@@ -482,7 +504,7 @@ int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows) {
         ++check;
         if (stream_rows == kTile) {
           const int qt = orient == 0 ? t : y, kb = orient == 0 ? y : t;
-          if (block_fully_visible(qt, kb, window, sinks) && !all) return 1 + check;
+          if (block_fully_visible(qt, kb, window, sinks, block, T) && !all) return 1 + check;
           ++check;
           if (!all) {
             const int be = block_edges(qt, kb, window, sinks);
@@ -492,16 +514,17 @@ int nlfa_check_mask_geometry(int T, int window, int sinks, int stream_rows) {
         }
       }
   // (4) fused backward: the key blocks that stream query tile t take the turns 0 .. count - 1
-  //     exactly once each, in ascending block order, the diagonal block last
+  //     exactly once each, in ascending block order
   if (stream_rows == kTile)
     for (int t = 0; t < n128; ++t) {
       int expect = 0, count = 0;
       for (int j = 0; j < n128; ++j) {
-        if (t < j || t > last_query_tile_of_block(j, n128, kTile, window, sinks)) continue;
-        const int turn = dq_turn_of_block(j, t, window, sinks, &count);
+        if (t < first_query_of_key(j * kTile, block) / kTile ||
+            t > last_query_tile_of_block(j, n128, kTile, window, sinks))
+          continue;
+        const int turn = dq_turn_of_block(j, t, window, sinks, &count, block, n128);
         if (turn != expect) return 1 + check;
         ++expect;
-        if ((turn == count - 1) != (j == t)) return 1 + check;
       }
       ++check;
       if (expect != count) return 1 + check;

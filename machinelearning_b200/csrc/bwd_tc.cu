@@ -43,6 +43,7 @@ enum { MODE_DQ = 0, MODE_DKV = 1, MODE_FUSED = 2 };
 struct BwdParams {
   int T, H, Hkv;
   int window, sinks;
+  int block;             // > 0: block-causal mask of this many positions (window == 0)
   int n_tiles;           // 128-row tiles
   int n_ytiles;          // streamed tiles (YR rows each)
   int BH;                // B * H (dQ) or B * Hkv (dK/dV)
@@ -125,7 +126,7 @@ __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p
     // keys [lo_pos, last row of the tile], plus the sink prefix
     const int q_last = w.tile * kTile + kTile - 1;
     const int lo_pos = p.window > 0 ? w.tile * kTile - (p.window - p.sinks) + 1 : 0;
-    int hi = q_last / YR;
+    int hi = last_key_of_query(q_last, p.block) / YR;
     hi = hi < p.n_ytiles - 1 ? hi : p.n_ytiles - 1;
     w.s_lo = lo_pos > 0 ? lo_pos / YR : 0;
     const int sink_tiles = p.window > 0 ? (p.sinks + YR - 1) / YR : 0;
@@ -137,7 +138,7 @@ __device__ __forceinline__ BwdUnit<MODE> make_bwd_unit(int u, const BwdParams& p
     w.b = bh / p.Hkv;
     w.hk = bh - w.b * p.Hkv;
     w.h = w.hk * group;
-    w.s_lo = w.tile * (kTile / YR);             // first query tile that reaches the block
+    w.s_lo = first_query_of_key(w.tile * kTile, p.block) / YR;   // first query tile that reaches the block
     const int s_hi = last_query_tile_of_block(w.tile, p.n_ytiles, YR, p.window, p.sinks);
     w.extra = 0;
     w.n_inner = s_hi - w.s_lo + 1;
@@ -324,7 +325,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         if (inner == w.n_inner) { inner = 0; ++gq; }
         const int qt = w.s_lo + inner;
         int n_blocks;
-        const int order = dq_turn_of_block(w.tile, qt, p.window, p.sinks, &n_blocks);
+        const int order = dq_turn_of_block(w.tile, qt, p.window, p.sinks, &n_blocks, p.block, p.n_tiles);
         unsigned* turn = p.dq_turn + (static_cast<long long>(w.b) * p.H + (w.h + gq)) * p.n_tiles + qt;
         if (watcher) {
           if (order > 0) {
@@ -403,7 +404,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
           if (inner == w.n_inner) { inner = 0; ++gq; }
           const int qt = w.s_lo + inner;                       // query tile of this iteration
           int n_blocks;
-          const int order = dq_turn_of_block(w.tile, qt, p.window, p.sinks, &n_blocks);
+          const int order = dq_turn_of_block(w.tile, qt, p.window, p.sinks, &n_blocks, p.block, p.n_tiles);
           const long long slot = (static_cast<long long>(w.b) * p.H + (w.h + gq)) * p.n_tiles + qt;
           float4* acc = reinterpret_cast<float4*>(p.dq_acc + slot * (kTile * D)) + row;
           ok = mbar_wait(bar(DQ_READY), git & 1, wctx, 43);
@@ -791,13 +792,16 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
       // positions below vsink (sink keys; dQ orientation only).
       int va, vsink = 0;
       unsigned vw;
+      // the causal edge as this row sees it: a query's last visible key, a key's first query
+      // (block-causal masks move both to the ends of the row's block)
+      const int edge = MODE == MODE_DQ ? last_key_of_query(pos, p.block, p.T) : first_query_of_key(pos, p.block);
       if (MODE == MODE_DQ) {                           // row = query `pos`, columns = keys
         const int lo = p.window > 0 ? pos - (p.window - p.sinks) + 1 : 0;
         va = lo > 0 ? lo : 0;
-        vw = static_cast<unsigned>(pos - va);
+        vw = static_cast<unsigned>(edge - va);
         vsink = p.window > 0 ? (p.sinks < pos + 1 ? p.sinks : pos + 1) : 0;   // sinks are causal too
       } else {                                         // row = key `pos`, columns = queries
-        va = pos;
+        va = edge;
         vw = (p.window > 0 && pos >= p.sinks) ? static_cast<unsigned>(p.window - p.sinks - 1)
                                                : 0x7fffffffu;
       }
@@ -852,7 +856,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
         const int q_hi = q_lo + (MODE == MODE_DQ ? kTile : YR) - 1;
         const int k_lo = MODE == MODE_DQ ? idx * YR : w.tile * kTile;
         const int k_hi = k_lo + (MODE == MODE_DQ ? YR : kTile) - 1;
-        const bool full = rect_fully_visible(q_lo, q_hi, k_lo, k_hi, p.window, p.sinks);
+        const bool full = rect_fully_visible(q_lo, q_hi, k_lo, k_hi, p.window, p.sinks, p.block, p.T);
         const int edges = rect_edges(q_lo, q_hi, k_lo, k_hi, p.window, p.sinks);
         const ulonglong2* vec2 =
             reinterpret_cast<const ulonglong2*>(gen + L::kVec + s * 1024) + (YR / 8) * half;
@@ -887,8 +891,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
             unpack_f2(xb, p2, p3);
             p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
             if (kMasked == 2) {
-              // plain causal: one compare per element against a per-thread limit
-              const int lim = pos - other0;      // dQ: last visible column; dK/dV: first visible
+              // the causal edge alone: one compare per element against a per-thread limit
+              const int lim = edge - other0;     // dQ: last visible column; dK/dV: first visible
               if (MODE == MODE_DQ) {
                 if (c + 0 > lim) p0 = 0.f;
                 if (c + 1 > lim) p1 = 0.f;
@@ -1052,6 +1056,7 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   bp.Hkv = p.Hkv;
   bp.window = p.window;
   bp.sinks = p.sinks;
+  bp.block = p.block;
   bp.n_tiles = (p.T + kTile - 1) / kTile;
   bp.n_ytiles = (p.T + YR - 1) / YR;
   bp.BH = p.B * (MODE == MODE_DQ ? p.H : p.Hkv);

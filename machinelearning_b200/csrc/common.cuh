@@ -23,7 +23,22 @@ struct Problem {
   int window, sinks;     // window == 0: plain causal
   float scale;
   int dtype;             // NLFA_DTYPE_*
+  int block = 0;         // > 0: block-causal (bidirectional inside blocks of this many positions); needs window == 0
 };
+
+// Block-causal attention (nanolab/mixers.py:78-93, `block_causal_mask`): a query sees every
+// position of its own block and of all earlier blocks, i.e. query q sees the keys up to the end
+// of its block, and key k is seen by the queries from the start of its block on.  block == 0
+// (or 1) is plain causal attention.  A block may reach past the end of the sequence (`t_len`
+// positions): the keys stop there.
+__host__ __device__ inline int last_key_of_query(int q, int block, int t_len = 1 << 30) {
+  if (block <= 1) return q;
+  const int last = (q / block + 1) * block - 1;
+  return last < t_len - 1 ? last : t_len - 1;
+}
+__host__ __device__ inline int first_query_of_key(int k, int block) {
+  return block > 1 ? (k / block) * block : k;
+}
 
 // Which key blocks a 128-row query tile must visit.  Block j covers keys
 // [128 j, 128 j + 127].  The mask is the reference's sliding_window_mask
@@ -34,9 +49,13 @@ struct TileRange {
   int sink_blocks;       // blocks [0, sink_blocks) hold sink keys
 };
 
-__host__ __device__ inline TileRange tile_range(int tile, int window, int sinks) {
+// `block` > 0 (block-causal; window must be 0) lets a tile see past the diagonal, up to the end
+// of its last row's block; `n_tiles` bounds that.
+__host__ __device__ inline TileRange tile_range(int tile, int window, int sinks, int block = 0,
+                                                int n_tiles = 1 << 30) {
   TileRange r;
-  r.hi = tile;
+  r.hi = last_key_of_query(tile * kTile + kTile - 1, block) / kTile;
+  r.hi = r.hi < n_tiles - 1 ? r.hi : n_tiles - 1;
   r.lo = 0;
   r.sink_blocks = 0;
   if (window > 0) {
@@ -50,8 +69,9 @@ __host__ __device__ inline TileRange tile_range(int tile, int window, int sinks)
 
 // True when every (row, key) of query tile `tile` x key block `j` survives the
 // mask, so the element-wise predicate can be skipped.
-__host__ __device__ inline bool block_fully_visible(int tile, int j, int window, int sinks) {
-  if (j >= tile) return false;                                   // diagonal block
+__host__ __device__ inline bool block_fully_visible(int tile, int j, int window, int sinks, int block = 0,
+                                                    int t_len = 1 << 30) {
+  if (j * kTile + kTile - 1 > last_key_of_query(tile * kTile, block, t_len)) return false;   // the causal edge cuts in
   if (window > 0) {
     const int span = window - sinks;
     const int last_row = tile * kTile + kTile - 1;
@@ -78,8 +98,8 @@ __host__ __device__ inline int block_edges(int tile, int j, int window, int sink
 // The same two questions for a rectangle of query positions [q_lo, q_hi] x key positions
 // [k_lo, k_hi] (tiles of unequal height).
 __host__ __device__ inline bool rect_fully_visible(int q_lo, int q_hi, int k_lo, int k_hi,
-                                                   int window, int sinks) {
-  if (k_hi > q_lo) return false;                                           // causal edge cuts in
+                                                   int window, int sinks, int block = 0, int t_len = 1 << 30) {
+  if (k_hi > last_key_of_query(q_lo, block, t_len)) return false;          // causal edge cuts in
   if (window > 0 && k_lo <= q_hi - (window - sinks)) return false;         // lower window edge cuts in
   return true;
 }
@@ -105,17 +125,19 @@ __host__ __device__ inline int last_query_tile_of_block(int block, int n_ytiles,
 
 // Fused backward: key block `block`'s place in the fixed order in which the blocks that see
 // 128-row query tile `tile` add their dQ shares (ascending block index: sink blocks below the
-// window first, then the window's blocks up to the diagonal, which closes the sum).  *count is
-// the number of such blocks.
-__host__ __device__ inline int dq_turn_of_block(int block, int tile, int window, int sinks, int* count) {
-  const TileRange r = tile_range(tile, window, sinks);
+// window first, then the window's blocks up to the last one the tile sees -- the diagonal, or
+// beyond it under a block-causal mask of `mask_block` positions).  *count is the number of such blocks.
+__host__ __device__ inline int dq_turn_of_block(int block, int tile, int window, int sinks, int* count,
+                                                int mask_block = 0, int n_tiles = 1 << 30) {
+  const TileRange r = tile_range(tile, window, sinks, mask_block, n_tiles);
   const int extra = r.sink_blocks < r.lo ? r.sink_blocks : r.lo;
-  *count = extra + (tile - r.lo + 1);
+  *count = extra + (r.hi - r.lo + 1);
   return block < extra ? block : extra + (block - r.lo);
 }
 
-__host__ __device__ inline bool key_visible(int q, int k, int window, int sinks) {
-  if (k > q) return false;
+__host__ __device__ inline bool key_visible(int q, int k, int window, int sinks, int block = 0,
+                                            int t_len = 1 << 30) {
+  if (k > last_key_of_query(q, block, t_len)) return false;
   if (window == 0) return true;
   return (k > q - (window - sinks)) || (k < sinks);
 }

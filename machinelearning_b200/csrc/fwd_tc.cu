@@ -32,6 +32,7 @@ namespace {
 struct FwdParams {
   int T, H, Hkv;
   int window, sinks;
+  int block;              // > 0: block-causal mask of this many positions (window == 0)
   int n_tiles;            // ceil(T / 128)
   int n_units;            // ceil(n_tiles / NT)
   int total_units;        // n_units * B * H
@@ -99,7 +100,7 @@ __device__ __forceinline__ Unit<NT> make_unit(int u, const FwdParams& p, int BH)
 #pragma unroll
   for (int t = 0; t < NT; ++t) {
     w.valid[t] = (w.tile0 + t) < p.n_tiles;
-    w.tr[t] = tile_range(w.tile0 + t, p.window, p.sinks);
+    w.tr[t] = tile_range(w.tile0 + t, p.window, p.sinks, p.block, p.n_tiles);
     if (w.valid[t]) {
       w.lo = w.tr[t].lo < w.lo ? w.tr[t].lo : w.lo;
       hi = w.tr[t].hi > hi ? w.tr[t].hi : hi;
@@ -511,6 +512,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       const int tile = w.tile0 + t;
       const int qpos = tile * kTile + row;
+      const int qlim = last_key_of_query(qpos, p.block, p.T);     // last key this row sees (plain causal: itself)
       // Online softmax in base 2.  m_ref is the reference exponent (scaled units): P =
       // 2^(x - m_ref).  It starts at the first block's row maximum and is afterwards only
       // raised (with O and l rescaled) when a block's maximum exceeds it by more than 2^8,
@@ -549,14 +551,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         // its own are too few to cover the unit's latency (measured: 1760 clocks per row with
         // per-chunk branches against 1130 without).
         const int k0 = j * kTile;
-        const int edges = block_fully_visible(tile, j, p.window, p.sinks)
+        const int edges = block_fully_visible(tile, j, p.window, p.sinks, p.block, p.T)
                               ? -1 : block_edges(tile, j, p.window, p.sinks);
         if (edges == EDGE_CAUSAL) {
           // only the causal edge cuts the block: the row sees the columns up to its own
-          // position -- one compare per element against a per-thread limit
+          // position (block-causal: up to the end of its block) -- one compare per element
+          // against a per-thread limit
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const int last = qpos - (k0 + 32 * c);                       // last visible column of the chunk
+            const int last = qlim - (k0 + 32 * c);                       // last visible column of the chunk
             if (__all_sync(0xffffffffu, last >= 31)) continue;
 #pragma unroll
             for (int i = 0; i < 32; ++i)
@@ -757,6 +760,7 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
   fp.Hkv = p.Hkv;
   fp.window = p.window;
   fp.sinks = p.sinks;
+  fp.block = p.block;
   fp.n_tiles = (p.T + kTile - 1) / kTile;
   fp.n_units = (fp.n_tiles + NT - 1) / NT;
   fp.total_units = fp.n_units * p.B * p.H;

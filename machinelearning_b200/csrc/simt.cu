@@ -77,7 +77,9 @@ fwd_simt_kernel(Problem p, const T* __restrict__ q, const T* __restrict__ k,
   const T* kbase = k + (static_cast<long long>(b) * p.T * p.Hkv + hk) * D;
   const T* vbase = v + (static_cast<long long>(b) * p.T * p.Hkv + hk) * D;
 
-  const int n = nsink + (t - lo + 1);
+  int t_last = last_key_of_query(t, p.block);            // block-causal: to the end of the row's block
+  t_last = t_last < p.T - 1 ? t_last : p.T - 1;
+  const int n = nsink + (t_last - lo + 1);
   for (int idx = 0; idx < n; ++idx) {
     const int j = idx < nsink ? idx : lo + (idx - nsink);
     const T* krow = kbase + j * kv_stride;
@@ -196,7 +198,9 @@ dq_simt_kernel(Problem p, const T* __restrict__ dout, const T* __restrict__ q,
   const long long kv_stride = static_cast<long long>(p.Hkv) * D;
   const T* kbase = k + (static_cast<long long>(b) * p.T * p.Hkv + hk) * D;
   const T* vbase = v + (static_cast<long long>(b) * p.T * p.Hkv + hk) * D;
-  const int n = nsink + (t - lo + 1);
+  int t_last = last_key_of_query(t, p.block);            // block-causal: to the end of the row's block
+  t_last = t_last < p.T - 1 ? t_last : p.T - 1;
+  const int n = nsink + (t_last - lo + 1);
   for (int idx = 0; idx < n; ++idx) {
     const int j = idx < nsink ? idx : lo + (idx - nsink);
     const T* krow = kbase + j * kv_stride;
@@ -255,7 +259,7 @@ dkv_simt_kernel(Problem p, const T* __restrict__ dout, const T* __restrict__ q,
   for (int g = 0; g < group; ++g) {
     const int h = hk * group + g;
     const long long bh = static_cast<long long>(b) * p.H + h;
-    for (int i = j; i <= last; ++i) {
+    for (int i = first_query_of_key(j, p.block); i <= last; ++i) {
       const long long qoff = ((static_cast<long long>(b) * p.T + i) * p.H + h) * D;
       float qr[R], dor[R];
       float ps = 0.f, pd = 0.f;

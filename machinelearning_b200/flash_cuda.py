@@ -208,8 +208,13 @@ def supports(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
     return True
 
 
-def check_window(window: int, sinks: int) -> None:
-    """Same refusals as ``sliding_window_mask`` (``nanolab/mixers.py:119-123``)."""
+def check_window(window: int, sinks: int, block: int = 0) -> None:
+    """Same refusals as ``sliding_window_mask`` (``nanolab/mixers.py:119-123``), and the mixer's for a
+    block-causal mask next to a window (``mixers.py:300-304``)."""
+    if block < 0:
+        raise ValueError(f"block length must be >= 0, got {block}")
+    if block and window:
+        raise ValueError("block-causal (diffusion) attention and SWA are mutually exclusive masks")
     if window == 0:
         if sinks:
             raise ValueError("swa sinks set without a window")
@@ -221,9 +226,10 @@ def check_window(window: int, sinks: int) -> None:
                          f"got sinks={sinks} window={window}")
 
 
-def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0):
+def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0, block: int = 0):
     """(O, LSE) through the C ABI.  Contiguous same-dtype CUDA tensors only
-    (reference native entry: ``flash_attn_cuda.cu:1655-1704``)."""
+    (reference native entry: ``flash_attn_cuda.cu:1655-1704``).  ``block > 0``: the block-causal mask
+    of ``nanolab/mixers.py:78-93`` instead of the causal one."""
     lib = _load()
     if lib is None:
         raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
@@ -234,17 +240,17 @@ def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0):
     o = torch.empty_like(q)
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
-        st = lib.nlfa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
-                          B, T, H, Hkv, D, float(scale), int(window), int(sinks),
-                          _DTYPE_CODE[q.dtype],
-                          _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
-                          torch.cuda.current_stream().cuda_stream)
+        st = lib.nlfa_fwd_masked(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                                 B, T, H, Hkv, D, float(scale), int(window), int(sinks), int(block),
+                                 _DTYPE_CODE[q.dtype],
+                                 _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
+                                 torch.cuda.current_stream().cuda_stream)
     _lib.check("nlfa_fwd", st)
     return o, lse
 
 
 def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sinks: int = 0,
-        fused: bool | None = None):
+        fused: bool | None = None, block: int = 0):
     """(dQ, dK, dV) through the C ABI (reference: ``flash_attn_cuda.cu:1744-1813``).
 
     ``fused`` picks the backward's layout on the tensor-core path at head dims up to 64: the
@@ -266,15 +272,15 @@ def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sin
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     nbytes = lib.nlfa_bwd_fused_scratch_bytes(B, T, H, D) if fused else lib.nlfa_bwd_scratch_bytes(B, T, H)
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
-    entry = lib.nlfa_bwd_fused if fused else lib.nlfa_bwd
+    passes = (_lib.PASS_DELTA | _lib.PASS_FUSED) if fused else _lib.PASS_ALL
     with torch.cuda.device(q.device):
-        st = entry(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                   lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                   scratch.data_ptr(), scratch.numel(), B, T, H, Hkv, D, float(scale),
-                   int(window), int(sinks), _DTYPE_CODE[q.dtype],
-                   _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
-                   torch.cuda.current_stream().cuda_stream)
-    _lib.check("nlfa_bwd_fused" if fused else "nlfa_bwd", st)
+        st = lib.nlfa_bwd_masked(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                 lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                 scratch.data_ptr(), scratch.numel(), B, T, H, Hkv, D, float(scale),
+                                 int(window), int(sinks), int(block), _DTYPE_CODE[q.dtype],
+                                 _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT, passes,
+                                 torch.cuda.current_stream().cuda_stream)
+    _lib.check("nlfa_bwd_masked", st)
     return dq, dk, dv
 
 
@@ -283,12 +289,12 @@ class _FlashAttnFn(torch.autograd.Function):
     backward (reference: ``flash_cuda.py:205-230``)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, scale, use_mma, window, sinks):
-        o, lse = fwd(q, k, v, scale, use_mma, window, sinks)
+    def forward(ctx, q, k, v, scale, use_mma, window, sinks, block=0):
+        o, lse = fwd(q, k, v, scale, use_mma, window, sinks, block)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.scale = float(scale)
         ctx.use_mma = bool(use_mma)
-        ctx.window, ctx.sinks = int(window), int(sinks)
+        ctx.window, ctx.sinks, ctx.block = int(window), int(sinks), int(block)
         return o
 
     @staticmethod
@@ -296,15 +302,15 @@ class _FlashAttnFn(torch.autograd.Function):
     def backward(ctx, dout):
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = bwd(dout.contiguous(), q, k, v, o, lse, ctx.scale, ctx.use_mma,
-                         ctx.window, ctx.sinks)
-        return dq, dk, dv, None, None, None, None
+                         ctx.window, ctx.sinks, block=ctx.block)
+        return dq, dk, dv, None, None, None, None, None
 
 
 def _tensor_path_fits(dtype, head_dim) -> bool:
     return dtype in MMA_DTYPES and head_dim in MMA_HEAD_DIMS
 
 
-def prepare(q, k, v, scale, use_mma, window, sinks):
+def prepare(q, k, v, scale, use_mma, window, sinks, block=0):
     """The checks, defaults and casts of ``flash_attn`` (reference: ``flash_cuda.py:251-278``);
     returns ``(q, k, v, scale, use_mma)`` ready for the kernels."""
     if not supports(q, k, v):
@@ -314,7 +320,7 @@ def prepare(q, k, v, scale, use_mma, window, sinks):
             f"v={tuple(v.shape)}/{v.dtype}); head_dim must be one of "
             f"{SUPPORTED_HEAD_DIMS} and the effective dtype one of "
             f"{SUPPORTED_DTYPES}")
-    check_window(window, sinks)
+    check_window(window, sinks, block)
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     dtype = effective_dtype(q, k, v)
@@ -343,19 +349,22 @@ def prepare(q, k, v, scale, use_mma, window, sinks):
 
 def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                scale: float | None = None, use_mma: bool | None = None, *,
-               window: int = 0, sinks: int = 0) -> torch.Tensor:
+               window: int = 0, sinks: int = 0, block: int = 0) -> torch.Tensor:
     """Causal GQA flash attention. q [B,T,H,D], k/v [B,T,Hkv,D] -> [B,T,H,D].
 
     Same contract as the reference (``flash_cuda.py:233-279``): raises
     ``ValueError`` for unsupported inputs instead of falling back; casts q/k/v to
     the effective dtype and makes them contiguous as autograd ops.  ``window`` /
-    ``sinks`` select the sliding-window mask; ``window=0`` is plain causal.
+    ``sinks`` select the sliding-window mask; ``window=0`` is plain causal.  ``block > 0``
+    selects the block-causal mask of nanolab's diffusion / semi-autoregressive mode instead
+    (``nanolab/mixers.py:78-93``: a query sees its own block of ``block`` positions and every
+    earlier one; ``block >= T`` is fully bidirectional attention); it excludes a window.
     """
-    q, k, v, scale, use_mma = prepare(q, k, v, scale, use_mma, window, sinks)
+    q, k, v, scale, use_mma = prepare(q, k, v, scale, use_mma, window, sinks, block)
     if torch.compiler.is_compiling():
         from . import compile_ops              # registered operators: one graph node instead of a graph break
-        return compile_ops.attn_fwd(q, k, v, float(scale), bool(use_mma), int(window), int(sinks))[0]
-    return _FlashAttnFn.apply(q, k, v, scale, use_mma, window, sinks)
+        return compile_ops.attn_fwd(q, k, v, float(scale), bool(use_mma), int(window), int(sinks), int(block))[0]
+    return _FlashAttnFn.apply(q, k, v, scale, use_mma, window, sinks, block)
 
 
 def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tensor, scale: float | None = None, *,

@@ -13,8 +13,9 @@ document:
     (``nanolab/mixers.py:347-370``) extended to sliding windows: the reference
     declines every step whose mixer has ``swa_window`` set because its kernel
     takes no mask (``mixers.py:357``); these kernels take ``window`` / ``sinks``
-    with the mask of ``sliding_window_mask`` (``mixers.py:125-132``), so only
-    non-causal and block-causal steps are declined.  Returns the ``[B,T,H,D]``
+    with the mask of ``sliding_window_mask`` (``mixers.py:125-132``) and ``block``
+    with that of ``block_causal_mask`` (``mixers.py:78-93``; a non-causal step is
+    one block of the whole sequence), so every mask the mixer has goes through.  Returns the ``[B,T,H,D]``
     result, or ``None`` when the caller should use its SDPA branch -- with the
     reason logged once per mixer, as the reference does, so that an enabled flag
     never silently means nothing.
@@ -53,22 +54,30 @@ def decline_reason(mixer, q, k, v) -> str | None:
     """
     if not getattr(mixer, "flash_cuda", False):
         return "flash_cuda is off"
-    if not getattr(mixer, "causal", True):
-        return "non-causal attention"
-    if getattr(mixer, "block_attn", 0) > 0:
-        return "block-causal attention"
     window = int(getattr(mixer, "swa_window", 0) or 0)
     sinks = int(getattr(mixer, "swa_sinks", 0) or 0)
-    if window:
-        try:
-            flash_cuda.check_window(window, sinks)
-        except ValueError as e:
-            return str(e)
+    block = mask_block(mixer, q.shape[1])
+    if window and not getattr(mixer, "causal", True):
+        return "SWA is causal-only"                                 # the mixer raises for this itself (mixers.py:323-325)
+    try:
+        flash_cuda.check_window(window, sinks, block)
+    except ValueError as e:
+        return str(e)
     if not flash_cuda.supports(q, k, v):
         return f"unsupported inputs: {tuple(q.shape)} {q.dtype} on {q.device}"
     if not flash_cuda.is_available():
         return flash_cuda.unavailable_reason()
     return None
+
+
+def mask_block(mixer, T: int) -> int:
+    """The block length of the mixer's current mask, 0 for a causal one: ``block_attn`` when set
+    (``nanolab/mixers.py:319-321``), and -- a non-causal step being one bidirectional block -- ``T``
+    when ``causal`` is off (``mixers.py:338``, ``is_causal=self.causal``)."""
+    block = int(getattr(mixer, "block_attn", 0) or 0)
+    if block > 0:
+        return block
+    return 0 if getattr(mixer, "causal", True) else int(T)
 
 
 def attention_core(mixer, q, k, v, scale):
@@ -77,7 +86,8 @@ def attention_core(mixer, q, k, v, scale):
     if why is None:
         return flash_cuda.flash_attn(q, k, v, scale,
                                      window=int(getattr(mixer, "swa_window", 0) or 0),
-                                     sinks=int(getattr(mixer, "swa_sinks", 0) or 0))
+                                     sinks=int(getattr(mixer, "swa_sinks", 0) or 0),
+                                     block=mask_block(mixer, q.shape[1]))
     if getattr(mixer, "flash_cuda", False) and not getattr(mixer, "_flash_declined", False):
         try:
             mixer._flash_declined = True

@@ -9,6 +9,9 @@ TEST INFRASTRUCTURE.  A restatement of the reference's brute-force oracle:
   ``k <= q`` and (``k > q - (window - sinks)`` or ``k < sinks``).  ``window == 0``
   means plain causal (the reference's ``Attention`` without ``swa_window``);
   ``window >= T`` degenerates to plain causal (``mixers.py:117-118``).
+* block-causal mask -- ``nanolab/mixers.py:78-93`` (``block_causal_mask``): with
+  ``blk = position // block``, keep ``blk[q] >= blk[k]`` (bidirectional inside a
+  block, causal across blocks); it excludes a window (``mixers.py:300-304``).
 * backward -- the reference differentiates its forward with autograd
   (``nanolab/tests.py:386-388``).  Here the same gradients are written out in
   closed form, the algebra of ``flash_attn_cuda.cu:1265-1482``:
@@ -24,15 +27,21 @@ from __future__ import annotations
 import numpy as np
 
 
-def keep_mask(T: int, window: int = 0, sinks: int = 0) -> np.ndarray:
+def keep_mask(T: int, window: int = 0, sinks: int = 0, block: int = 0) -> np.ndarray:
     """[T,T] boolean keep-mask, rows = queries, columns = keys.
 
     Mirrors ``sliding_window_mask`` (``nanolab/mixers.py:119-132``) including its
-    argument checks; ``window == 0`` is the plain causal mask.
+    argument checks; ``window == 0`` is the plain causal mask, or, with ``block > 0``,
+    ``block_causal_mask`` (``mixers.py:88-91``).
     """
     i = np.arange(T)
     q, k = i[:, None], i[None, :]
     causal = k <= q
+    if block:
+        if window:
+            raise ValueError("block-causal (diffusion) attention and SWA are mutually exclusive masks")
+        blk = i // block
+        return blk[:, None] >= blk[None, :]
     if window == 0:
         if sinks:
             raise ValueError("swa sinks set without a window")
@@ -48,8 +57,10 @@ def keep_mask(T: int, window: int = 0, sinks: int = 0) -> np.ndarray:
     return keep
 
 
-def unmasked_pairs(T: int, window: int = 0, sinks: int = 0) -> int:
+def unmasked_pairs(T: int, window: int = 0, sinks: int = 0, block: int = 0) -> int:
     """Number of (query, key) pairs one head attends to: the FLOP count's unit."""
+    if block:
+        return int(keep_mask(T, block=block).sum())
     if window == 0:
         return T * (T + 1) // 2
     span = window - sinks
@@ -72,13 +83,13 @@ def _f64(x) -> np.ndarray:
     return np.asarray(x, dtype=np.float64)
 
 
-def attention_fwd(q, k, v, scale: float, window: int = 0, sinks: int = 0):
+def attention_fwd(q, k, v, scale: float, window: int = 0, sinks: int = 0, block: int = 0):
     """(O [B,T,H,D], LSE [B,H,T]) in float64.  q [B,T,H,D], k/v [B,T,Hkv,D]."""
     q, k, v = _f64(q), _f64(k), _f64(v)
     B, T, H, D = q.shape
     Hkv = k.shape[2]
     group = H // Hkv
-    keep = keep_mask(T, window, sinks)
+    keep = keep_mask(T, window, sinks, block)
     o = np.empty((B, T, H, D))
     lse = np.empty((B, H, T))
     for b in range(B):
@@ -99,13 +110,13 @@ def attention_delta(o, dout) -> np.ndarray:
     return np.einsum("bthd,bthd->bht", _f64(o), _f64(dout))
 
 
-def attention_bwd(dout, q, k, v, scale: float, window: int = 0, sinks: int = 0):
+def attention_bwd(dout, q, k, v, scale: float, window: int = 0, sinks: int = 0, block: int = 0):
     """(dQ, dK, dV) in float64, recomputing P from the inputs."""
     dout, q, k, v = _f64(dout), _f64(q), _f64(k), _f64(v)
     B, T, H, D = q.shape
     Hkv = k.shape[2]
     group = H // Hkv
-    keep = keep_mask(T, window, sinks)
+    keep = keep_mask(T, window, sinks, block)
     dq = np.zeros_like(q)
     dk = np.zeros_like(k)
     dv = np.zeros_like(v)

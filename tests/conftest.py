@@ -22,9 +22,10 @@ def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
 
 def load_golden(path):
     d = np.load(path)
-    B, T, H, Hkv, D, window, sinks = (int(x) for x in d["meta"])
+    B, T, H, Hkv, D, window, sinks = (int(x) for x in d["meta"][:7])
+    block = int(d["meta"][7]) if len(d["meta"]) > 7 else 0           # block-causal fixtures carry their block length
     case = dict(name=pathlib.Path(path).stem, B=B, T=T, H=H, Hkv=Hkv, D=D,
-                window=window, sinks=sinks, scale=float(d["scale"]))
+                window=window, sinks=sinks, block=block, scale=float(d["scale"]))
     for key in ("q", "k", "v", "dout"):
         case[key] = bf16_bits_to_f32(d[key])
     for key in ("o", "lse", "dq", "dk", "dv"):
@@ -34,7 +35,7 @@ def load_golden(path):
 
 def golden_paths():
     """The attention fixtures (the whole-model and prologue fixtures have their own loaders)."""
-    return sorted([*GOLDEN.glob("causal_*.npz"), *GOLDEN.glob("swa_*.npz")])
+    return sorted([*GOLDEN.glob("causal_*.npz"), *GOLDEN.glob("swa_*.npz"), *GOLDEN.glob("blockcausal_*.npz")])
 
 
 @pytest.fixture(params=golden_paths(), ids=lambda p: p.stem)

@@ -43,6 +43,15 @@ CASES = [
     ("swa_t65_w64_s4", 1, 65, 2, 2, 32, 64, 4),
     ("swa_t128_w32_s1", 1, 128, 2, 2, 32, 32, 1),
 ]
+# block-causal masks (nanolab/mixers.py:78-93): (name, B, T, H, Hkv, D, block); the block lengths
+# straddle the kernels' 128-row tiles on purpose
+BLOCK_CASES = [
+    ("blockcausal_t300_b32", 1, 300, 2, 1, 64, 32),
+    ("blockcausal_t300_b100", 1, 300, 2, 2, 32, 100),
+    ("blockcausal_t260_b128", 1, 260, 2, 1, 64, 128),
+    ("blockcausal_t200_b512", 1, 200, 2, 2, 64, 512),      # one block: fully bidirectional
+    ("blockcausal_t150_b1", 1, 150, 2, 1, 32, 1),           # blocks of one: plain causal
+]
 
 
 def main(ref_root: str) -> None:
@@ -50,15 +59,30 @@ def main(ref_root: str) -> None:
     from nanolab.csrc.flash_attn_sim import reference_attention
     from nanolab import mixers
 
-    for seed, (name, B, T, H, Hkv, D, window, sinks) in enumerate(CASES):
+    cases = [(*c, 0) for c in CASES] + [(*c[:6], 0, 0, c[6]) for c in BLOCK_CASES]
+    for seed, (name, B, T, H, Hkv, D, window, sinks, block) in enumerate(cases):
         g = torch.Generator().manual_seed(1000 + seed)
         bf = lambda *shape: torch.randn(*shape, generator=g).bfloat16()
         q, k, v, do = bf(B, T, H, D), bf(B, T, Hkv, D), bf(B, T, Hkv, D), bf(B, T, H, D)
         bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)
         scale = 1.0 / math.sqrt(D)
         qa, ka, va = (t.double().requires_grad_() for t in (q, k, v))
-        if window == 0:
+        if window == 0 and block == 0:
             o, lse = reference_attention(qa, ka, va, scale)
+        elif block:
+            # reference_attention's own lines with the reference's block-causal keep-mask
+            group = H // Hkv
+            qs = qa.permute(0, 2, 1, 3)
+            ks = ka.repeat_interleave(group, dim=2).permute(0, 2, 1, 3)
+            vs = va.repeat_interleave(group, dim=2).permute(0, 2, 1, 3)
+            scores = (qs @ ks.transpose(-1, -2)) * scale
+            keep = mixers.block_causal_mask(T, block, "cpu", {})
+            scores = scores.masked_fill(~keep, -math.inf)
+            lse = torch.logsumexp(scores, dim=-1).contiguous()
+            o = (torch.softmax(scores, dim=-1) @ vs).permute(0, 2, 1, 3).contiguous()
+            if block == 1:                                     # must be the plain causal reference
+                o_c, lse_c = reference_attention(qa.detach(), ka.detach(), va.detach(), scale)
+                assert (o_c - o.detach()).abs().max() < 1e-12 and (lse_c - lse.detach()).abs().max() < 1e-12
         else:
             # reference_attention's own lines with the reference's SWA keep-mask
             group = H // Hkv
@@ -80,7 +104,7 @@ def main(ref_root: str) -> None:
                  q=bits(q), k=bits(k), v=bits(v), dout=bits(do),
                  o=o.detach().numpy(), lse=lse.detach().numpy(),
                  dq=qa.grad.numpy(), dk=ka.grad.numpy(), dv=va.grad.numpy(),
-                 meta=np.array([B, T, H, Hkv, D, window, sinks]),
+                 meta=np.array([B, T, H, Hkv, D, window, sinks] + ([block] if block else [])),
                  scale=np.array(scale))
         print(f"wrote {name}.npz")
 

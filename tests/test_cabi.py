@@ -107,6 +107,15 @@ def test_mask_geometry_matches_the_elementwise_predicate(lib, T, window, sinks, 
     assert lib.nlfa_check_mask_geometry(T, window, sinks, stream_rows) == 0
 
 
+@pytest.mark.parametrize("T,block", [(1024, 1), (1024, 32), (1024, 96), (1024, 128), (900, 256), (700, 333),
+                                     (1024, 4096), (385, 7), (2048, 512)])
+@pytest.mark.parametrize("stream_rows", [64, 128])
+def test_block_causal_geometry_matches_the_elementwise_predicate(lib, T, block, stream_rows):
+    """The same checks for the block-causal mask (keep key k for query q iff q // block >= k // block)."""
+    assert lib.nlfa_check_mask_geometry_masked(T, 0, 0, block, stream_rows) == 0
+    assert lib.nlfa_check_mask_geometry_masked(T, 64, 4, block, stream_rows) < 0      # a window excludes it
+
+
 def test_mask_geometry_rejects_bad_arguments(lib):
     assert lib.nlfa_check_mask_geometry(0, 0, 0, 128) < 0
     assert lib.nlfa_check_mask_geometry(256, 8, 8, 128) < 0

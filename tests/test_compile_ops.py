@@ -22,14 +22,14 @@ def test_shape_functions_and_autograd_formula_on_fake_tensors():
         q = torch.empty(2, 100, 8, 64, dtype=torch.bfloat16, device="cuda", requires_grad=True)
         k = torch.empty(2, 100, 2, 64, dtype=torch.bfloat16, device="cuda", requires_grad=True)
         v = torch.empty(2, 100, 2, 64, dtype=torch.bfloat16, device="cuda", requires_grad=True)
-        o, lse = torch.ops.nlfa.attn_fwd(q, k, v, 0.125, True, 0, 0)
+        o, lse = torch.ops.nlfa.attn_fwd(q, k, v, 0.125, True, 0, 0, 0)
         assert o.shape == q.shape and o.dtype == torch.bfloat16 and o.device.type == "cuda"
         assert lse.shape == (2, 8, 100) and lse.dtype == torch.float32
         assert o.grad_fn is not None                    # the autograd formula is attached
         # running the engine needs a CUDA context even for fake tensors; the backward operator's
         # shape function is checked directly (the GPU tests run the formula end to end)
         dq, dk, dv = torch.ops.nlfa.attn_bwd(torch.empty_like(o), q.detach(), k.detach(), v.detach(), o.detach(),
-                                             lse, 0.125, True, 0, 0)
+                                             lse, 0.125, True, 0, 0, 0)
         assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
         assert dk.dtype == torch.bfloat16
 
@@ -160,5 +160,5 @@ def test_opcheck_passes_on_the_forward_operator():
     from machinelearning_b200 import flash_cuda
     assert flash_cuda.is_available()
     q, k, v = (torch.randn(1, 64, h, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True) for h in (2, 1, 1))
-    torch.library.opcheck(torch.ops.nlfa.attn_fwd.default, (q, k, v, 0.125, True, 0, 0),
+    torch.library.opcheck(torch.ops.nlfa.attn_fwd.default, (q, k, v, 0.125, True, 0, 0, 0),
                           test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))

@@ -50,9 +50,9 @@ def device_status_ok():
     return _lib.load().nlfa_device_status(ctypes.byref(raw)) == 0 and raw.value == 0
 
 
-def run_fwd_bwd(fc, q, k, v, do, scale, use_mma, window=0, sinks=0):
+def run_fwd_bwd(fc, q, k, v, do, scale, use_mma, window=0, sinks=0, block=0):
     q, k, v = (t.detach().clone().requires_grad_() for t in (q, k, v))
-    y = fc.flash_attn(q, k, v, scale, use_mma=use_mma, window=window, sinks=sinks)
+    y = fc.flash_attn(q, k, v, scale, use_mma=use_mma, window=window, sinks=sinks, block=block)
     dq, dk, dv = torch.autograd.grad(y, (q, k, v), do)
     return y, dq, dk, dv
 
@@ -74,8 +74,8 @@ def test_selftest_passes_for_every_tensor_core_variant(fc):
 def test_simt_fp32_matches_reference_golden(fc, path):
     g = load_golden(path)
     q, k, v, do = (torch.from_numpy(g[n]).cuda() for n in ("q", "k", "v", "dout"))
-    o, lse = fc.fwd(q, k, v, g["scale"], False, g["window"], g["sinks"])
-    dq, dk, dv = fc.bwd(do, q, k, v, o, lse, g["scale"], False, g["window"], g["sinks"])
+    o, lse = fc.fwd(q, k, v, g["scale"], False, g["window"], g["sinks"], block=g["block"])
+    dq, dk, dv = fc.bwd(do, q, k, v, o, lse, g["scale"], False, g["window"], g["sinks"], block=g["block"])
     assert mabs(o, g["o"]) <= ABS_F32
     assert mabs(lse, g["lse"]) <= ABS_F32
     for got, name in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
@@ -91,11 +91,11 @@ def test_tensor_core_matches_reference_golden(fc, path, dtype):
     if dtype is torch.bfloat16:
         ref = {n: g[n] for n in ("o", "lse", "dq", "dk", "dv")}
     else:
-        o_r, lse_r = orc.attention_fwd(q, k, v, g["scale"], g["window"], g["sinks"])
-        gq, gk, gv = orc.attention_bwd(do, q, k, v, g["scale"], g["window"], g["sinks"])
+        o_r, lse_r = orc.attention_fwd(q, k, v, g["scale"], g["window"], g["sinks"], g["block"])
+        gq, gk, gv = orc.attention_bwd(do, q, k, v, g["scale"], g["window"], g["sinks"], g["block"])
         ref = dict(o=o_r, lse=lse_r, dq=gq, dk=gk, dv=gv)
-    o, lse = fc.fwd(q, k, v, g["scale"], True, g["window"], g["sinks"])
-    dq, dk, dv = fc.bwd(do, q, k, v, o, lse, g["scale"], True, g["window"], g["sinks"])
+    o, lse = fc.fwd(q, k, v, g["scale"], True, g["window"], g["sinks"], block=g["block"])
+    dq, dk, dv = fc.bwd(do, q, k, v, o, lse, g["scale"], True, g["window"], g["sinks"], block=g["block"])
     assert device_status_ok()
     assert rel(o, ref["o"]) <= REL_16BIT
     assert mabs(lse, ref["lse"]) <= 1e-3
@@ -138,6 +138,42 @@ def test_tensor_core_fwd_bwd_vs_oracle(fc, B, T, H, Hkv, D, window, sinks, dtype
     # the logsumexp tape
     _, lse = fc.fwd(q, k, v, scale, True, window, sinks)
     assert mabs(lse, lse_r) <= 1e-3
+
+
+BLOCK_CASES = [
+    # B, T, H, Hkv, D, block: the reference's block-causal mask (nanolab/mixers.py:78-93)
+    (1, 1024, 2, 2, 64, 96),         # blocks that straddle the 128-row tiles
+    (2, 640, 4, 2, 64, 128),         # blocks equal to the tiles
+    (1, 700, 2, 1, 128, 333),
+    (1, 520, 2, 2, 32, 40),
+    (1, 300, 3, 1, 64, 1024),        # one block: fully bidirectional
+    (1, 200, 2, 2, 64, 1),           # blocks of one position: plain causal
+    (1, 1536, 1, 1, 64, 512),
+]
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,D,block", BLOCK_CASES)
+def test_block_causal_mask_tensor_core_and_simt_vs_oracle(fc, B, T, H, Hkv, D, block):
+    torch.manual_seed(1)
+    q, k, v, do = (torch.randn(B, T, h, D, device="cuda").bfloat16() for h in (H, Hkv, Hkv, H))
+    scale = 1.0 / math.sqrt(D)
+    o_r, lse_r = orc.attention_fwd(q, k, v, scale, block=block)
+    gq, gk, gv = orc.attention_bwd(do, q, k, v, scale, block=block)
+    for use_mma in (True, False):
+        y, dq, dk, dv = run_fwd_bwd(fc, q, k, v, do, scale, use_mma, block=block)
+        assert device_status_ok()
+        for got, want, name in ((y, o_r, "o"), (dq, gq, "dq"), (dk, gk, "dk"), (dv, gv, "dv")):
+            assert rel(got, want) <= REL_16BIT, (use_mma, name)
+        _, lse = fc.fwd(q, k, v, scale, use_mma, block=block)
+        assert mabs(lse, lse_r) <= 1e-3
+    # fp32 inputs through the SIMT kernels: the 1e-5 bar
+    q32, k32, v32, do32 = (t.float() for t in (q, k, v, do))
+    y, dq, dk, dv = run_fwd_bwd(fc, q32, k32, v32, do32, scale, False, block=block)
+    assert mabs(y, o_r) <= ABS_F32
+    for got, want in ((dq, gq), (dk, gk), (dv, gv)):
+        assert mabs(got, want) <= 2 * ABS_F32
+    with pytest.raises(ValueError, match="mutually exclusive"):
+        fc.flash_attn(q, k, v, scale, window=64, sinks=4, block=block or 8)
 
 
 @pytest.mark.parametrize("B,T,H,Hkv,D,window,sinks", [c for c in CASES if c[1] <= 700])

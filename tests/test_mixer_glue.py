@@ -55,14 +55,22 @@ def test_install_refuses_after_mixers_bound_elsewhere():
 
 @pytest.mark.parametrize("kw,needle", [
     (dict(flash_cuda=False), "off"),
-    (dict(causal=False), "non-causal"),
-    (dict(block_attn=16), "block-causal"),
+    (dict(causal=False, swa_window=8, swa_sinks=2), "causal-only"),      # nanolab/mixers.py:323-325
+    (dict(block_attn=16, swa_window=8, swa_sinks=2), "mutually exclusive"),  # mixers.py:300-304
     (dict(swa_window=8, swa_sinks=8), "sinks"),
 ])
 def test_decline_reasons_before_any_load(kw, needle):
     q, k, v = _cpu_qkv()
     why = mixer_glue.decline_reason(FakeMixer(**kw), q, k, v)
     assert why is not None and needle in why
+
+
+def test_mask_block_follows_the_mixers_mode():
+    """``block_attn`` wins (mixers.py:319-321); a non-causal step is one block of the whole sequence."""
+    assert mixer_glue.mask_block(FakeMixer(), 100) == 0
+    assert mixer_glue.mask_block(FakeMixer(block_attn=16), 100) == 16
+    assert mixer_glue.mask_block(FakeMixer(causal=False), 100) == 100
+    assert mixer_glue.mask_block(FakeMixer(causal=False, block_attn=8), 100) == 8
 
 
 def test_cpu_tensors_decline_and_warn_once(caplog):
@@ -100,3 +108,22 @@ def test_windowed_mixer_routes_through_the_kernel():
                                         0.125, window=64, sinks=4)
     err = np.abs(y.float().cpu().numpy() - ref).max() / np.abs(ref).max()
     assert err <= 2e-2, err        # relative, bf16 tolerance of the path
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("kw,block", [(dict(block_attn=48), 48), (dict(causal=False), 200)])
+def test_block_causal_and_bidirectional_steps_route_through_the_kernel(kw, block):
+    """The diffusion modes of the mixer (``set_block_attn`` / ``set_causal(False)``, nanolab/model.py:305-314)
+    against the oracle with the reference's block-causal mask."""
+    from oracle import attention_f64
+    assert flash_cuda.is_available(), flash_cuda.unavailable_reason()
+    g = torch.Generator().manual_seed(9)
+    B, T, H, Hkv, D = 2, 200, 4, 2, 64
+    q = torch.randn(B, T, H, D, generator=g).bfloat16()
+    k = torch.randn(B, T, Hkv, D, generator=g).bfloat16()
+    v = torch.randn(B, T, Hkv, D, generator=g).bfloat16()
+    m = FakeMixer(**kw)
+    y = mixer_glue.attention_core(m, q.cuda(), k.cuda(), v.cuda(), 0.125)
+    assert y is not None and not m._flash_declined
+    ref, _ = attention_f64.attention_fwd(q.double().numpy(), k.double().numpy(), v.double().numpy(), 0.125, block=block)
+    assert np.abs(y.float().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max()

@@ -11,9 +11,9 @@ from oracle import sdpa_port
 
 def test_oracle_matches_reference_golden(golden):
     g = golden
-    o, lse = orc.attention_fwd(g["q"], g["k"], g["v"], g["scale"], g["window"], g["sinks"])
+    o, lse = orc.attention_fwd(g["q"], g["k"], g["v"], g["scale"], g["window"], g["sinks"], g["block"])
     dq, dk, dv = orc.attention_bwd(g["dout"], g["q"], g["k"], g["v"], g["scale"],
-                                   g["window"], g["sinks"])
+                                   g["window"], g["sinks"], g["block"])
     # same bar the reference holds its own CPU mirror to (nanolab/tests.py:280-293)
     for name, got in (("o", o), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
         assert np.abs(got - g[name]).max() < 1e-12, f"{g['name']}: {name}"
