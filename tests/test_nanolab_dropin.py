@@ -172,3 +172,35 @@ def test_real_swa_mixer_through_attention_core():
     print("swa ok", l_on, l_off, worst)
     """)
     assert "swa ok" in out
+
+
+@needs_nanolab
+@pytest.mark.gpu
+def test_real_gpt_in_its_diffusion_modes_through_attention_core():
+    """nanolab's own ``GPT.set_block_attention`` / ``set_causal(False)`` (``nanolab/model.py:295-314``):
+    the block-causal and the bidirectional step go through the kernels (routing as in the SWA case) and
+    give the logits of the SDPA branch."""
+    out = run_script(GPU_COMMON + """
+    mixers.Attention._flash_cuda_attn = lambda self, q, k, v, scale: mixer_glue.attention_core(self, q, k, v, scale)
+    on, cfg, opt_on = make(True)
+    off, _, _ = make(False)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randint(0, cfg.vocab_size, (cfg.batch_size, cfg.block_size), generator=g).cuda()
+    for _ in range(2):                       # off the zero-initialised output projections
+        one_step(on, cfg, opt_on, x)
+    off.load_state_dict(on.state_dict())
+    for mode in ("block 48", "block 256 (one block)", "bidirectional"):
+        for m in (on, off):
+            m.set_causal(mode != "bidirectional")
+            m.set_block_attention(48 if mode == "block 48" else 256 if mode.startswith("block 256") else 0)
+        before = calls["fwd"]
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            la, _ = on(x, x)
+            lb, _ = off(x, x)
+        assert calls["fwd"] - before == cfg.n_layer, (mode, calls)
+        err = (la.float() - lb.float()).abs().max().item() / lb.float().abs().max().item()
+        assert err <= 2e-2, (mode, err)
+        print(mode, "ok", err)
+    print("diffusion ok")
+    """)
+    assert "diffusion ok" in out
