@@ -33,6 +33,7 @@ attention core in the library, next to the same step with the flag off (SDPA).
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import math
 import os
@@ -725,7 +726,9 @@ def run_whole_model_arm(args, rank, world, local_rank):
         barrier()
         loss = (first_loss, third_loss)
         flops_tok = model.flops_per_token()
+        step.close()
         del model, step
+        gc.collect()
         torch.cuda.empty_cache()
         return (sharding.max_over_ranks(resident, dev), sharding.max_over_ranks(e2e, dev), n_calls, loss,
                 flops_tok, sampler.summary() if sampler else None)
@@ -743,7 +746,7 @@ def run_whole_model_arm(args, rank, world, local_rank):
         "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WHOLE_MODEL_TEXT, "global_batch": GLOBAL_BATCH, "per_gpu_batch": per_rank,
-                   "parallelism": f"data-parallel x{world}, flat-bucket NCCL all-reduce of the gradients",
+                   "parallelism": f"data-parallel x{world}, bucketed NCCL all-reduce of the gradients overlapped with the backward",
                    "l2": "activations and weights far larger than the 126 MB L2",
                    "params": 123699612, "flops_per_token": flops_tok,
                    "launch": "whole step replayed from one CUDA graph" if captured.get(True) else "eager launches"},
@@ -807,6 +810,7 @@ def main():
             run_gpu_arm(args, shape, rank, world, local_rank)
     finally:
         if world > 1:
+            torch.cuda.synchronize()
             dist.destroy_process_group()
     return 0
 

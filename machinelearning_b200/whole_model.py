@@ -259,16 +259,38 @@ class GPT(nn.Module):
         return logits, loss
 
 
+class _Bucket:
+    """A flat fp32 buffer that holds the gradients of a run of parameters (their ``.grad`` are views of it)."""
+
+    def __init__(self, params, device):
+        self.params = params
+        self.flat = torch.zeros(sum(p.numel() for p in params), dtype=torch.float32, device=device)
+        self.pending = len(params)
+        self.launched = False
+        offset = 0
+        for p in params:
+            p.grad = self.flat[offset:offset + p.numel()].view_as(p)
+            offset += p.numel()
+
+
 class DataParallelStep:
     """One optimiser step of the whole-model configuration on this rank's share of the batch.
 
     ``step(idx, targets)``: autocast forward, backward, gradient average across
     ranks, global-norm clip (nanolab's default 1.0, ``config.py:163``), fused AdamW.
-    Gradients are averaged in flat fp32 buckets of ``bucket_mb``: every parameter
-    that received a gradient is packed, one ``all_reduce`` runs per bucket, and
-    the result is unpacked -- layer 0's ``vr_lambda`` never gets a gradient (it has
-    no ``v0``), which is why this does not use a wrapper that expects every
-    parameter to take part.  With one rank no collective is issued.
+    The average is the reference's only data-parallel convention, a per-gradient
+    all-reduce (``Rust_MLKit/arch_02_value_resid/train_gpt_sprint_native.py:1407``,
+    ``:1916``, ``:2006``: ``if p.grad is not None: all_reduce(p.grad, AVG)``), done in
+    flat fp32 buckets of ``bucket_mb`` and overlapped with the backward: the
+    parameters' gradients are views of the buckets (nothing is packed or unpacked),
+    a hook on every parameter counts its bucket down, and when the last gradient of
+    a bucket has arrived the bucket's ``all_reduce`` is launched on a side stream
+    while autograd carries on with the earlier layers.  The main stream joins the
+    side stream before the clip.  Buckets follow the order in which gradients
+    appear (last layer first).  Which parameters take part is learnt from the first
+    step, which averages without overlap -- layer 0's ``vr_lambda`` never gets a
+    gradient (it has no ``v0``), which is why this is not a wrapper that expects
+    every parameter to take part.  With one rank no collective is issued.
 
     ``capture(idx, targets)`` records the whole step -- forward, backward, the NCCL
     all-reduces, the clip and the optimiser -- into one CUDA graph; ``step`` then copies
@@ -280,10 +302,11 @@ class DataParallelStep:
     """
 
     def __init__(self, model: GPT, lr: float = 6e-4, weight_decay: float = 0.1, grad_clip: float = 1.0,
-                 dtype=torch.bfloat16, bucket_mb: int = 128, group=None):
+                 dtype=torch.bfloat16, bucket_mb: int = 32, group=None, overlap: bool = True):
         self.model, self.grad_clip, self.dtype, self.group = model, grad_clip, dtype, group
         self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         self.bucket_elems = bucket_mb * (1 << 20) // 4
+        self.overlap = overlap
         params = list(model.parameters())
         decay = [p for p in params if p.dim() >= 2]
         rest = [p for p in params if p.dim() < 2]
@@ -293,32 +316,86 @@ class DataParallelStep:
         self.opt = torch.optim.AdamW(
             [dict(params=decay, weight_decay=weight_decay), dict(params=rest, weight_decay=0.0)],
             lr=self.lr, betas=(0.9, 0.95), fused=on_gpu, capturable=on_gpu)
-        self._flat = None
         self.collectives = 0
         self._graph = None
+        self._buckets = None                 # built after the first backward
+        self._bucket_of = {}
+        self._hooks = []
+        self._comm = torch.cuda.Stream(device=params[0].device) if on_gpu and self.world > 1 else None
+
+    # ---- gradient averaging -------------------------------------------------------------------
+    def _build_buckets(self) -> None:
+        """After the first backward: the parameters that received a gradient, in the order their gradients
+        appear (the reverse of registration), packed into flat buffers that own the gradients from now on."""
+        got = [p for p in reversed(list(self.model.parameters())) if p.grad is not None]
+        first = {id(p): p.grad for p in got}
+        self._buckets, run, used = [], [], 0
+        for p in got:
+            if run and used + p.numel() > self.bucket_elems:
+                self._buckets.append(run)
+                run, used = [], 0
+            run.append(p)
+            used += p.numel()
+        if run:
+            self._buckets.append(run)
+        self._buckets = [_Bucket(ps, got[0].device) for ps in self._buckets]
+        for b in self._buckets:
+            for p in b.params:
+                p.grad.copy_(first[id(p)])                        # this step's gradients move in
+                self._bucket_of[id(p)] = b
+                self._hooks.append(p.register_post_accumulate_grad_hook(self._grad_arrived))
+
+    def _grad_arrived(self, p) -> None:
+        b = self._bucket_of[id(p)]
+        b.pending -= 1
+        if b.pending == 0 and self.overlap:
+            self._launch(b)
+
+    def _launch(self, b: _Bucket) -> None:
+        b.launched = True
+        self.collectives += 1
+        if self._comm is None:                                    # CPU ranks: nothing to overlap with
+            dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group)
+            b.flat.mul_(1.0 / self.world)
+            return
+        self._comm.wait_stream(torch.cuda.current_stream())       # the bucket's last gradient has been written
+        with torch.cuda.stream(self._comm):
+            dist.all_reduce(b.flat, op=dist.ReduceOp.SUM, group=self.group)
+            b.flat.mul_(1.0 / self.world)
 
     def average_gradients(self) -> None:
+        """Called after the backward: launches what the hooks have not (every bucket on the first step or
+        without overlap; a bucket one of whose parameters got no gradient this time) and joins the side stream."""
         if self.world == 1:
             return
-        grads = [p.grad for p in self.model.parameters() if p.grad is not None]
-        if self._flat is None:
-            n = min(self.bucket_elems, sum(g.numel() for g in grads))
-            self._flat = torch.empty(max(n, max(g.numel() for g in grads)), dtype=torch.float32,
-                                     device=grads[0].device)
-        i = 0
-        while i < len(grads):
-            j, used = i, 0
-            while j < len(grads) and (used == 0 or used + grads[j].numel() <= self._flat.numel()):
-                used += grads[j].numel()
-                j += 1
-            flat = self._flat[:used]
-            views = torch.split(flat, [g.numel() for g in grads[i:j]])
-            torch._foreach_copy_(list(views), [g.reshape(-1) for g in grads[i:j]])
-            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
-            flat.mul_(1.0 / self.world)
-            torch._foreach_copy_([g.view(-1) for g in grads[i:j]], list(views))
-            self.collectives += 1
-            i = j
+        if self._buckets is None:
+            self._build_buckets()
+        for b in self._buckets:
+            if not b.launched:
+                self._launch(b)
+        if self._comm is not None:
+            torch.cuda.current_stream().wait_stream(self._comm)
+
+    def close(self) -> None:
+        """Detach from the model: remove the gradient hooks (they hold this object, and through it a captured
+        graph with NCCL kernels, alive past ``del``) and drop the graph and the buckets.  Call it before the
+        process group is destroyed."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks, self._bucket_of, self._graph = [], {}, None
+        if self._buckets is not None:
+            for b in self._buckets:
+                for p in b.params:
+                    p.grad = None
+            self._buckets = None
+
+    def _zero_grad(self) -> None:
+        if self._buckets is None:
+            self.opt.zero_grad(set_to_none=True)
+            return
+        for b in self._buckets:                                   # the gradients stay views of the buckets
+            b.flat.zero_()
+            b.pending, b.launched = len(b.params), False
 
     def capture(self, idx, targets) -> None:
         """Record one whole step into a CUDA graph (GPU only); later ``step`` calls replay it."""
@@ -359,7 +436,7 @@ class DataParallelStep:
         self.average_gradients()
         torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.grad_clip)
         self.opt.step()
-        self.opt.zero_grad(set_to_none=True)
+        self._zero_grad()
         return loss.detach()
 
 
