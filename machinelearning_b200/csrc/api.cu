@@ -256,6 +256,14 @@ int ensure_dynamic_smem(const void* kernel, int bytes) {
   return NLFA_OK;
 }
 
+bool overlap_launches() {
+  static const bool on = [] {
+    const char* v = std::getenv("NLFA_PDL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
+
 int sm_count() {
   const int dev = current_device();
   if (dev < 0) return 1;

@@ -59,6 +59,9 @@ struct BwdParams {
   float* dq_acc;         // per (b, h, query tile): 128 x 64 fp32 partial sums, rows permuted (see drain)
   unsigned* dq_turn;     // per (b, h, query tile): how many key blocks have added their share
   int sched_group;       // (batch, KV head) pairs whose units are handed out together
+  int dep_wait_first;    // 1: wait for the stream's previous kernel before the first global read; 0: the
+                         // previous kernel is this call's dK/dV pass, whose results this pass does not
+                         // read -- it is waited for on the way out instead
 };
 
 template <int D, int STAGES, int XBUF, int YR, bool FUSED = false>
@@ -256,6 +259,10 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const bool dead = *abort_flag != 0;
+  // Everything above touched only this CTA's own state and may have run while the stream's
+  // previous kernel was finishing; from here on its results are read.
+  if (p.dep_wait_first) grid_dep_wait();
+  grid_dep_release();
 
   // Sixteen warps: 0-7 compute, 8 scheduler + TMA producer, 9 MMA issuer, 10-11 idle, 12-15
   // epilogue (one warp per TMEM lane quarter).  The launch gives every thread 128 registers;
@@ -1014,6 +1021,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
   }
   // scheduler bookkeeping: the last CTA of the launch to get here re-arms the counters
   if (threadIdx.x == 0) {
+    // a pass that started beside its predecessor does not finish before it: what follows this
+    // grid in the stream may rely on both
+    if (!p.dep_wait_first) grid_dep_wait();
     __threadfence();
     const unsigned done = atomicAdd(&p.sched[1], 1u);
     if (done == gridDim.x - 1) {
@@ -1027,7 +1037,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
 template <typename T, int D, int MODE, int STAGES, int XBUF, int YR>
 int launch_mode(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                 const float* lse, const float* delta, void* out0, void* out1, unsigned* status,
-                cudaStream_t stream, void* dq = nullptr, const FusedScratch* fused = nullptr) {
+                cudaStream_t stream, void* dq = nullptr, const FusedScratch* fused = nullptr,
+                bool beside_previous = false) {
   // stationary tensors in boxes of 128 rows, streamed tensors in boxes of YR rows; output tiles
   // leave through TMA stores: dQ is [B,T,H,D], dK and dV are [B,T,Hkv,D]
   const void* x0 = MODE == MODE_DQ ? q : k;
@@ -1081,8 +1092,14 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   if (sst != NLFA_OK) return sst;
   const int grid = bp.total_units < sm_count() ? bp.total_units : sm_count();
   bp.sched_group = MODE == MODE_DQ ? bp.BH : grid;      // (the dQ pass gains nothing from groups)
-  kern<<<grid, 512, L::kDynamic, stream>>>(mx0, mx1, my0, my1, mo0, mo1, bp);
-  if (cudaGetLastError() != cudaSuccess) return NLFA_ERR_CUDA;
+  // (the fused pass follows a memset, not a kernel: launched the plain way)
+  const bool overlap = MODE != MODE_FUSED && overlap_launches();
+  bp.dep_wait_first = (overlap && beside_previous) ? 0 : 1;
+  if (launch_kernel(kern, dim3(grid), dim3(512), L::kDynamic, stream, overlap, mx0, mx1, my0, my1, mo0, mo1, bp) !=
+      cudaSuccess) {
+    (void)cudaGetLastError();
+    return NLFA_ERR_CUDA;
+  }
   if (MODE == MODE_FUSED) {
     // the fp32 sums, complete now, become dQ: scaled, converted, rows put back in order
     const long long pieces = static_cast<long long>(p.B) * p.H * bp.n_tiles * kTile * 16;
@@ -1107,8 +1124,11 @@ int launch_both(const Problem& p, const void* dout, const void* q, const void* k
   if (passes & NLFA_PASS_DKV)
     st = launch_mode<T, D, MODE_DKV, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dk, dv, status, stream);
   if (st != NLFA_OK) return st;
+  // Launched right behind this call's dK/dV pass, the dQ pass reads none of its results and may
+  // take the SMs it leaves one by one.
   if (passes & NLFA_PASS_DQ)
-    st = launch_mode<T, D, MODE_DQ, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dq, nullptr, status, stream);
+    st = launch_mode<T, D, MODE_DQ, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dq, nullptr, status, stream,
+                                                     nullptr, nullptr, (passes & NLFA_PASS_DKV) != 0);
   return st;
 }
 

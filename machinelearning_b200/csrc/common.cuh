@@ -184,4 +184,28 @@ int ensure_dynamic_smem(const void* kernel, int bytes);
 
 int sm_count();
 
+// True unless NLFA_PDL=0: the tensor-core kernels are launched with programmatic stream
+// serialization, so a kernel's set-up (barriers, TMEM, descriptors) overlaps its predecessor's
+// last CTAs, and the dQ pass fills the SMs the dK/dV pass leaves.
+bool overlap_launches();
+
+// One launch through cudaLaunchKernelEx, with the programmatic-serialization attribute when
+// `overlap` is set.  The kernel must then call grid_dep_wait() before it reads anything an earlier
+// kernel of the stream wrote.
+template <typename... Params, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          bool overlap, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1u : 0u;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 }  // namespace nlfa

@@ -180,6 +180,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const bool dead = *abort_flag != 0;
+  // Everything above touched only this CTA's own state and may have run while the stream's
+  // previous kernel was finishing; from here on its results are read.
+  grid_dep_wait();
+  grid_dep_release();
 
   // Every role reads the index of its uc-th unit from the ring the producer fills;
   // a negative index means there is no more work.
@@ -771,8 +775,12 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
   const int sst = sched_counters(stream, &fp.sched);
   if (sst != NLFA_OK) return sst;
   const int grid = fp.total_units < sm_count() ? fp.total_units : sm_count();
-  kern<<<grid, NT * 128 + 128, L::kDynamic, stream>>>(mq, mk, mv, mo, fp);
-  return cudaGetLastError() == cudaSuccess ? NLFA_OK : NLFA_ERR_CUDA;
+  if (launch_kernel(kern, dim3(grid), dim3(NT * 128 + 128), L::kDynamic, stream, overlap_launches(), mq, mk, mv, mo,
+                    fp) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return NLFA_ERR_CUDA;
+  }
+  return NLFA_OK;
 }
 
 }  // namespace

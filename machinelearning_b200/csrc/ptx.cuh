@@ -240,6 +240,16 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
                : "memory");
 }
 
+// Programmatic dependent launch.  A kernel launched with the stream-serialization attribute may
+// start while its predecessor in the stream is still running; grid_dep_wait() returns once that
+// predecessor has completed and its writes are visible (at once when there is no such edge).
+// grid_dep_release() lets the next kernel of the stream, if it asked for it, be scheduled as
+// soon as every CTA of this grid has called it or left.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_release() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

@@ -12,6 +12,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace nlfa {
 namespace {
@@ -132,6 +133,8 @@ delta_vec_kernel(Problem p, const T* __restrict__ dout, const T* __restrict__ o,
                  float* __restrict__ delta) {
   constexpr int kLanesPerRow = D / 8;                      // 8 (D = 64) or 16 (D = 128)
   constexpr int kRowsPerWarp = 32 / kLanesPerRow;
+  grid_dep_wait();                                         // O comes from the stream's previous kernel
+  grid_dep_release();
   const int lane = threadIdx.x & 31;
   const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long rows = static_cast<long long>(p.B) * p.T * p.H;     // rows index [B,T,H]
@@ -308,8 +311,11 @@ int delta_t(const Problem& p, const void* dout, const void* o, float* delta, cud
   if constexpr (sizeof(T) == 2 && (D == 64 || D == 128)) {
     constexpr int kRowsPerBlock = 8 * (32 / (D / 8));           // 8 warps per block
     const unsigned blocks = static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock);
-    delta_vec_kernel<T, D><<<blocks, 256, 0, s>>>(p, static_cast<const T*>(dout),
-                                                  static_cast<const T*>(o), delta);
+    if (launch_kernel(delta_vec_kernel<T, D>, dim3(blocks), dim3(256), 0, s, overlap_launches(), p,
+                      static_cast<const T*>(dout), static_cast<const T*>(o), delta) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return NLFA_ERR_CUDA;
+    }
   } else {
     delta_kernel<T, D><<<blocks_for(rows), kWarpsPerBlock * 32, 0, s>>>(
         p, static_cast<const T*>(dout), static_cast<const T*>(o), delta);

@@ -226,6 +226,28 @@ def check_window(window: int, sinks: int, block: int = 0) -> None:
                          f"got sinks={sinks} window={window}")
 
 
+class _on_device:
+    """``torch.cuda.device(index)`` when ``index`` is not the current device, else nothing: the
+    context manager costs several microseconds per call, the comparison a fraction of one."""
+    __slots__ = ("guard",)
+
+    def __init__(self, index: int):
+        self.guard = None if index == torch.cuda.current_device() else torch.cuda.device(index)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+
+
+def _stream_of(index: int) -> int:
+    """The raw handle of torch's current stream on device ``index``."""
+    return torch._C._cuda_getCurrentRawStream(index)
+
+
 def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0, block: int = 0):
     """(O, LSE) through the C ABI.  Contiguous same-dtype CUDA tensors only
     (reference native entry: ``flash_attn_cuda.cu:1655-1704``).  ``block > 0``: the block-causal mask
@@ -235,17 +257,19 @@ def fwd(q, k, v, scale: float, use_mma: bool, window: int = 0, sinks: int = 0, b
         raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
     B, T, H, D = q.shape
     Hkv = k.shape[2]
-    if q.device.index not in _status_words:
-        _watch_device(lib, q.device.index)
+    index = q.device.index
+    if index not in _status_words:
+        _watch_device(lib, index)
     o = torch.empty_like(q)
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
-    with torch.cuda.device(q.device):
+    with _on_device(index):
         st = lib.nlfa_fwd_masked(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
                                  B, T, H, Hkv, D, float(scale), int(window), int(sinks), int(block),
                                  _DTYPE_CODE[q.dtype],
                                  _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT,
-                                 torch.cuda.current_stream().cuda_stream)
-    _lib.check("nlfa_fwd", st)
+                                 _stream_of(index))
+    if st:
+        _lib.check("nlfa_fwd", st)
     return o, lse
 
 
@@ -262,8 +286,9 @@ def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sin
         raise RuntimeError(f"flash_cuda is unavailable ({unavailable_reason()})")
     B, T, H, D = q.shape
     Hkv = k.shape[2]
-    if q.device.index not in _status_words:
-        _watch_device(lib, q.device.index)
+    index = q.device.index
+    if index not in _status_words:
+        _watch_device(lib, index)
     can_fuse = bool(use_mma) and D <= 64
     if fused is None:
         fused = can_fuse and FUSED_BACKWARD
@@ -273,14 +298,15 @@ def bwd(dout, q, k, v, o, lse, scale: float, use_mma: bool, window: int = 0, sin
     nbytes = lib.nlfa_bwd_fused_scratch_bytes(B, T, H, D) if fused else lib.nlfa_bwd_scratch_bytes(B, T, H)
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
     passes = (_lib.PASS_DELTA | _lib.PASS_FUSED) if fused else _lib.PASS_ALL
-    with torch.cuda.device(q.device):
+    with _on_device(index):
         st = lib.nlfa_bwd_masked(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
                                  lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                  scratch.data_ptr(), scratch.numel(), B, T, H, Hkv, D, float(scale),
                                  int(window), int(sinks), int(block), _DTYPE_CODE[q.dtype],
                                  _lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT, passes,
-                                 torch.cuda.current_stream().cuda_stream)
-    _lib.check("nlfa_bwd_masked", st)
+                                 _stream_of(index))
+    if st:
+        _lib.check("nlfa_bwd_masked", st)
     return dq, dk, dv
 
 

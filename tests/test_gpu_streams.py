@@ -53,3 +53,41 @@ def test_graph_replay_and_eager_launches_do_not_share_work_counters():
             bad += sum(not torch.equal(g, w) for g, w in zip(got_b, want_b))
     torch.cuda.synchronize()
     assert bad == 0
+
+
+def test_overlapped_launches_give_the_bits_of_serialised_ones():
+    """The tensor-core kernels are launched with programmatic stream serialization (a kernel's set-up
+    runs beside its predecessor's last CTAs, the dQ pass fills the SMs the dK/dV pass leaves);
+    ``NLFA_PDL=0`` launches them the plain way.  The two must agree bit for bit, back to back, with a
+    window and without."""
+    import os
+    import subprocess
+    import sys
+    import pathlib
+    root = pathlib.Path(__file__).resolve().parent.parent
+    script = f"""
+import sys, math, hashlib
+sys.path.insert(0, {str(root)!r})
+import torch
+from machinelearning_b200 import flash_cuda as fc
+assert fc.mma_available(), fc.mma_unavailable_reason()
+h = hashlib.sha256()
+for (B, T, H, Hkv, D, w, s) in ((3, 700, 4, 2, 64, 0, 0), (2, 1024, 4, 4, 128, 0, 0), (2, 900, 4, 2, 64, 128, 4)):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    mk = lambda heads: torch.randn(B, T, heads, D, device="cuda", generator=g).bfloat16()
+    q, k, v, d = mk(H), mk(Hkv), mk(Hkv), mk(H)
+    for _ in range(20):                        # back to back: every launch has a predecessor still running
+        o, lse = fc.fwd(q, k, v, 1 / math.sqrt(D), True, w, s)
+        grads = fc.bwd(d, q, k, v, o, lse, 1 / math.sqrt(D), True, w, s)
+    torch.cuda.synchronize()
+    for t in (o, lse, *grads):
+        h.update(t.cpu().contiguous().view(torch.uint8).numpy().tobytes())
+print("digest", h.hexdigest())
+"""
+    digests = []
+    for flag in ("1", "0"):
+        env = dict(os.environ, NLFA_PDL=flag)
+        r = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300, env=env)
+        assert r.returncode == 0, r.stderr[-2000:]
+        digests.append(r.stdout.strip().splitlines()[-1])
+    assert digests[0] == digests[1]
