@@ -126,6 +126,15 @@ int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* 
                     size_t scratch_bytes, int B, int T, int H, int Hkv, int D, float scale,
                     int window, int sinks, int dtype, int path, int passes, void* stream);
 
+/* How many kernels nlfa_bwd_passes launches for this problem and mask on the
+ * current device (0 for inputs it would refuse).  On the tensor-core path at
+ * D = 64 a large problem (at least sixteen 128-row query tiles per SM) takes two:
+ * the dQ pass forms Delta itself -- the row sums of dO * O, added in the order of
+ * the Delta kernel, so the gradients are bit-identical either way -- and runs
+ * before the dK/dV pass; smaller problems and other head dims take the three
+ * kernels named above.  For launch accounting (bench.py's `gpu_launches`). */
+int nlfa_bwd_kernel_count(int B, int T, int H, int D, int dtype, int path, int passes);
+
 /* nlfa_bwd_passes with the mask given in full (`block` as in nlfa_fwd_masked). */
 int nlfa_bwd_masked(const void* dout, const void* q, const void* k, const void* v, const void* o,
                     const float* lse, void* dq, void* dk, void* dv, void* scratch,

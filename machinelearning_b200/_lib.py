@@ -37,6 +37,7 @@ SIGNATURES = {
     "nlfa_bwd_passes": (_c_int, [_c_void_p] * 10 + [_c_size_t] + [_c_int] * 5 + [_c_float]
                         + [_c_int] * 5 + [_c_void_p]),
     "nlfa_bwd_fused_scratch_bytes": (_c_size_t, [_c_int, _c_int, _c_int, _c_int]),
+    "nlfa_bwd_kernel_count": (_c_int, [_c_int] * 7),
     "nlfa_bwd_fused": (_c_int, [_c_void_p] * 10 + [_c_size_t] + [_c_int] * 5 + [_c_float]
                        + [_c_int] * 4 + [_c_void_p]),
     "nlfa_static_scratch_max_rows": (_c_size_t, []),

@@ -256,12 +256,12 @@ int ensure_dynamic_smem(const void* kernel, int bytes) {
   return NLFA_OK;
 }
 
-bool overlap_launches() {
-  static const bool on = [] {
+bool overlap_launches(int kernel) {
+  static const int mask = [] {
     const char* v = std::getenv("NLFA_PDL");
-    return !(v != nullptr && v[0] == '0');
+    return v != nullptr ? std::atoi(v) : kOverlapDefault;
   }();
-  return on;
+  return (mask & kernel) != 0;
 }
 
 int sm_count() {
@@ -397,6 +397,23 @@ int nlfa_bwd_fused(const void* dout, const void* q, const void* k, const void* v
   return nlfa_bwd_passes(dout, q, k, v, o, lse, dq, dk, dv, scratch, scratch_bytes, B, T, H, Hkv,
                          D, scale, window, sinks, dtype, path,
                          fused ? (NLFA_PASS_DELTA | NLFA_PASS_FUSED) : NLFA_PASS_ALL, stream);
+}
+
+int nlfa_bwd_kernel_count(int B, int T, int H, int D, int dtype, int path, int passes) {
+  if (passes <= 0 || passes > (NLFA_PASS_ALL | NLFA_PASS_FUSED) || B <= 0 || T <= 0 || H <= 0) return 0;
+  const int resolved = nlfa_resolve_path(dtype, D, path);
+  if (resolved < 0) return 0;
+  const int delta = (passes & NLFA_PASS_DELTA) ? 1 : 0;
+  if (passes & NLFA_PASS_FUSED) {
+    if ((passes & (NLFA_PASS_DKV | NLFA_PASS_DQ)) || resolved != NLFA_PATH_TENSOR || D > 64) return 0;
+    return delta + 2;                                          // the pass and the convert kernel
+  }
+  const int two = ((passes & NLFA_PASS_DKV) ? 1 : 0) + ((passes & NLFA_PASS_DQ) ? 1 : 0);
+  if (resolved == NLFA_PATH_TENSOR) {
+    Problem p{B, T, H, H, D, 0, 0, 1.f, dtype, 0};
+    if (bwd_delta_in_dq(p, passes)) return two;
+  }
+  return delta + two;
 }
 
 int nlfa_bwd_passes(const void* dout, const void* q, const void* k, const void* v, const void* o,

@@ -30,6 +30,8 @@
 // stages of 128-row tiles (one load in flight) and TMEM no separate P / dS columns.
 #include <type_traits>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -59,25 +61,30 @@ struct BwdParams {
   float* dq_acc;         // per (b, h, query tile): 128 x 64 fp32 partial sums, rows permuted (see drain)
   unsigned* dq_turn;     // per (b, h, query tile): how many key blocks have added their share
   int sched_group;       // (batch, KV head) pairs whose units are handed out together
+  float* delta_out;      // dQ pass, when it also forms Delta (see kDeltaIn): where the dK/dV pass will read it
+  int delta_in_pass;     // 1: this dQ launch computes Delta = rowsum(dO * O) itself, tile by tile
   int dep_wait_first;    // 1: wait for the stream's previous kernel before the first global read; 0: the
                          // previous kernel is this call's dK/dV pass, whose results this pass does not
                          // read -- it is waited for on the way out instead
 };
 
-template <int D, int STAGES, int XBUF, int YR, bool FUSED = false>
+template <int D, int STAGES, int XBUF, int YR, bool FUSED = false, bool DELTA = false>
 struct BwdSmem {
   static constexpr int kTileBytes = kTile * D * 2;              // stationary tile: 128 rows
   static constexpr int kYTileBytes = YR * D * 2;                // streamed tile: YR rows
   static constexpr int kX = 0;                                  // [XBUF] x (X0, X1)
   static constexpr int kY = kX + XBUF * 2 * kTileBytes;         // per stage: Y0, Y1
   static constexpr int kDs = kY + STAGES * 2 * kYTileBytes;     // fused pass: dS^T [128 keys][128 queries] 16-bit
-  static constexpr int kVec = kDs + (FUSED ? kTile * YR * 2 : 0);   // per stage: -lse2[YR], -delta[YR]
-  static constexpr int kBar = kVec + STAGES * 1024;
+  static constexpr int kO = kDs + (FUSED ? kTile * YR * 2 : 0);     // dQ pass forming Delta: the next unit's O tile
+  static constexpr int kVec = kO + (DELTA ? kTileBytes : 0);        // per stage: -lse2[YR], -delta[YR]
+  static constexpr int kDeltaS = kVec + STAGES * 1024;              // dQ pass forming Delta: [XBUF][128] fp32
+  static constexpr int kBar = kDeltaS + (DELTA ? XBUF * 512 : 0);
   // barriers: x_full[XBUF], x_empty[XBUF], t_full, t_consumed, pd_full, out_ready,
   //           sched_full[kRing], y_full[S], y_empty[S]
   static constexpr int kRing = 8;
-  //           unit_done, out_drained, dq_ready, dq_drained, group, issued[4]
-  static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES + 9;
+  //           unit_done, out_drained, dq_ready, dq_drained, group, issued[4],
+  //           o_full, o_empty, delta_full[XBUF]
+  static constexpr int kNumBars = 2 * XBUF + 4 + kRing + 2 * STAGES + 9 + 2 + XBUF;
   static constexpr int kSched = (kBar + 8 * kNumBars + 15) / 16 * 16;   // ring of unit descriptors (8 ints each)
   static constexpr int kTmemSlot = kSched + 32 * kRing;
   static constexpr int kAbort = kTmemSlot + 4;
@@ -184,7 +191,15 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
               const __grid_constant__ CUtensorMap tm_y0, const __grid_constant__ CUtensorMap tm_y1,
               const __grid_constant__ CUtensorMap tm_out0,
               const __grid_constant__ CUtensorMap tm_out1, const BwdParams p) {
-  using L = BwdSmem<D, STAGES, XBUF, YR, MODE == MODE_FUSED>;
+  // The dQ pass at D = 64 (two stationary buffers: the next unit's tiles arrive during this one) can
+  // form Delta = rowsum(dO * O) itself: the producer also fetches the next unit's O tile, the
+  // epilogue warps -- idle except at unit boundaries -- multiply it with the dO tile that is
+  // already there, hand the row sums to the compute warps through shared memory and write them
+  // out for the dK/dV pass, which then runs second.  That removes the separate Delta kernel
+  // (a full pass over dO and O) from the backward.  Same arithmetic, same order of additions as
+  // delta_vec_kernel, so the results are bit-identical to it.
+  constexpr bool kDeltaIn = MODE == MODE_DQ && XBUF == 2 && D == 64;
+  using L = BwdSmem<D, STAGES, XBUF, YR, MODE == MODE_FUSED, kDeltaIn>;
   static_assert(YR == 64 || YR == 128, "streamed tiles are 64 or 128 rows");
   static_assert(MODE != MODE_FUSED || (D == 64 && YR == 128), "the fused pass exists for 64-wide tiles");
   constexpr int kBoxes = D / 64;
@@ -219,7 +234,8 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
                 Y_FULL = SCHED_FULL + kRing, Y_EMPTY = Y_FULL + STAGES,
                 UNIT_DONE = Y_EMPTY + STAGES, OUT_DRAINED = UNIT_DONE + 1,
                 DQ_READY = UNIT_DONE + 2, DQ_DRAINED = UNIT_DONE + 3, GROUP = UNIT_DONE + 4,
-                ISSUED = UNIT_DONE + 5;          // [4]: iteration g uses ISSUED + (g & 3)
+                ISSUED = UNIT_DONE + 5,          // [4]: iteration g uses ISSUED + (g & 3)
+                O_FULL = ISSUED + 4, O_EMPTY = O_FULL + 1, DELTA_FULL = O_FULL + 2;   // DELTA_FULL[XBUF]
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::kAbort);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::kTmemSlot);
   volatile int* sched_ring = reinterpret_cast<volatile int*>(gen + L::kSched);
@@ -241,6 +257,9 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
     mbar_init(bar(DQ_DRAINED), 128);
     mbar_init(bar(GROUP), 128);
     for (int i = 0; i < 4; ++i) mbar_init(bar(ISSUED + i), 128);
+    mbar_init(bar(O_FULL), 1);
+    mbar_init(bar(O_EMPTY), 4);              // one arrival per epilogue warp
+    for (int i = 0; i < XBUF; ++i) mbar_init(bar(DELTA_FULL + i), 4);
     reinterpret_cast<volatile int*>(gen + L::kTurnOk)[0] = 0;      // iterations whose turn has come
     reinterpret_cast<volatile int*>(gen + L::kTurnOk)[1] = 0;      // iterations whose share has been released
     for (int i = 0; i < kRing; ++i) mbar_init(bar(SCHED_FULL + i), 1);
@@ -392,11 +411,72 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
       ++group_phase;
       ok = __all_sync(0xffffffffu, done && *abort_flag == 0);
     };
+    // dQ pass forming Delta: row sums of dO * O for unit `duc` (descriptor `dw`), eight lanes per
+    // row and eight elements per lane, summed exactly as delta_vec_kernel does; handed to the
+    // compute warps through shared memory and written out for the dK/dV pass.
+    auto form_delta = [&](int duc, const BwdUnit<MODE>& dw) {
+      const int xb = duc % XBUF;
+      // (sleeping waits: these warps share their schedulers with the compute warps)
+      ok = mbar_wait_idle(bar(X_FULL + xb), (duc / XBUF) & 1, wctx, 47);   // the dO tile
+      if (ok) ok = mbar_wait_idle(bar(O_FULL), duc & 1, wctx, 48);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return;
+      const uint32_t do_tile = base + L::kX + xb * 2 * L::kTileBytes + L::kTileBytes;
+      const uint32_t o_tile = base + L::kO;
+      float* delta_s = reinterpret_cast<float*>(gen + L::kDeltaS) + xb * kTile;
+      const int chunk = lane & 7;
+#pragma unroll 2
+      for (int step = 0; step < 8; ++step) {
+        const int r = 32 * (warp & 3) + 4 * step + (lane >> 3);
+        const uint32_t off = static_cast<uint32_t>(r) * 128u +
+                             ((static_cast<uint32_t>(chunk) ^ static_cast<uint32_t>(r & 7)) << 4);
+        uint32_t a[4], b[4];
+        ld_shared_v4(do_tile + off, a[0], a[1], a[2], a[3]);
+        ld_shared_v4(o_tile + off, b[0], b[1], b[2], b[3]);
+        float part = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          T a2[2], b2[2];
+          *reinterpret_cast<uint32_t*>(a2) = a[i];
+          *reinterpret_cast<uint32_t*>(b2) = b[i];
+          part = fmaf(static_cast<float>(a2[0]), static_cast<float>(b2[0]), part);
+          part = fmaf(static_cast<float>(a2[1]), static_cast<float>(b2[1]), part);
+        }
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        const int pos = dw.tile * kTile + r;
+        if (chunk == 0) {
+          delta_s[r] = part;
+          if (pos < p.T) p.delta_out[(static_cast<long long>(dw.b) * p.H + dw.h) * p.T + pos] = part;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(O_EMPTY));                 // the O buffer may be reloaded
+        mbar_arrive(bar(DELTA_FULL + xb));         // the compute warps may read this unit's row sums
+      }
+    };
     for (int uc = 0; ok; ++uc) {
       BwdUnit<MODE> w;
       const int u = next_unit(uc, ok, w);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok || u < 0) break;
+      if constexpr (kDeltaIn) {
+        if (p.delta_in_pass) {
+          if (uc == 0) form_delta(0, w);
+          if (!ok) break;
+          // The next unit's Delta, while this unit computes (its descriptor is published, and its
+          // tiles are requested, a few iterations into this unit).
+          BwdUnit<MODE> wn;
+          ok = mbar_wait_idle(bar(SCHED_FULL + ((uc + 1) % kRing)), ((uc + 1) / kRing) & 1, wctx, 40);
+          const int un = ok ? next_unit(uc + 1, ok, wn) : -1;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (un >= 0) form_delta(uc + 1, wn);
+          if (!ok) break;
+        }
+      }
       if constexpr (kFused) {
         // dQ of query tile i is the sum over the key blocks j that see it of dS_ij K_j.  Each
         // iteration leaves one such share (128 x 64 fp32) in TMEM.  These warps pull it into
@@ -542,6 +622,16 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
               tma_load_4d(xa + x * kBoxBytes, mx0, bar(X_FULL + xb), 64 * x, xh, w.tile * kTile, w.b);
               tma_load_4d(xa + L::kTileBytes + x * kBoxBytes, mx1, bar(X_FULL + xb), 64 * x, xh,
                           w.tile * kTile, w.b);
+            }
+          }
+          if constexpr (kDeltaIn) {
+            // the unit's O tile, for its Delta; one buffer, free once the previous unit's Delta is done
+            if (ok && p.delta_in_pass) {
+              if (uc > 0) ok = mbar_wait(bar(O_EMPTY), (uc - 1) & 1, wctx, 46);
+              if (ok) {
+                mbar_arrive_expect_tx(bar(O_FULL), L::kTileBytes);
+                tma_load_4d(base + L::kO, &tm_out1, bar(O_FULL), 0, w.h, w.tile * kTile, w.b);
+              }
             }
           }
         }
@@ -813,15 +903,25 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
                                                : 0x7fffffffu;
       }
       uint64_t negl2_row = pack_f2(-INFINITY, -INFINITY), negd_row = 0ull;
+      const bool delta_here = kDeltaIn && p.delta_in_pass != 0;      // Delta comes from the epilogue warps
       if (MODE == MODE_DQ && pos < p.T) {
         if (uc > 0) {                       // fetched during the previous unit's last iteration
           negl2_row = pack_f2(-pre_lse * kLog2e, -pre_lse * kLog2e);
           negd_row = pack_f2(-pre_delta, -pre_delta);
         } else {
           const long long idx = (static_cast<long long>(w.b) * p.H + w.h) * p.T + pos;
-          const float l2 = -p.lse[idx] * kLog2e, dl = -p.delta[idx];
+          const float l2 = -p.lse[idx] * kLog2e, dl = delta_here ? 0.f : -p.delta[idx];
           negl2_row = pack_f2(l2, l2);
           negd_row = pack_f2(dl, dl);
+        }
+      }
+      if constexpr (kDeltaIn) {
+        if (delta_here) {
+          ok = mbar_wait(bar(DELTA_FULL + uc % XBUF), (uc / XBUF) & 1, wctx, 49);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const float dl = -reinterpret_cast<const volatile float*>(gen + L::kDeltaS)[(uc % XBUF) * kTile + row];
+          negd_row = pos < p.T ? pack_f2(dl, dl) : 0ull;
         }
       }
 
@@ -841,7 +941,7 @@ bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__
           if (un >= 0 && pos_n < p.T) {
             const long long nidx = (static_cast<long long>(wn.b) * p.H + wn.h) * p.T + pos_n;
             pre_lse = p.lse[nidx];
-            pre_delta = p.delta[nidx];
+            if (!delta_here) pre_delta = p.delta[nidx];
           }
         }
         ok = mbar_wait(bar(T_FULL), g & 1, wctx, 35);
@@ -1038,7 +1138,8 @@ template <typename T, int D, int MODE, int STAGES, int XBUF, int YR>
 int launch_mode(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                 const float* lse, const float* delta, void* out0, void* out1, unsigned* status,
                 cudaStream_t stream, void* dq = nullptr, const FusedScratch* fused = nullptr,
-                bool beside_previous = false) {
+                bool beside_previous = false, const void* o_for_delta = nullptr, float* delta_out = nullptr,
+                bool plain_launch = false) {
   // stationary tensors in boxes of 128 rows, streamed tensors in boxes of YR rows; output tiles
   // leave through TMA stores: dQ is [B,T,H,D], dK and dV are [B,T,Hkv,D]
   const void* x0 = MODE == MODE_DQ ? q : k;
@@ -1053,10 +1154,14 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   if (mst == NLFA_OK) mst = make_tile_map(&my0, y0, p.dtype, p.B, p.T, y_heads, p.D, YR);
   if (mst == NLFA_OK) mst = make_tile_map(&my1, y1, p.dtype, p.B, p.T, y_heads, p.D, YR);
   if (mst == NLFA_OK) mst = make_tile_map(&mo0, out0, p.dtype, p.B, p.T, x_heads, p.D, kTile);
+  // (the dQ pass has one output; its second map describes O when the pass also forms Delta)
   if (mst == NLFA_OK)
-    mst = make_tile_map(&mo1, MODE == MODE_DQ ? out0 : out1, p.dtype, p.B, p.T, x_heads, p.D, kTile);
+    mst = make_tile_map(&mo1, MODE == MODE_DQ ? (o_for_delta ? o_for_delta : out0) : out1, p.dtype, p.B, p.T,
+                        x_heads, p.D, kTile);
   if (mst != NLFA_OK) return mst;
-  using L = BwdSmem<D, STAGES, XBUF, YR, MODE == MODE_FUSED>;
+  constexpr bool kDeltaIn = MODE == MODE_DQ && XBUF == 2 && D == 64;
+  if (o_for_delta != nullptr && !kDeltaIn) return NLFA_ERR_UNSUPPORTED_PATH;
+  using L = BwdSmem<D, STAGES, XBUF, YR, MODE == MODE_FUSED, kDeltaIn>;
   static_assert(L::kDynamic <= 232448, "over the shared memory a CTA can have");
   auto kern = bwd_tc_kernel<T, D, MODE, STAGES, XBUF, YR>;
   if (ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kDynamic) != NLFA_OK)
@@ -1079,6 +1184,8 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   bp.out0 = out0;
   bp.out1 = out1;
   bp.status = status;
+  bp.delta_in_pass = o_for_delta != nullptr ? 1 : 0;
+  bp.delta_out = delta_out;
   bp.dq_acc = fused ? fused->dq_acc : nullptr;
   bp.dq_turn = fused ? fused->dq_turn : nullptr;
   if (MODE == MODE_FUSED) {
@@ -1093,7 +1200,7 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   const int grid = bp.total_units < sm_count() ? bp.total_units : sm_count();
   bp.sched_group = MODE == MODE_DQ ? bp.BH : grid;      // (the dQ pass gains nothing from groups)
   // (the fused pass follows a memset, not a kernel: launched the plain way)
-  const bool overlap = MODE != MODE_FUSED && overlap_launches();
+  const bool overlap = MODE != MODE_FUSED && !plain_launch && overlap_launches(MODE == MODE_DQ ? kOverlapDq : kOverlapDkv);
   bp.dep_wait_first = (overlap && beside_previous) ? 0 : 1;
   if (launch_kernel(kern, dim3(grid), dim3(512), L::kDynamic, stream, overlap, mx0, mx1, my0, my1, mo0, mo1, bp) !=
       cudaSuccess) {
@@ -1110,9 +1217,27 @@ int launch_mode(const Problem& p, const void* dout, const void* q, const void* k
   return NLFA_OK;
 }
 
+// True when the backward does without the separate Delta kernel: Delta and the dQ pass both asked
+// for, real head dim 64 (two stationary buffers in the dQ pass; the sums then match
+// delta_vec_kernel's bit for bit) -- and a problem large enough for it to pay.  With fewer than
+// sixteen query tiles per SM the backward is faster the other way round (measured at B = 4, 8, 16
+// of H = 12, T = 1024: the dQ pass can then start beside the dK/dV pass, and a short Delta kernel
+// costs less than the later start of the first unit).  NLFA_DELTA_IN_DQ=0 / 1 forces either.
+inline bool delta_in_dq_pass(const Problem& p, int passes) {
+  static const int forced = [] {
+    const char* v = std::getenv("NLFA_DELTA_IN_DQ");
+    return v == nullptr ? -1 : (v[0] == '0' ? 0 : 1);
+  }();
+  const int both = NLFA_PASS_DELTA | NLFA_PASS_DQ;
+  if (p.D != 64 || (passes & NLFA_PASS_FUSED) != 0 || (passes & both) != both || forced == 0) return false;
+  if (forced == 1) return true;
+  const long long tiles = static_cast<long long>(p.B) * p.H * ((p.T + kTile - 1) / kTile);
+  return tiles >= 16ll * sm_count();
+}
+
 template <typename T, int D, int STAGES, int XBUF, int YR>
-int launch_both(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
-                const float* lse, const float* delta, void* dq, void* dk, void* dv, int passes,
+int launch_both(const Problem& p, const void* dout, const void* q, const void* k, const void* v, const void* o,
+                const float* lse, float* delta, void* dq, void* dk, void* dv, int passes,
                 unsigned* status, cudaStream_t stream, const FusedScratch* fused) {
   int st = NLFA_OK;
   if constexpr (D == 64 && YR == 128) {
@@ -1120,6 +1245,16 @@ int launch_both(const Problem& p, const void* dout, const void* q, const void* k
     if (passes & NLFA_PASS_FUSED)
       return launch_mode<T, D, MODE_FUSED, 3, XBUF, YR>(p, dout, q, k, v, lse, delta, dk, dv, status, stream,
                                                        dq, fused);
+    // The whole backward in two launches: the dQ pass forms Delta on its way and runs first, the
+    // dK/dV pass reads it.
+    if (delta_in_dq_pass(p, passes)) {
+      // (plain launches: between these two long kernels the overlapped set-up measured slower)
+      st = launch_mode<T, D, MODE_DQ, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dq, nullptr, status, stream,
+                                                       nullptr, nullptr, false, o, delta, true);
+      if (st != NLFA_OK || (passes & NLFA_PASS_DKV) == 0) return st;
+      return launch_mode<T, D, MODE_DKV, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dk, dv, status, stream,
+                                                        nullptr, nullptr, false, nullptr, nullptr, true);
+    }
   }
   if (passes & NLFA_PASS_DKV)
     st = launch_mode<T, D, MODE_DKV, STAGES, XBUF, YR>(p, dout, q, k, v, lse, delta, dk, dv, status, stream);
@@ -1134,6 +1269,8 @@ int launch_both(const Problem& p, const void* dout, const void* q, const void* k
 
 }  // namespace
 
+bool bwd_delta_in_dq(const Problem& p, int passes) { return delta_in_dq_pass(p, passes); }
+
 int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void* k, const void* v,
                   const void* o, const float* lse, void* dq, void* dk, void* dv, float* delta,
                   int passes, unsigned* status, cudaStream_t stream, const FusedScratch* fused) {
@@ -1144,19 +1281,19 @@ int launch_bwd_tc(const Problem& p, const void* dout, const void* q, const void*
   // TMA boxes are 64 wide, so loads fill columns 32-63 with zeros (which add nothing to any
   // product) and stores drop them.
   int st = NLFA_OK;
-  if (passes & NLFA_PASS_DELTA) st = launch_delta(p, dout, o, delta, stream);
+  if ((passes & NLFA_PASS_DELTA) && !delta_in_dq_pass(p, passes)) st = launch_delta(p, dout, o, delta, stream);
   if (st != NLFA_OK) return st;
   const bool bf16 = p.dtype == NLFA_DTYPE_BF16;
   if (p.D <= 64) {
     // 128-row streamed tiles, four stages, two stationary buffers
-    return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused)
-                : launch_both<__half, 64, 4, 2, 128>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused);
+    return bf16 ? launch_both<__nv_bfloat16, 64, 4, 2, 128>(p, dout, q, k, v, o, lse, delta, dq, dk, dv, passes, status, stream, fused)
+                : launch_both<__half, 64, 4, 2, 128>(p, dout, q, k, v, o, lse, delta, dq, dk, dv, passes, status, stream, fused);
   }
   // D = 128: shared memory holds one stationary pair (64 KB) and 128 KB of streamed tiles.
   // As 64-row tiles that is four stages in flight instead of two, and the narrower T tiles
   // leave TMEM columns for separate P / dS operands, i.e. for the one-iteration lookahead.
-  return bf16 ? launch_both<__nv_bfloat16, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused)
-              : launch_both<__half, 128, 4, 1, 64>(p, dout, q, k, v, lse, delta, dq, dk, dv, passes, status, stream, fused);
+  return bf16 ? launch_both<__nv_bfloat16, 128, 4, 1, 64>(p, dout, q, k, v, o, lse, delta, dq, dk, dv, passes, status, stream, fused)
+              : launch_both<__half, 128, 4, 1, 64>(p, dout, q, k, v, o, lse, delta, dq, dk, dv, passes, status, stream, fused);
 }
 
 

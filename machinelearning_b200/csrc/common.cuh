@@ -184,10 +184,15 @@ int ensure_dynamic_smem(const void* kernel, int bytes);
 
 int sm_count();
 
-// True unless NLFA_PDL=0: the tensor-core kernels are launched with programmatic stream
-// serialization, so a kernel's set-up (barriers, TMEM, descriptors) overlaps its predecessor's
-// last CTAs, and the dQ pass fills the SMs the dK/dV pass leaves.
-bool overlap_launches();
+// Which kernels are launched with programmatic stream serialization, so that their set-up
+// (barriers, TMEM, descriptors) overlaps the predecessor's last CTAs.  NLFA_PDL=<mask> overrides
+// the default (0: none).
+enum { kOverlapFwd = 1, kOverlapDelta = 2, kOverlapDkv = 4, kOverlapDq = 8, kOverlapDefault = 15 };
+bool overlap_launches(int kernel);
+
+// Whether the tensor-core backward forms Delta inside its dQ pass for this problem and mask
+// (bwd_tc.cu); then it launches two kernels instead of three.
+bool bwd_delta_in_dq(const Problem& p, int passes);
 
 // One launch through cudaLaunchKernelEx, with the programmatic-serialization attribute when
 // `overlap` is set.  The kernel must then call grid_dep_wait() before it reads anything an earlier

@@ -775,7 +775,7 @@ int launch_t(const Problem& p, const CUtensorMap& mq, const CUtensorMap& mk, con
   const int sst = sched_counters(stream, &fp.sched);
   if (sst != NLFA_OK) return sst;
   const int grid = fp.total_units < sm_count() ? fp.total_units : sm_count();
-  if (launch_kernel(kern, dim3(grid), dim3(NT * 128 + 128), L::kDynamic, stream, overlap_launches(), mq, mk, mv, mo,
+  if (launch_kernel(kern, dim3(grid), dim3(NT * 128 + 128), L::kDynamic, stream, overlap_launches(kOverlapFwd), mq, mk, mv, mo,
                     fp) != cudaSuccess) {
     (void)cudaGetLastError();
     return NLFA_ERR_CUDA;

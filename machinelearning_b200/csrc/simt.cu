@@ -311,7 +311,7 @@ int delta_t(const Problem& p, const void* dout, const void* o, float* delta, cud
   if constexpr (sizeof(T) == 2 && (D == 64 || D == 128)) {
     constexpr int kRowsPerBlock = 8 * (32 / (D / 8));           // 8 warps per block
     const unsigned blocks = static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock);
-    if (launch_kernel(delta_vec_kernel<T, D>, dim3(blocks), dim3(256), 0, s, overlap_launches(), p,
+    if (launch_kernel(delta_vec_kernel<T, D>, dim3(blocks), dim3(256), 0, s, overlap_launches(kOverlapDelta), p,
                       static_cast<const T*>(dout), static_cast<const T*>(o), delta) != cudaSuccess) {
       (void)cudaGetLastError();
       return NLFA_ERR_CUDA;

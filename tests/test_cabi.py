@@ -121,3 +121,28 @@ def test_mask_geometry_rejects_bad_arguments(lib):
     assert lib.nlfa_check_mask_geometry(256, 8, 8, 128) < 0
     assert lib.nlfa_check_mask_geometry(256, 0, 4, 128) < 0
     assert lib.nlfa_check_mask_geometry(256, 0, 0, 96) < 0
+
+
+def test_backward_kernel_count_follows_the_layout(lib):
+    """``nlfa_bwd_kernel_count``: Delta + dK/dV + dQ; two kernels where the dQ pass forms Delta (head dim
+    64, tensor-core path, a large problem -- every problem is large next to the one SM a machine
+    without a GPU reports); Delta + pass + convert for the one-pass layout; 0 for what is refused."""
+    from machinelearning_b200 import _lib
+    count = lib.nlfa_bwd_kernel_count
+    bf16, f32 = _lib.DTYPE_BF16, _lib.DTYPE_F32
+    tensor, simt = _lib.PATH_TENSOR, _lib.PATH_SIMT
+    assert count(32, 1024, 12, 128, bf16, tensor, _lib.PASS_ALL) == 3
+    assert count(32, 1024, 12, 32, bf16, tensor, _lib.PASS_ALL) == 3
+    assert count(32, 1024, 12, 64, f32, simt, _lib.PASS_ALL) == 3
+    assert count(32, 1024, 12, 64, bf16, simt, _lib.PASS_ALL) == 3
+    assert count(32, 1024, 12, 64, bf16, tensor, _lib.PASS_DKV) == 1
+    assert count(32, 1024, 12, 64, bf16, tensor, _lib.PASS_DELTA | _lib.PASS_DKV) == 2
+    assert count(32, 1024, 12, 64, bf16, tensor, _lib.PASS_DELTA | _lib.PASS_FUSED) == 3
+    assert count(32, 1024, 12, 64, bf16, tensor, _lib.PASS_FUSED | _lib.PASS_DQ) == 0
+    assert count(32, 1024, 12, 128, bf16, tensor, _lib.PASS_FUSED) == 0
+    assert count(32, 1024, 12, 64, f32, tensor, _lib.PASS_ALL) == 0
+    assert count(0, 1024, 12, 64, bf16, tensor, _lib.PASS_ALL) == 0
+    assert count(32, 1024, 12, 64, bf16, tensor, 0) == 0
+    # the large-problem layout (needs the device's SM count on a GPU box; 4,096 x 12 x 8 tiles is large anywhere)
+    assert count(4096, 1024, 12, 64, bf16, tensor, _lib.PASS_ALL) == 2
+    assert count(4096, 1024, 12, 64, bf16, tensor, _lib.PASS_DELTA | _lib.PASS_DQ) == 1

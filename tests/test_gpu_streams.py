@@ -91,3 +91,41 @@ print("digest", h.hexdigest())
         assert r.returncode == 0, r.stderr[-2000:]
         digests.append(r.stdout.strip().splitlines()[-1])
     assert digests[0] == digests[1]
+
+
+def test_delta_formed_in_the_dq_pass_gives_the_bits_of_the_delta_kernel():
+    """Large problems at head dim 64 skip the Delta kernel: the dQ pass forms the row sums of dO * O
+    itself (same additions in the same order) and runs before the dK/dV pass.  ``NLFA_DELTA_IN_DQ``
+    forces either layout; every gradient must agree bit for bit, causal, windowed and block-causal,
+    with query rows past the end of the last tile."""
+    import os
+    import subprocess
+    import sys
+    import pathlib
+    root = pathlib.Path(__file__).resolve().parent.parent
+    script = f"""
+import sys, math, hashlib
+sys.path.insert(0, {str(root)!r})
+import torch
+from machinelearning_b200 import flash_cuda as fc
+assert fc.mma_available(), fc.mma_unavailable_reason()
+h = hashlib.sha256()
+for (B, T, H, Hkv, w, s, blk) in ((3, 700, 4, 2, 0, 0, 0), (2, 1000, 6, 6, 128, 4, 0), (2, 517, 4, 1, 0, 0, 96), (40, 1024, 12, 12, 0, 0, 0)):
+    g = torch.Generator(device="cuda").manual_seed(6)
+    mk = lambda heads: torch.randn(B, T, heads, 64, device="cuda", generator=g).bfloat16()
+    q, k, v, d = mk(H), mk(Hkv), mk(Hkv), mk(H)
+    for _ in range(3):
+        o, lse = fc.fwd(q, k, v, 0.125, True, w, s, blk)
+        grads = fc.bwd(d, q, k, v, o, lse, 0.125, True, w, s, block=blk)
+    torch.cuda.synchronize()
+    for t in grads:
+        h.update(t.cpu().contiguous().view(torch.uint8).numpy().tobytes())
+print("digest", h.hexdigest())
+"""
+    digests = []
+    for flag in ("1", "0"):
+        env = dict(os.environ, NLFA_DELTA_IN_DQ=flag)
+        r = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, timeout=300, env=env)
+        assert r.returncode == 0, r.stderr[-2000:]
+        digests.append(r.stdout.strip().splitlines()[-1])
+    assert digests[0] == digests[1]
