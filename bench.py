@@ -628,8 +628,8 @@ def run_whole_model_reference_arm(args, rank):
 
 def nanolab_own_bench(batch):
     """nanolab's own ``bench_gpu.bench`` (``nanolab/bench_gpu.py:41-110``: its GPT, Muon + AdamW, eager
-    launches, wall clock), unmodified, with this package injected as ``nanolab.flash_cuda`` -- flag on and
-    off.  Runs in a child process (``nanolab.mixers`` binds the module at import time); needs the staged
+    launches, wall clock), unmodified, with this package injected as ``nanolab.flash_cuda`` -- flag on,
+    flag off, and flag on with ``mixer_glue.fuse_mixer()`` (the mixer's elementwise passes fused as well).  Runs in a child process (``nanolab.mixers`` binds the module at import time); needs the staged
     copy of the reference's caller (``oracle/build_ref.py``) and answers why not when it is absent."""
     code = f"""
 import sys, json
@@ -653,12 +653,15 @@ def counted(*a, **k):
     calls["n"] += 1
     return real(*a, **k)
 flash_cuda.fwd = counted
-for flag in (True, False):
+for arm, flag, fused in (("flash_cuda_on", True, False), ("flash_cuda_off", False, False),
+                        ("flash_cuda_on_fused_mixer", True, True)):
+    if fused:       # Attention.forward through the prologue, blend, core and gate kernels (mixer_glue.fuse_mixer)
+        mixer_glue.fuse_mixer()
     cfg = build_config("phase1", dict(run_name="bench", batch_size={batch}, block_size=1024, grad_accum=1,
                                       flash_cuda=flag, compile=False, dtype="bf16"))
     calls["n"] = 0
     r = bench_gpu.bench(cfg, peak_flops=1.0)
-    out["flash_cuda_on" if flag else "flash_cuda_off"] = {{
+    out[arm] = {{
         "tokens_per_s": r["tok_s"], "ms_per_step": r["ms_per_step"], "fwd_ms": r["fwd_ms"], "bwd_ms": r["bwd_ms"],
         "opt_ms": r["opt_ms"], "loss": r["loss"], "library_forward_calls": calls["n"]}}
     torch.cuda.empty_cache()

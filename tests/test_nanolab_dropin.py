@@ -204,3 +204,68 @@ def test_real_gpt_in_its_diffusion_modes_through_attention_core():
     print("diffusion ok")
     """)
     assert "diffusion ok" in out
+
+
+@needs_nanolab
+def test_fused_mixer_is_inert_on_cpu():
+    """``mixer_glue.fuse_mixer()`` replaces nanolab's ``Attention.forward``; a step the kernels cannot take
+    (CPU tensors here) must go to nanolab's own forward: loss and every gradient bit-identical to the
+    unpatched class, flag on or off."""
+    out = run_script("""
+        def toy(flag):
+            torch.manual_seed(0)
+            cfg = build_config(None, dict(vocab_size=256, device="cpu", dtype="fp32", n_layer=2, d_model=64, n_head=4,
+                                          n_kv_head=2, head_dim=16, block_size=32, batch_size=4, compile=False,
+                                          mixer="attention", flash_cuda=flag))
+            return build_model(cfg), cfg
+        def run(flag):
+            m, cfg = toy(flag)
+            g = torch.Generator().manual_seed(0)
+            x = torch.randint(0, cfg.vocab_size, (cfg.batch_size, cfg.block_size), generator=g)
+            _, loss = m(x, x.clone())
+            loss.backward()
+            return loss.detach(), [p.grad.clone() for p in m.parameters() if p.grad is not None]
+        plain = {flag: run(flag) for flag in (False, True)}
+        mixer_glue.fuse_mixer()
+        assert mixers.Attention.forward is mixer_glue.fused_attention_forward
+        for flag in (False, True):
+            loss, grads = run(flag)
+            assert torch.equal(loss, plain[flag][0])
+            assert len(grads) == len(plain[flag][1]) and all(torch.equal(a, b) for a, b in zip(grads, plain[flag][1]))
+        mixer_glue.unfuse_mixer()
+        assert mixers.Attention.forward is not mixer_glue.fused_attention_forward
+        print("fused inert ok")
+    """)
+    assert "fused inert ok" in out
+
+
+@needs_nanolab
+@pytest.mark.gpu
+def test_real_gpt_with_the_fused_mixer_trains_like_the_plain_one():
+    """nanolab's own ``GPT`` with ``fuse_mixer()``: QK-norm + RoPE, the value-residual blend, the attention
+    core and the head gate all through the kernels -- losses over three optimiser steps and every
+    gradient at trained weights against the flag-off model (torch passes + SDPA), causal and SWA."""
+    out = run_script(GPU_COMMON + """
+    from machinelearning_b200 import qk_prologue, value_gate
+    mixer_glue.fuse_mixer()
+    seen = {"prologue": 0, "blend": 0, "gate": 0}
+    def counting(mod, name, key):
+        real = getattr(mod, name)
+        def f(*a, **k):
+            seen[key] += 1
+            return real(*a, **k)
+        setattr(mod, name, f)
+    counting(qk_prologue, "qk_prologue", "prologue")
+    counting(value_gate, "value_blend", "blend")
+    counting(value_gate, "head_gate", "gate")
+    for kw in ({}, dict(mixer="swa", swa_window=64, swa_sinks=4)):
+        before = dict(seen)
+        l_on, l_off, worst = compare(kw)
+        # three training steps and one gradient evaluation of the flag-on model, two layers each
+        assert seen["prologue"] - before["prologue"] == 4 * 2 * 2, seen       # q and k
+        assert seen["gate"] - before["gate"] == 4 * 2, seen
+        assert seen["blend"] - before["blend"] == 4 * 1, seen                 # the first layer has no v0
+        print("fused", kw, l_on, l_off, worst)
+    print("fused mixer ok")
+    """)
+    assert "fused mixer ok" in out
