@@ -35,7 +35,7 @@ STAGED = HERE / "_ref" / "nanolab"
 # the modules the attention caller imports, directly or not (nanolab/model.py:22-23,
 # nanolab/bench_gpu.py:24-27); flash_cuda.py is staged too, as the module this package replaces
 NANOLAB_MODULES = ("__init__", "config", "mixers", "model", "optim", "utils", "bench_gpu", "flash_cuda",
-                   "schedules")
+                   "schedules", "data", "diffusion", "bench_modes")
 
 
 def _reference_root(ref_root: str | None) -> pathlib.Path:

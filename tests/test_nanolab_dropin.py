@@ -269,3 +269,65 @@ def test_real_gpt_with_the_fused_mixer_trains_like_the_plain_one():
     print("fused mixer ok")
     """)
     assert "fused mixer ok" in out
+
+
+@needs_nanolab
+@pytest.mark.gpu
+def test_real_cached_block_forward_through_the_fused_mixer():
+    """nanolab's own ``GPT.forward_hidden_window`` (``nanolab/model.py:329-362``: ``Attention.forward_cached`` in
+    every layer, with commits) block by block, with and without ``fuse_mixer()``: same hidden states and the
+    same caches (layout, positions, eviction), for a bidirectional block, a causal block and SWA with
+    eviction, in fp32 and bf16; late blocks are long enough for the tensor-core kernel."""
+    out = run_script("""
+    assert ours.is_available(), ours.unavailable_reason()
+    calls = {"n": 0}
+    real = ours.flash_attn_cached
+    def counted(*a, **k):
+        calls["n"] += 1
+        return real(*a, **k)
+    ours.flash_attn_cached = counted
+    blocks = (96, 64, 128, 32, 48)
+    mixer_glue.CACHED_MIN_WORK = 0                      # these blocks are small; take the kernels anyway
+    for dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 3e-2)):
+        for tag, kw, causal in (("bidirectional", {}, False), ("causal", {}, True),
+                                ("swa", dict(mixer="swa", swa_window=64, swa_sinks=4), True)):
+            torch.manual_seed(0)
+            cfg = build_config(None, dict(vocab_size=512, device="cuda", dtype="fp32", n_layer=2, d_model=256,
+                                          n_head=4, n_kv_head=2, head_dim=64, block_size=512, batch_size=2,
+                                          compile=False, flash_cuda=True, dropout=0.0, **({"mixer": "attention"} | kw)))
+            model = build_model(cfg).cuda().to(dtype).eval()
+            with torch.no_grad():
+                for p in model.parameters():           # off the zero-initialised projections
+                    p.add_(torch.randn_like(p) * 0.02)
+            g = torch.Generator().manual_seed(5)
+            tokens = torch.randint(0, cfg.vocab_size, (2, sum(blocks)), generator=g).cuda()
+
+            def drive():
+                caches = [{} for _ in model.blocks]
+                hidden, start = [], 0
+                with torch.no_grad():
+                    for n in blocks:
+                        hidden.append(model.forward_hidden_window(tokens[:, start:start + n], start, caches, True, causal))
+                        start += n
+                return hidden, caches
+
+            want_h, want_c = drive()
+            mixer_glue.fuse_mixer()
+            before = calls["n"]
+            got_h, got_c = drive()
+            mixer_glue.unfuse_mixer()
+            assert calls["n"] - before == len(blocks) * cfg.n_layer, calls
+            for a, b in zip(got_h, want_h):
+                err = (a.float() - b.float()).abs().max().item() / b.float().abs().max().item()
+                assert err <= tol, (tag, dtype, err)
+            for ca, cb in zip(got_c, want_c):
+                assert set(ca) == set(cb), (tag, set(ca), set(cb))
+                assert ca["k"].shape == cb["k"].shape and ca["v"].shape == cb["v"].shape
+                if "pos" in cb:
+                    assert torch.equal(ca["pos"], cb["pos"]) and ca["end"] == cb["end"]
+                kerr = (ca["k"].float() - cb["k"].float()).abs().max().item() / cb["k"].float().abs().max().item()
+                assert kerr <= tol, (tag, dtype, kerr)
+            print(tag, dtype, "ok")
+    print("cached mixer ok")
+    """)
+    assert "cached mixer ok" in out
