@@ -390,6 +390,8 @@ def flash_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     if torch.compiler.is_compiling():
         from . import compile_ops              # registered operators: one graph node instead of a graph break
         return compile_ops.attn_fwd(q, k, v, float(scale), bool(use_mma), int(window), int(sinks), int(block))[0]
+    if not (torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)):
+        return fwd(q, k, v, scale, use_mma, window, sinks, block)[0]       # inference: no autograd node
     return _FlashAttnFn.apply(q, k, v, scale, use_mma, window, sinks, block)
 
 
@@ -437,14 +439,14 @@ def flash_attn_cached(q: torch.Tensor, k_full: torch.Tensor, v_full: torch.Tenso
     lse = torch.empty((B, H, T), dtype=torch.float32, device=q.device) if return_lse else None
     nbytes = lib.nlfa_fwd_cached_scratch_bytes(B, T, H, Hkv, L, D)      # > 0: the keys are split over CTAs
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
-    with torch.cuda.device(q.device):
+    with _on_device(q.device.index):
         path = _lib.PATH_AUTO if use_mma is None else (_lib.PATH_TENSOR if use_mma else _lib.PATH_SIMT)
         st = lib.nlfa_fwd_cached_path(q.data_ptr(), k_full.data_ptr(), v_full.data_ptr(), o.data_ptr(),
                                       None if lse is None else lse.data_ptr(),
                                       None if qp is None else qp.data_ptr(), None if kp is None else kp.data_ptr(),
                                       B, T, H, Hkv, L, D, float(scale), int(bool(causal)), int(window), int(sinks),
                                       _DTYPE_CODE[q.dtype], path, None if scratch is None else scratch.data_ptr(),
-                                      nbytes, torch.cuda.current_stream().cuda_stream)
+                                      nbytes, _stream_of(q.device.index))
     if st == 7 and use_mma:
         raise ValueError("flash_attn_cached: use_mma=True but the tensor-core kernel does not apply to these inputs")
     _lib.check("nlfa_fwd_cached", st)

@@ -60,11 +60,13 @@ def fwd(x, weight, cos, sin, eps: float, out_dtype):
     B, T, H, D = x.shape
     y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
     rstd = torch.empty(B * T * H if weight is not None else 1, dtype=torch.float32, device=x.device)
-    with torch.cuda.device(x.device):
+    index = x.device.index
+    with flash_cuda._on_device(index):
         st = lib.nlfa_qk_prologue_fwd(x.data_ptr(), _DTYPE_CODE[x.dtype], _ptr(weight), _ptr(cos), _ptr(sin),
                                       y.data_ptr(), _DTYPE_CODE[out_dtype], rstd.data_ptr(),
-                                      B, T, H, D, float(eps), torch.cuda.current_stream().cuda_stream)
-    _lib.check("nlfa_qk_prologue_fwd", st)
+                                      B, T, H, D, float(eps), flash_cuda._stream_of(index))
+    if st:
+        _lib.check("nlfa_qk_prologue_fwd", st)
     return y, rstd
 
 
@@ -78,12 +80,14 @@ def bwd(gy, x, weight, cos, sin, rstd):
     gw = torch.empty(D if weight is not None else 1, dtype=torch.float32, device=x.device)
     nbytes = lib.nlfa_qk_prologue_scratch_bytes(D) if weight is not None else 0
     scratch = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    index = x.device.index
+    with flash_cuda._on_device(index):
         st = lib.nlfa_qk_prologue_bwd(gy.data_ptr(), _DTYPE_CODE[gy.dtype], x.data_ptr(), _DTYPE_CODE[x.dtype],
                                       _ptr(weight), _ptr(cos), _ptr(sin), rstd.data_ptr(), gx.data_ptr(),
                                       gw.data_ptr() if weight is not None else None, scratch.data_ptr(),
-                                      scratch.numel(), B, T, H, D, torch.cuda.current_stream().cuda_stream)
-    _lib.check("nlfa_qk_prologue_bwd", st)
+                                      scratch.numel(), B, T, H, D, flash_cuda._stream_of(index))
+    if st:
+        _lib.check("nlfa_qk_prologue_bwd", st)
     return gx, gw
 
 
@@ -122,6 +126,9 @@ def qk_prologue(x: torch.Tensor, weight=None, cos=None, sin=None, eps: float = E
     if torch.compiler.is_compiling():
         from . import compile_ops              # registered operators: one graph node instead of a graph break
         return compile_ops.qk_prologue(x, weight, cos, sin, eps, out_dtype)
+    if not (torch.is_grad_enabled() and (x.requires_grad or (weight is not None and weight.requires_grad))):
+        # nothing to differentiate (inference): the kernel alone, no autograd node
+        return fwd(x.contiguous(), _f32(weight), _f32(cos), _f32(sin), eps, out_dtype)[0]
     return _QkPrologueFn.apply(x, weight, cos, sin, eps, out_dtype)
 
 

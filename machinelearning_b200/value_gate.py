@@ -28,8 +28,8 @@ def _lib_or_raise():
     return lib
 
 
-def _stream():
-    return torch.cuda.current_stream().cuda_stream
+def _stream(t):
+    return flash_cuda._stream_of(t.device.index)
 
 
 def supports_blend(v: torch.Tensor, v0: torch.Tensor, lam: torch.Tensor) -> bool:
@@ -46,9 +46,9 @@ def blend_fwd(v, v0, lam32, out_dtype):
     """The blend through the C ABI: contiguous ``v`` / ``v0`` of one dtype, ``lam32`` one float32 on the device."""
     lib = _lib_or_raise()
     out = torch.empty(v.shape, dtype=out_dtype, device=v.device)
-    with torch.cuda.device(v.device):
+    with flash_cuda._on_device(v.device.index):
         st = lib.nlfa_value_blend_fwd(v.data_ptr(), v0.data_ptr(), _DTYPE_CODE[v.dtype], lam32.data_ptr(),
-                                      out.data_ptr(), _DTYPE_CODE[out_dtype], v.numel(), _stream())
+                                      out.data_ptr(), _DTYPE_CODE[out_dtype], v.numel(), _stream(v))
     _lib.check("nlfa_value_blend_fwd", st)
     return out
 
@@ -59,10 +59,10 @@ def blend_bwd(g, v, v0, lam32):
     dv, dv0 = torch.empty_like(v), torch.empty_like(v0)
     dlam = torch.empty(1, dtype=torch.float32, device=v.device)
     scratch = torch.empty(lib.nlfa_value_blend_scratch_bytes(), dtype=torch.uint8, device=v.device)
-    with torch.cuda.device(v.device):
+    with flash_cuda._on_device(v.device.index):
         st = lib.nlfa_value_blend_bwd(g.data_ptr(), _DTYPE_CODE[g.dtype], v.data_ptr(), v0.data_ptr(),
                                       _DTYPE_CODE[v.dtype], lam32.data_ptr(), dv.data_ptr(), dv0.data_ptr(),
-                                      dlam.data_ptr(), scratch.data_ptr(), scratch.numel(), v.numel(), _stream())
+                                      dlam.data_ptr(), scratch.data_ptr(), scratch.numel(), v.numel(), _stream(v))
     _lib.check("nlfa_value_blend_bwd", st)
     return dv, dv0, dlam
 
@@ -71,9 +71,9 @@ def gate_fwd(y, gate):
     lib = _lib_or_raise()
     out = torch.empty_like(y)
     rows, D = y.numel() // y.shape[-1], y.shape[-1]
-    with torch.cuda.device(y.device):
+    with flash_cuda._on_device(y.device.index):
         st = lib.nlfa_head_gate_fwd(y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(), _DTYPE_CODE[gate.dtype],
-                                    out.data_ptr(), rows, D, _stream())
+                                    out.data_ptr(), rows, D, _stream(y))
     _lib.check("nlfa_head_gate_fwd", st)
     return out
 
@@ -83,9 +83,9 @@ def gate_bwd(g, y, gate):
     lib = _lib_or_raise()
     dy, dgate = torch.empty_like(y), torch.empty_like(gate)
     rows, D = y.numel() // y.shape[-1], y.shape[-1]
-    with torch.cuda.device(y.device):
+    with flash_cuda._on_device(y.device.index):
         st = lib.nlfa_head_gate_bwd(g.data_ptr(), y.data_ptr(), _DTYPE_CODE[y.dtype], gate.data_ptr(),
-                                    _DTYPE_CODE[gate.dtype], dy.data_ptr(), dgate.data_ptr(), rows, D, _stream())
+                                    _DTYPE_CODE[gate.dtype], dy.data_ptr(), dgate.data_ptr(), rows, D, _stream(y))
     _lib.check("nlfa_head_gate_bwd", st)
     return dy, dgate
 
@@ -132,6 +132,10 @@ def value_blend(v: torch.Tensor, v0: torch.Tensor, lam: torch.Tensor, out_dtype=
     if torch.compiler.is_compiling():
         from . import compile_ops              # registered operators: one graph node instead of a graph break
         return compile_ops.value_blend(v, v0, lam, out_dtype)
+    if not (torch.is_grad_enabled() and (v.requires_grad or v0.requires_grad or lam.requires_grad)):
+        # nothing to differentiate (inference): the kernel alone, no autograd node
+        return blend_fwd(v.contiguous(), v0.contiguous(), lam.detach().to(torch.float32).reshape(1).contiguous(),
+                         out_dtype)
     return _ValueBlendFn.apply(v, v0, lam, out_dtype)
 
 
@@ -143,6 +147,8 @@ def head_gate(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     if torch.compiler.is_compiling():
         from . import compile_ops
         return compile_ops.head_gate(y, gate)
+    if not (torch.is_grad_enabled() and (y.requires_grad or gate.requires_grad)):
+        return gate_fwd(y.contiguous(), gate.contiguous())
     return _HeadGateFn.apply(y, gate)
 
 
