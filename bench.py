@@ -371,6 +371,32 @@ def other_workload(name, dev, iters=5):
     return rec
 
 
+def same_box_comparison(shape, dev, iters=20):
+    """The public call a user makes -- ``flash_attn`` + autograd -- next to torch's SDPA (what nanolab's
+    mixer runs with the flag off) on the same inputs and GPU: forward and forward + backward, both as
+    calls back to back between two events (throughput) and as the median of calls timed one at a time
+    with a synchronisation each (what the reference's self-check prints, ``flash_cuda.py:297-312``).
+    Plain causal shapes only (``sdpa_reference`` is the causal arm)."""
+    from machinelearning_b200 import flash_cuda
+    B, T, H, Hkv, D, window, sinks = shape
+    q, k, v, do = make_inputs(shape, 77, dev)
+    q, k, v = (t.requires_grad_() for t in (q, k, v))
+    scale = 1.0 / math.sqrt(D)
+    arms = {"these_kernels": lambda: flash_cuda.flash_attn(q, k, v, scale),
+            "torch_sdpa": lambda: flash_cuda.sdpa_reference(q, k, v, scale)}
+    out = {"what": "flash_attn / SDPA through autograd on resident inputs, ms; back_to_back = calls queued between "
+                   "two events, per_call = median of calls synchronised one at a time", "iters": iters}
+    for name, fwd in arms.items():
+        both = lambda fwd=fwd: torch.autograd.grad(fwd(), (q, k, v), do)
+        for _ in range(5):
+            both()
+        out[name] = {"back_to_back": {"fwd": time_region(fwd, iters), "fwd_bwd": time_region(both, iters)},
+                     "per_call": {"fwd": flash_cuda._median_ms(fwd, iters), "fwd_bwd": flash_cuda._median_ms(both, iters)}}
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_gpu_arm(args, shape, rank, world, local_rank):
     import torch.distributed as dist
     from machinelearning_b200 import flash_cuda, host_pipeline, sharding
@@ -573,6 +599,8 @@ def run_gpu_arm(args, shape, rank, world, local_rank):
             others["c3"]["frac_of_hbm_peak"] = others["c3"]["algorithmic_gb_per_s"] / measured_hbm()
         if others:
             line["other_workloads"] = others
+        if window == 0 and not args.no_other_workloads:
+            line["same_box_comparison"] = same_box_comparison(local_shape, dev)
     if cpu:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
