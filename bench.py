@@ -349,7 +349,7 @@ def algorithmic_bytes(B, T, H, Hkv, D):
     """(forward, backward) bytes that have to move: every input and output once, plus the fp32 rows."""
     qo, kv, rows = B * T * H * D * 2, B * T * Hkv * D * 2, B * H * T * 4
     fwd = 2 * qo + 2 * kv + rows                            # q, o, k, v, lse
-    bwd = 4 * qo + 4 * kv + 3 * rows                        # q, o, dO, dq, k, v, dk, dv, lse, Delta w+r
+    bwd = 4 * qo + 4 * kv + 4 * rows                        # q, o, dO, dq, k, v, dk, dv, lse, Delta written, read twice
     return fwd, bwd
 
 
