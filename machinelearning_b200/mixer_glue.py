@@ -166,13 +166,12 @@ def fused_attention_forward(self, x, cos, sin, v0=None):
     return self.o_proj(y.reshape(B, T, H * D)), raw_v
 
 
-# Query rows x keys below which a cached block forward stays with nanolab's own lines.  A block that
-# small is bound by the host's launches, not by the GPU, and there the handful of torch calls it
-# replaces cost the host no more than the calls into this library: nanolab's own samplers (one sequence,
-# 32-token blocks, the 124M model) measured 683 tokens/s on nanolab's lines and 551-603 through the
-# kernels.  Batched decoding (8 sequences, 32-token blocks over 1,056 keys: 3.2 M) is where the kernels
-# are 3-8x faster than the lines they replace.
-CACHED_MIN_WORK = 1 << 20
+# Query rows x keys below which a cached block forward stays with nanolab's own lines (0: every block
+# goes through the kernels).  Even a single sequence in 32-token blocks gains -- nanolab's own
+# `sample_blockwise_cached` on the 124M model: 683 -> 746 tokens/s, `forward_hidden_window` alone 1.6x --
+# because such blocks are bound by the host's launches and the fused path makes a third as many; the knob
+# is for callers whose host path differs.
+CACHED_MIN_WORK = 0
 
 
 def _cached_step_declined(self, x, causal, cache) -> bool:
@@ -303,7 +302,12 @@ def main() -> int:
     ap.add_argument("--block", type=int, default=32)
     ap.add_argument("--context", type=int, default=1024)
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--min-work", type=int, default=None,
+                    help="override CACHED_MIN_WORK (0: every block through the kernels)")
     args = ap.parse_args()
+    if args.min_work is not None:
+        global CACHED_MIN_WORK
+        CACHED_MIN_WORK = args.min_work
     if not torch.cuda.is_available() or not flash_cuda.is_available():
         print(f"nothing to run: {flash_cuda.unavailable_reason() or 'no CUDA device'}")
         return 1

@@ -287,7 +287,6 @@ def test_real_cached_block_forward_through_the_fused_mixer():
         return real(*a, **k)
     ours.flash_attn_cached = counted
     blocks = (96, 64, 128, 32, 48)
-    mixer_glue.CACHED_MIN_WORK = 0                      # these blocks are small; take the kernels anyway
     for dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 3e-2)):
         for tag, kw, causal in (("bidirectional", {}, False), ("causal", {}, True),
                                 ("swa", dict(mixer="swa", swa_window=64, swa_sinks=4), True)):
