@@ -102,9 +102,10 @@ size_t nlfa_bwd_scratch_bytes(int B, int T, int H);
 
 /* Backward: Delta = rowsum(dO * O), then dQ, dK, dV with P recomputed from the
  * taped lse.  Replaces `flash_attn_bwd` (nanolab/csrc/flash_attn_cuda.cu:1744-1813)
- * and its launch sequence (:1518-1587): Delta kernel, dQ kernel, dK/dV kernel on
- * one stream, no atomics, bit-reproducible.  `scratch` must hold
- * nlfa_bwd_scratch_bytes(B, T, H) bytes. */
+ * and its launch sequence (:1518-1587): Delta kernel, dK/dV kernel, dQ kernel on
+ * one stream (two kernels for large problems at D = 64, see
+ * nlfa_bwd_kernel_count), no atomics, bit-reproducible.  `scratch` must hold
+ * nlfa_bwd_scratch_bytes(B, T, H) bytes; Delta is left in it. */
 int nlfa_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
              const float* lse, void* dq, void* dk, void* dv, void* scratch, size_t scratch_bytes,
              int B, int T, int H, int Hkv, int D, float scale, int window, int sinks, int dtype,
