@@ -127,3 +127,63 @@ def test_block_causal_and_bidirectional_steps_route_through_the_kernel(kw, block
     assert y is not None and not m._flash_declined
     ref, _ = attention_f64.attention_fwd(q.double().numpy(), k.double().numpy(), v.double().numpy(), 0.125, block=block)
     assert np.abs(y.float().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max()
+
+
+def _fake_package(name):
+    """A stand-in for nanolab: ``<name>.mixers`` bound to this package's ``flash_cuda`` with an ``Attention``
+    whose ``forward`` / ``forward_cached`` record their calls."""
+    pkg = types.ModuleType(name)
+    mixers = types.ModuleType(f"{name}.mixers")
+    mixers.flash_cuda = flash_cuda
+
+    class Attention(FakeMixer):
+        def forward(self, x, cos, sin, v0=None):
+            return ("plain forward", x.shape)
+
+        def forward_cached(self, x, cos, sin, v0, cache, commit, causal=False):
+            return ("plain forward_cached", commit, causal)
+
+    mixers.Attention = Attention
+    sys.modules[name] = pkg
+    sys.modules[f"{name}.mixers"] = mixers
+    sys.modules[f"{name}.flash_cuda"] = flash_cuda
+    return mixers
+
+
+def test_fuse_mixer_patches_and_hands_declined_steps_to_the_own_methods():
+    """``fuse_mixer`` swaps the class's two methods, ``unfuse_mixer`` restores them, and every step the kernels
+    decline before touching the projections (flag off, CPU tensors; for the cached step also gradients being
+    recorded or a window without ``causal``) goes to the class's own method with its arguments intact."""
+    mixers = _fake_package("fakelab3")
+    try:
+        own_forward, own_cached = mixers.Attention.forward, mixers.Attention.forward_cached
+        mixer_glue.fuse_mixer("fakelab3")
+        assert mixers.Attention.forward is mixer_glue.fused_attention_forward
+        assert mixers.Attention.forward_cached is mixer_glue.fused_attention_forward_cached
+        mixer_glue.fuse_mixer("fakelab3")                                     # idempotent
+        x = torch.zeros(2, 8, 16)
+        for kw in (dict(flash_cuda=False), dict()):                          # flag off; flag on but CPU tensors
+            m = mixers.Attention(**kw)
+            assert m.forward(x, None, None) == ("plain forward", x.shape)
+            assert m.forward_cached(x, None, None, None, {}, True, causal=True) == ("plain forward_cached", True, True)
+        with torch.no_grad():
+            m = mixers.Attention(swa_window=8, swa_sinks=2)
+            assert m.forward_cached(x, None, None, None, {}, False) == ("plain forward_cached", False, False)
+        mixer_glue.unfuse_mixer("fakelab3")
+        assert mixers.Attention.forward is own_forward and mixers.Attention.forward_cached is own_cached
+        mixer_glue.unfuse_mixer("fakelab3")                                   # nothing left to undo
+    finally:
+        mixer_glue.unfuse_mixer("fakelab3")
+        for n in ("fakelab3", "fakelab3.mixers", "fakelab3.flash_cuda"):
+            sys.modules.pop(n, None)
+
+
+def test_fuse_mixer_refuses_a_package_bound_to_another_module():
+    mixers = _fake_package("fakelab4")
+    mixers.flash_cuda = types.ModuleType("someone_elses_flash_cuda")
+    try:
+        with pytest.raises(RuntimeError):
+            mixer_glue.fuse_mixer("fakelab4")
+    finally:
+        for n in ("fakelab4", "fakelab4.mixers", "fakelab4.flash_cuda"):
+            sys.modules.pop(n, None)
